@@ -1,0 +1,483 @@
+#!/usr/bin/env python
+"""Benchmark of the RMSNorm hot path (and, as side results, the SwiGLU MLP) on B200.
+
+    python bench.py --gpus N --steps K --warmup W            # this library (default N=1)
+    python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU path, host cores
+    torchrun --nproc-per-node N ... bench.py --gpus N ...    # N > 1: one rank per GPU
+
+A step is one RMSNorm forward + backward over one batch: bf16, 65536 rows x hidden 8192 per GPU
+(x ~ N(0,2), w = 1 + 0.1 N(0,1), dy ~ N(0,1), eps 1e-6, seeded). With N > 1 every rank holds its own
+row block of that size (weak scaling) and the fp32 dW partial is all-reduced over NCCL each step.
+The metric is algorithmic bytes per second, 5*R*H*s + 3*H*s + 8*R bytes per step and GPU.
+
+Rank 0 prints ONE JSON line. `value` is timed with inputs resident in HBM; `e2e` goes through the
+public module API with pinned host buffers and host<->device copies inside the timed region.
+"""
+from __future__ import annotations
+
+import argparse
+import ctypes
+import json
+import os
+import statistics
+import sys
+import threading
+import time
+from pathlib import Path
+
+ROOT = Path(__file__).resolve().parent
+if str(ROOT) not in sys.path:
+    sys.path.insert(0, str(ROOT))
+
+import torch
+
+METRIC = "RMSNorm fwd+bwd GB/s"
+UNIT = "GB/s"
+ROWS_PER_GPU = 65536
+HIDDEN = 8192
+EPS = 1e-6
+SEED = 1234
+CPU_SAMPLE_ROWS = 4096
+# DRAM bytes (read + write) per launch of the dominant kernel from one ncu capture, per algorithmic
+# byte; None until a capture has been summarised under profiles/.
+TRAFFIC_PER_ALGO_BYTE = None
+
+
+def rms_bytes(rows: int, cols: int, s: int) -> dict:
+    fwd = 2 * rows * cols * s + cols * s + 4 * rows
+    bwd = 3 * rows * cols * s + 2 * cols * s + 4 * rows
+    return {"fwd": fwd, "bwd": bwd, "total": fwd + bwd}
+
+
+def measured_peaks() -> tuple[dict, str]:
+    p = ROOT / "MEASURED_PEAKS.json"
+    if p.exists():
+        try:
+            return json.loads(p.read_text()), "measured"
+        except Exception:
+            pass
+    return {"hbm_gbs": 6650.0, "bf16_tflops": 1590.0, "bf16_tflops_sustained": 1400.0}, "fallback"
+
+
+# ---------------------------------------------------------------------------------------------------
+# clocks during the timed region (read-only NVML queries)
+# ---------------------------------------------------------------------------------------------------
+
+class ClockSampler:
+    REASONS = {0x4: "sw_power_cap", 0x8: "hw_slowdown", 0x20: "sw_thermal_slowdown", 0x40: "hw_thermal_slowdown",
+               0x80: "hw_power_brake_slowdown", 0x2: "applications_clocks_setting", 0x10: "sync_boost"}
+
+    def __init__(self, device_index: int, period_s: float = 0.005):
+        self.period = period_s
+        self.samples: list[tuple[float, int, int]] = []
+        self.max_mhz = None
+        self._stop = threading.Event()
+        self._thread = None
+        self._h = None
+        try:
+            import pynvml
+
+            pynvml.nvmlInit()
+            self._nv = pynvml
+            h = None
+            try:
+                uuid = str(torch.cuda.get_device_properties(device_index).uuid)
+                if not uuid.startswith("GPU-"):
+                    uuid = "GPU-" + uuid
+                h = pynvml.nvmlDeviceGetHandleByUUID(uuid.encode())
+            except Exception:
+                h = None
+            if h is None:
+                vis = os.environ.get("CUDA_VISIBLE_DEVICES")
+                idx = device_index
+                if vis:
+                    ent = vis.split(",")[device_index].strip()
+                    idx = int(ent) if ent.isdigit() else device_index
+                h = pynvml.nvmlDeviceGetHandleByIndex(idx)
+            self._h = h
+            self.max_mhz = int(pynvml.nvmlDeviceGetMaxClockInfo(h, pynvml.NVML_CLOCK_SM))
+        except Exception:
+            self._h = None
+
+    def _reasons(self) -> int:
+        nv = self._nv
+        for name in ("nvmlDeviceGetCurrentClocksEventReasons", "nvmlDeviceGetCurrentClocksThrottleReasons"):
+            fn = getattr(nv, name, None)
+            if fn is not None:
+                try:
+                    return int(fn(self._h))
+                except Exception:
+                    continue
+        return 0
+
+    def _run(self):
+        nv = self._nv
+        while not self._stop.is_set():
+            try:
+                mhz = int(nv.nvmlDeviceGetClockInfo(self._h, nv.NVML_CLOCK_SM))
+                self.samples.append((time.perf_counter(), mhz, self._reasons()))
+            except Exception:
+                pass
+            time.sleep(self.period)
+
+    def start(self):
+        if self._h is not None:
+            self._thread = threading.Thread(target=self._run, daemon=True)
+            self._thread.start()
+
+    def stop(self):
+        self._stop.set()
+        if self._thread is not None:
+            self._thread.join(timeout=2)
+
+    def summary(self, t0: float, t1: float) -> dict:
+        inside = [s for s in self.samples if t0 <= s[0] <= t1]
+        if not inside:
+            return {"sm_mhz": None, "sm_max_mhz": self.max_mhz, "reasons": [], "samples": 0,
+                    "note": "no NVML sample fell inside the timed region"}
+        bits = 0
+        for s in inside:
+            bits |= s[2]
+        reasons = sorted(name for bit, name in self.REASONS.items() if bits & bit)
+        return {"sm_mhz": int(statistics.median(s[1] for s in inside)), "sm_max_mhz": self.max_mhz,
+                "reasons": reasons, "samples": len(inside)}
+
+
+# ---------------------------------------------------------------------------------------------------
+# the reference's CPU path (torch formula on the host cores), used by both arms
+# ---------------------------------------------------------------------------------------------------
+
+def cpu_sample_inputs(rows: int, cols: int):
+    g = torch.Generator().manual_seed(SEED)
+    x = (2.0 ** 0.5 * torch.randn(rows, cols, generator=g)).to(torch.bfloat16)
+    w = (1 + 0.1 * torch.randn(cols, generator=g)).to(torch.bfloat16)
+    dy = torch.randn(rows, cols, generator=g).to(torch.bfloat16)
+    return x, w, dy
+
+
+def cpu_step(x, w, dy):
+    """One forward+backward of the reference formula on bf16 host tensors: fp32 math (the reference's
+    kernels accumulate in fp32), results rounded back to bf16."""
+    from oracle import oracle
+
+    y, dx, dw = oracle.rmsnorm_formula_torch(x.float(), w.float(), EPS, dy.float())
+    return y.to(torch.bfloat16), dx.to(torch.bfloat16), dw.to(torch.bfloat16)
+
+
+def time_cpu(steps: int, warmup: int, budget_s: float | None = None) -> dict:
+    x, w, dy = cpu_sample_inputs(CPU_SAMPLE_ROWS, HIDDEN)
+    for _ in range(warmup):
+        cpu_step(x, w, dy)
+    times = []
+    t_begin = time.perf_counter()
+    for _ in range(steps):
+        t0 = time.perf_counter()
+        cpu_step(x, w, dy)
+        times.append(time.perf_counter() - t0)
+        if budget_s is not None and time.perf_counter() - t_begin > budget_s:
+            break
+    per_step = sum(times) / len(times)
+    nbytes = rms_bytes(CPU_SAMPLE_ROWS, HIDDEN, 2)["total"]
+    return {"value": nbytes / per_step / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"torch formula fwd+bwd (fp32 math on bf16 tensors) on {CPU_SAMPLE_ROWS} of the {ROWS_PER_GPU} rows x {HIDDEN}, "
+                      f"{len(times)} steps, bytes counted as for the GPU arm (2 B/element)",
+            "ms_per_step": per_step * 1e3, "steps": len(times), "os_cpu_count": os.cpu_count()}
+
+
+def reference_arm(args) -> int:
+    rank = int(os.environ.get("RANK", "0"))
+    if rank != 0:
+        return 0
+    res = time_cpu(args.steps, max(args.warmup, 1))
+    line = {
+        "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
+        "steps": res["steps"], "warmup": max(args.warmup, 1), "ms_per_step": res["ms_per_step"], "higher_is_better": True,
+        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": workload_config(args.gpus),
+        "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
+        "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
+        "gpu_launches": 0,
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def workload_config(n_gpus: int) -> dict:
+    return {"workload": f"RMSNorm bf16 forward+backward, {ROWS_PER_GPU} rows x hidden {HIDDEN} per GPU, eps 1e-6 "
+                        "(x~N(0,2), w=1+0.1N(0,1), dy~N(0,1))",
+            "rows_per_gpu": ROWS_PER_GPU, "hidden": HIDDEN, "sharding": f"rows x{n_gpus}, fp32 dW all-reduce" if n_gpus > 1 else "none",
+            "l2": "inputs larger than L2 (1 GiB per tensor, 126 MB L2)", "seed": SEED}
+
+
+# ---------------------------------------------------------------------------------------------------
+# this library
+# ---------------------------------------------------------------------------------------------------
+
+def make_inputs(rows: int, cols: int, dtype, device, seed: int, x_scale: float):
+    g = torch.Generator(device=device).manual_seed(seed)
+    x = (x_scale * torch.randn(rows, cols, generator=g, device=device)).to(dtype)
+    w = (1 + 0.1 * torch.randn(cols, generator=g, device=device)).to(dtype)
+    dy = torch.randn(rows, cols, generator=g, device=device).to(dtype)
+    return x, w, dy
+
+
+class RmsBuffers:
+    """Pre-allocated device tensors for one problem; launches go straight to the C ABI."""
+
+    def __init__(self, L, rows, cols, dtype, device, seed, x_scale=1.0):
+        from mgrrmsnorm_b200 import rmsnorm_cuda_ops as ops
+
+        self.L, self.rows, self.cols = L, rows, cols
+        self.code = ops._DTYPES[dtype]
+        self.x, self.w, self.dy = make_inputs(rows, cols, dtype, device, seed, x_scale)
+        self.y = torch.empty_like(self.x)
+        self.dx = torch.empty_like(self.x)
+        self.inv = torch.empty(rows, dtype=torch.float32, device=device)
+        self.dw = torch.empty_like(self.w)
+        self.dw32 = torch.empty(cols, dtype=torch.float32, device=device)
+        nws = int(L.mgr_rmsnorm_bwd_workspace_bytes(rows, cols, self.code))
+        self.ws = torch.empty(max(nws, 16), dtype=torch.uint8, device=device)
+
+    def fwd(self, stream):
+        st = self.L.mgr_rmsnorm_fwd(self.y.data_ptr(), self.inv.data_ptr(), self.x.data_ptr(), self.w.data_ptr(),
+                                    self.rows, self.cols, EPS, self.code, stream)
+        if st:
+            raise RuntimeError(f"mgr_rmsnorm_fwd status {st}")
+
+    def bwd(self, stream):
+        st = self.L.mgr_rmsnorm_bwd(self.dx.data_ptr(), self.dw.data_ptr(), self.dw32.data_ptr(), self.dy.data_ptr(),
+                                    self.x.data_ptr(), self.w.data_ptr(), self.inv.data_ptr(), self.rows, self.cols,
+                                    self.code, self.ws.data_ptr(), self.ws.numel(), stream)
+        if st:
+            raise RuntimeError(f"mgr_rmsnorm_bwd status {st}")
+
+
+def time_device_resident(bufsets, steps, warmup, world, sampler=None):
+    """K steps over `bufsets` (rotated), CUDA events on the launching stream. Returns total ms, mean
+    fwd-call ms, mean bwd-call ms and the wall-clock window of the timed region."""
+    import torch.distributed as dist
+
+    stream = torch.cuda.current_stream()
+    sp = stream.cuda_stream
+
+    def step(b, evs=None):
+        if evs:
+            evs[0].record(stream)
+        b.fwd(sp)
+        if evs:
+            evs[1].record(stream)
+        b.bwd(sp)
+        if evs:
+            evs[2].record(stream)
+        if world > 1:
+            dist.all_reduce(b.dw32)
+            b.dw.copy_(b.dw32)
+
+    for i in range(warmup):
+        step(bufsets[i % len(bufsets)])
+    evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0.record(stream)
+    for i in range(steps):
+        step(bufsets[i % len(bufsets)], evs[i])
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    if world > 1:
+        dist.barrier()
+    total_ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([total_ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        total_ms = float(t.item())
+    fwd_ms = sum(e[0].elapsed_time(e[1]) for e in evs) / steps
+    bwd_ms = sum(e[1].elapsed_time(e[2]) for e in evs) / steps
+    return {"total_ms": total_ms, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "window": (t0, t1)}
+
+
+def time_e2e(rows, cols, device, steps, warmup, world, src):
+    """Through the public API (RMSNorm module + autograd) with pinned host buffers: every step copies
+    x and dy host->device, runs forward and backward, and copies y, dx and dW back."""
+    import torch.distributed as dist
+
+    from mgrrmsnorm_b200 import RMSNorm
+
+    dt = torch.bfloat16
+    hx = torch.empty((rows, cols), dtype=dt).pin_memory()
+    hdy = torch.empty((rows, cols), dtype=dt).pin_memory()
+    hy = torch.empty((rows, cols), dtype=dt).pin_memory()
+    hdx = torch.empty((rows, cols), dtype=dt).pin_memory()
+    hdw = torch.empty((cols,), dtype=dt).pin_memory()
+    hx.copy_(src.x)
+    hdy.copy_(src.dy)
+    norm = RMSNorm(cols, epsilon=EPS).to(device).to(dt)
+    with torch.no_grad():
+        norm.weight.copy_(src.w)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        x = hx.to(device, non_blocking=True).requires_grad_(True)
+        dy = hdy.to(device, non_blocking=True)
+        norm.weight.grad = None
+        y = norm(x)
+        y.backward(dy)
+        dw = norm.weight.grad
+        if world > 1:
+            dist.all_reduce(dw)   # public-API path: the rounded dW (the resident path reduces in fp32)
+        hy.copy_(y.detach(), non_blocking=True)
+        hdx.copy_(x.grad, non_blocking=True)
+        hdw.copy_(dw, non_blocking=True)
+
+    for _ in range(warmup):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    e0.record(stream)
+    for _ in range(steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    if world > 1:
+        dist.barrier()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device="cuda", dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    es = 2
+    return {"ms_per_step": ms / steps, "steps": steps, "h2d": 2 * rows * cols * es, "d2h": 2 * rows * cols * es + cols * es}
+
+
+def side_results(L, device, peak_gbs) -> dict:
+    """Other configurations, N=1 only: the fp16 [4096,4096] shape the reference publishes (L2-cold by
+    rotating 8 buffer sets = 1.25 GiB) and the bf16 hidden sweep at 2^29 elements."""
+    out = {}
+    sets = [RmsBuffers(L, 4096, 4096, torch.float16, device, SEED + i) for i in range(8)]
+    r = time_device_resident(sets, 400, 40, 1)
+    nb = rms_bytes(4096, 4096, 2)
+    out["rmsnorm_fp16_4096x4096"] = {
+        "l2": "cold: 8 rotating buffer sets (1.25 GiB)", "us_per_step": r["total_ms"] * 1e3 / 400,
+        "GBps": nb["total"] / (r["total_ms"] / 400 * 1e-3) / 1e9,
+        "fwd_us": r["fwd_ms"] * 1e3, "bwd_us": r["bwd_ms"] * 1e3,
+        "fwd_frac_of_peak": nb["fwd"] / (r["fwd_ms"] * 1e-3) / 1e9 / peak_gbs,
+        "bwd_frac_of_peak": nb["bwd"] / (r["bwd_ms"] * 1e-3) / 1e9 / peak_gbs}
+    del sets
+    torch.cuda.empty_cache()
+    sweep = {}
+    for h in (1024, 4096, 8192, 16384):
+        rows = (1 << 29) // h
+        b = RmsBuffers(L, rows, h, torch.bfloat16, device, SEED, x_scale=2.0 ** 0.5)
+        r = time_device_resident([b], 30, 5, 1)
+        nb = rms_bytes(rows, h, 2)
+        sweep[str(h)] = {"rows": rows, "ms_per_step": r["total_ms"] / 30,
+                         "GBps": nb["total"] / (r["total_ms"] / 30 * 1e-3) / 1e9,
+                         "fwd_frac_of_peak": nb["fwd"] / (r["fwd_ms"] * 1e-3) / 1e9 / peak_gbs,
+                         "bwd_frac_of_peak": nb["bwd"] / (r["bwd_ms"] * 1e-3) / 1e9 / peak_gbs}
+        del b
+        torch.cuda.empty_cache()
+    out["rmsnorm_bf16_hidden_sweep_2^29_elements"] = sweep
+    return out
+
+
+def main(argv=None) -> int:
+    ap = argparse.ArgumentParser()
+    ap.add_argument("--gpus", type=int, default=1)
+    ap.add_argument("--steps", type=int, default=200)
+    ap.add_argument("--warmup", type=int, default=10)
+    ap.add_argument("--impl", choices=["b200", "reference"], default="b200")
+    ap.add_argument("--e2e-steps", type=int, default=3)
+    ap.add_argument("--no-side", action="store_true", help="skip the other configurations (N=1 extras)")
+    ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
+    args = ap.parse_args(argv)
+    if args.impl == "reference":
+        return reference_arm(args)
+
+    import torch.distributed as dist
+
+    from mgrrmsnorm_b200 import _capi
+
+    world = int(os.environ.get("WORLD_SIZE", "1"))
+    rank = int(os.environ.get("RANK", "0"))
+    local_rank = int(os.environ.get("LOCAL_RANK", "0"))
+    if args.gpus > 1 and world != args.gpus:
+        print(f"bench.py --gpus {args.gpus} must be launched with one rank per GPU (torchrun --nproc-per-node {args.gpus})",
+              file=sys.stderr)
+        return 2
+    if not torch.cuda.is_available():
+        print("bench.py needs a CUDA device; there is no CPU fallback (use --impl reference for the CPU arm)", file=sys.stderr)
+        return 2
+    torch.cuda.set_device(local_rank)
+    device = torch.device("cuda", local_rank)
+    if world > 1:
+        os.environ.setdefault("MASTER_ADDR", "127.0.0.1")
+        dist.init_process_group("nccl", device_id=device)
+    L = _capi.lib()   # raises when the kernel library is missing
+    sms = ctypes.c_int(0)
+    _capi.check("mgr_device_check", L.mgr_device_check(ctypes.byref(sms)))
+    warmup = max(args.warmup, 3)
+    peaks, peak_kind = measured_peaks()
+    peak_gbs = float(peaks["hbm_gbs"])
+
+    main_buf = RmsBuffers(L, ROWS_PER_GPU, HIDDEN, torch.bfloat16, device, SEED + rank, x_scale=2.0 ** 0.5)
+    sampler = ClockSampler(local_rank) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    r = time_device_resident([main_buf], args.steps, warmup, world)
+    if sampler:
+        sampler.stop()
+    nb = rms_bytes(ROWS_PER_GPU, HIDDEN, 2)
+    ms_per_step = r["total_ms"] / args.steps
+    value = world * nb["total"] / (ms_per_step * 1e-3) / 1e9
+
+    e2e = time_e2e(ROWS_PER_GPU, HIDDEN, device, args.e2e_steps, 1, world, main_buf)
+    e2e_value = world * nb["total"] / (e2e["ms_per_step"] * 1e-3) / 1e9
+
+    side = {}
+    if world == 1 and not args.no_side:
+        del main_buf
+        torch.cuda.empty_cache()
+        side = side_results(L, device, peak_gbs)
+    cpu = None
+    if world == 1 and rank == 0 and not args.no_cpu:
+        cpu = time_cpu(steps=40, warmup=1, budget_s=15.0)
+
+    if rank == 0:
+        bwd_gbs = nb["bwd"] / (r["bwd_ms"] * 1e-3) / 1e9
+        fwd_gbs = nb["fwd"] / (r["fwd_ms"] * 1e-3) / 1e9
+        line = {
+            "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "frac_of_hbm_peak": value / world / peak_gbs,
+            "roofline": {"bound": "hbm", "kernel": "rms_bwd_reg + rms_dw_reduce (one mgr_rmsnorm_bwd call)",
+                         "achieved": bwd_gbs, "peak": peak_gbs, "unit": "GB/s", "frac": bwd_gbs / peak_gbs,
+                         "peak_source": f"of {peak_kind}",
+                         "algorithmic_bytes_per_launch": nb["bwd"], "avg_launch_ms": r["bwd_ms"],
+                         "traffic": (TRAFFIC_PER_ALGO_BYTE * nb["bwd"]) if TRAFFIC_PER_ALGO_BYTE else None},
+            "roofline_fwd": {"bound": "hbm", "kernel": "rms_fwd_reg", "achieved": fwd_gbs, "peak": peak_gbs, "unit": "GB/s",
+                             "frac": fwd_gbs / peak_gbs, "algorithmic_bytes_per_launch": nb["fwd"], "avg_launch_ms": r["fwd_ms"]},
+            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                    "ms_per_step": e2e["ms_per_step"], "steps": e2e["steps"],
+                    "path": "pinned host -> RMSNorm module fwd+bwd -> pinned host (y, dx, dW)"},
+            "gpu_launches": 3 * args.steps,
+            "clocks": sampler.summary(*r["window"]) if sampler else None,
+            "sm_count": sms.value,
+        }
+        if cpu:
+            line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
+        if side:
+            line["also"] = side
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
+if __name__ == "__main__":
+    sys.exit(main())

@@ -1,0 +1,128 @@
+/*
+ * mgr_b200.h -- C ABI of libmgr_b200.so: sm_100a (B200) kernels for the two MegaGemm hot paths,
+ * RMSNorm forward/backward and the SwiGLU MLP.
+ *
+ * This is the boundary a maintainer of the reference binds instead of its own kernel library:
+ * the typed C++ wrappers of src/rmsnorm_kernel.h:9-67 (called from pytorch_binding/binding.cpp:36-59,
+ * 96-126) and the Triton launches of megagemm/swiglu.py:103-107,125-129.
+ *
+ * Conventions shared by every entry point
+ *   - plain pointers and sizes only; every pointer is a DEVICE pointer on the current CUDA device
+ *     unless the comment says "host";
+ *   - `dtype` is one of MGR_F32 / MGR_F16 / MGR_BF16 and applies to every `void*` tensor of the call
+ *     (the reference has the same one-dtype-per-call contract, binding.cpp:34-63);
+ *   - `stream` is a cudaStream_t passed as void* (NULL = the legacy default stream, which is what
+ *     the reference always uses, src/rmsnorm_kernel.cu:542);
+ *   - the library allocates nothing, frees nothing, never synchronises the device, never prints;
+ *     outputs and scratch are caller-owned (the reference's binding allocates outputs through
+ *     torch the same way, binding.cpp:29-30,89-90);
+ *   - return value: MGR_OK (0) or a negative MGR_ERR_* code; mgr_status_str() names it. Argument
+ *     errors are detected on the host before anything is launched (the reference returns `false`
+ *     after an fprintf, src/rmsnorm_kernel.cu:533-549).
+ *   - tensors are row-major and dense: row r of an [rows, cols] tensor starts at element r*cols.
+ */
+#ifndef MGR_B200_H_
+#define MGR_B200_H_
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+#define MGR_ABI_VERSION 1
+
+/* element types (reference: fp32 / fp16 / bf16 kernel families, src/rmsnorm_kernel.h:9-67) */
+#define MGR_F32 0
+#define MGR_F16 1
+#define MGR_BF16 2
+
+/* status codes */
+#define MGR_OK 0
+#define MGR_ERR_BAD_DTYPE (-1)
+#define MGR_ERR_BAD_SHAPE (-2)
+#define MGR_ERR_NULL_PTR (-3)
+#define MGR_ERR_MISALIGNED (-4)
+#define MGR_ERR_WORKSPACE_TOO_SMALL (-5)
+#define MGR_ERR_UNSUPPORTED_ARCH (-6)
+#define MGR_ERR_LAUNCH_FAILED (-7)
+#define MGR_ERR_DEVICE_TIMEOUT (-8)
+#define MGR_ERR_TOO_LARGE (-9)
+#define MGR_ERR_CUDA (-10)
+
+/* Version of this ABI (MGR_ABI_VERSION of the library that was loaded). No reference counterpart. */
+int mgr_abi_version(void);
+
+/* Static, NUL-terminated name of a status code. Replaces the reference's stderr messages
+ * (src/rmsnorm_kernel.cu:534,538,546). Host pointer; never NULL. */
+const char* mgr_status_str(int status);
+
+/* Number of SMs of the current device and whether it can run this library (compute capability 10.x).
+ * Returns MGR_OK or MGR_ERR_UNSUPPORTED_ARCH / MGR_ERR_CUDA; *sm_count (host pointer, may be NULL)
+ * receives the SM count. No reference counterpart (the reference never asks the device). */
+int mgr_device_check(int* sm_count);
+
+/* ------------------------------------------------------------------------------------------------
+ * RMSNorm forward.   y[r,j] = round_dtype((x[r,j] * inv[r]) * w[j]),  inv[r] = 1/sqrt(mean_j x[r,j]^2 + eps)
+ *
+ * Replaces rmsnorm_cuda_fp32 / _fp16 / _bf16 (src/rmsnorm_kernel.cu:529-550, 577-594, 621-638) and
+ * the kernels they launch (src/rmsnorm_kernel.cu:42-230). Arithmetic is fp32 with one rounding to
+ * `dtype` on store, as there (:164, :228).
+ *   y        [rows, cols] out
+ *   inv_rms  [rows] fp32 out, may be NULL (the reference kernel skips the store on NULL, :83)
+ *   x        [rows, cols] in;  w [cols] in
+ * Accepts every shape the reference accepts (cols%4==0 for fp32, cols%2==0 for fp16/bf16) and, as a
+ * superset, any cols >= 1 and any element-aligned pointers (unaligned or odd shapes take a slower
+ * scalar kernel instead of being refused). rows == 0 is a no-op.
+ */
+int mgr_rmsnorm_fwd(void* y, float* inv_rms, const void* x, const void* w,
+                    int64_t rows, int64_t cols, float eps, int dtype, void* stream);
+
+/* Scratch bytes mgr_rmsnorm_bwd needs for this problem on the current device (per-CTA fp32 partial
+ * sums of dW). Returns 0 on invalid arguments. Host-only; no reference counterpart (the reference
+ * accumulates dW with atomics into the output, src/rmsnorm_kernel.cu:315-325). */
+size_t mgr_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t cols, int dtype);
+
+/* RMSNorm backward.
+ *   c[r]    = sum_j dy[r,j]*w[j]*x[r,j]
+ *   dx[r,j] = round_dtype(inv[r] * (dy[r,j]*w[j] - x[r,j] * c[r]*inv[r]^2/cols))
+ *   dw[j]   = round_dtype(sum_r dy[r,j]*x[r,j]*inv[r])          (fp32 sum, ONE rounding)
+ *
+ * Replaces rmsnorm_backward_cuda_fp32 / _fp16 / _bf16 (src/rmsnorm_kernel.cu:552-574, 596-618,
+ * 640-662) and their kernels (:235-522). Differences from the reference, all deliberate:
+ *   - dw is a fixed-order fp32 reduction (per-CTA partials in `workspace`, then a column reduce),
+ *     so it is bit-reproducible run to run; the reference uses atomicAdd (:319-322) and, for
+ *     fp16/bf16, half-precision atomics of rounded partials (:421-422, :517-518);
+ *   - every column of dw is produced for every supported cols (the reference leaves dw[8192:]
+ *     at zero for fp16/bf16, :344,:371-375);
+ *   - dw is fully overwritten; no pre-zeroing is needed (the reference memsets it, :562).
+ *   dx [rows, cols] out;  dw [cols] out in `dtype`, may be NULL
+ *   dw_f32 [cols] fp32 out, may be NULL: the same sum before the rounding (what a multi-GPU caller
+ *          all-reduces before casting). dw and dw_f32 must not both be NULL.
+ *   dy, x [rows, cols] in;  w [cols] in;  inv_rms [rows] fp32 in (as written by mgr_rmsnorm_fwd)
+ *   workspace / workspace_bytes: >= mgr_rmsnorm_bwd_workspace_bytes(rows, cols, dtype), 16-byte aligned.
+ * rows == 0 writes zeros to dw / dw_f32.
+ */
+int mgr_rmsnorm_bwd(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, const void* w,
+                    const float* inv_rms, int64_t rows, int64_t cols, int dtype,
+                    void* workspace, size_t workspace_bytes, void* stream);
+
+/* ------------------------------------------------------------------------------------------------
+ * SwiGLU activation on an already-projected tensor: gv = [gate | val] of shape [m, 2f] (gate =
+ * columns [0,f), val = columns [f,2f): the layout nn.Linear(d, 2*hidden) produces and
+ * benchmark_swiglu.py:85-89 fills).
+ *   forward : h[r,j]   = round_dtype(gate*sigmoid(gate)*val)                         h [m, f]
+ *   backward: dgv[r,j] = round_dtype(dh*val*sig*(1 + gate*(1 - sig)))   (d_gate)     dgv [m, 2f]
+ *             dgv[r,f+j] = round_dtype(dh*gate*sig)                     (d_val)
+ * Replace the Triton kernels _mg_swiglu_fwd_kernel / _mg_swiglu_bwd_kernel and their launches in
+ * MegaGemmFunction (megagemm/swiglu.py:18-43, 46-79, 103-107, 125-129). fp32 math, one rounding.
+ * Any f >= 1; m == 0 is a no-op.
+ */
+int mgr_swiglu_act_fwd(void* h, const void* gv, int64_t m, int64_t f, int dtype, void* stream);
+int mgr_swiglu_act_bwd(void* dgv, const void* dh, const void* gv, int64_t m, int64_t f, int dtype, void* stream);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* MGR_B200_H_ */

@@ -1,0 +1,57 @@
+// Entry points of libmgr_b200.so that are not tied to one kernel family: version, status names,
+// device probe.
+
+#include "mgr_common.cuh"
+
+namespace mgr {
+
+DeviceInfo current_device_info() {
+    static DeviceInfo cache[kMaxDevices];
+    static bool known[kMaxDevices] = {false};
+    DeviceInfo di{MGR_ERR_CUDA, -1, 0};
+    int dev = -1;
+    if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
+        (void)cudaGetLastError();
+        return di;
+    }
+    if (known[dev]) return cache[dev];
+    int major = 0, sms = 0;
+    if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
+        cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return di;
+    }
+    di.device = dev;
+    di.sm_count = sms;
+    di.status = (major == 10) ? MGR_OK : MGR_ERR_UNSUPPORTED_ARCH;
+    cache[dev] = di;
+    known[dev] = true;
+    return di;
+}
+
+}  // namespace mgr
+
+extern "C" int mgr_abi_version(void) { return MGR_ABI_VERSION; }
+
+extern "C" const char* mgr_status_str(int status) {
+    switch (status) {
+        case MGR_OK: return "ok";
+        case MGR_ERR_BAD_DTYPE: return "unsupported dtype (use MGR_F32, MGR_F16 or MGR_BF16)";
+        case MGR_ERR_BAD_SHAPE: return "bad shape (negative rows, non-positive cols or inconsistent dimensions)";
+        case MGR_ERR_NULL_PTR: return "required pointer is NULL";
+        case MGR_ERR_MISALIGNED: return "pointer is not aligned to its element size (workspace: 16 bytes)";
+        case MGR_ERR_WORKSPACE_TOO_SMALL: return "workspace is smaller than the size the *_workspace_bytes query returns";
+        case MGR_ERR_UNSUPPORTED_ARCH: return "current device is not compute capability 10.x (library is sm_100a only)";
+        case MGR_ERR_LAUNCH_FAILED: return "kernel launch failed";
+        case MGR_ERR_DEVICE_TIMEOUT: return "a bounded device-side wait ran out";
+        case MGR_ERR_TOO_LARGE: return "dimension exceeds the supported maximum";
+        case MGR_ERR_CUDA: return "CUDA runtime call failed (no usable device?)";
+        default: return "unknown status";
+    }
+}
+
+extern "C" int mgr_device_check(int* sm_count) {
+    const mgr::DeviceInfo di = mgr::current_device_info();
+    if (sm_count != nullptr) *sm_count = di.sm_count;
+    return di.status;
+}

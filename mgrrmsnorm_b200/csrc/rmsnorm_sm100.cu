@@ -1,0 +1,545 @@
+// RMSNorm forward / backward for sm_100a.
+//
+// Replaces the six SIMT kernels and six host wrappers of the reference's src/rmsnorm_kernel.cu
+// (forward :42-230, backward :235-522, wrappers :529-662). Same arithmetic (fp32 accumulate, one
+// rounding on store), different execution plan:
+//   * a row lives in registers (16-byte packets), so x (and dy) are read from HBM once per direction
+//     -- the reference makes two passes over each row;
+//   * CTAs are persistent (grid = SMs x resident CTAs) and keep the weight row in registers;
+//   * dW is accumulated per thread in fp32 registers over all rows a CTA visits, written once as a
+//     per-CTA partial row, and summed by a second fixed-order kernel -- no atomics, so dW is
+//     bit-reproducible (the reference: atomicAdd at :319-322, half-precision atomics at :421-422).
+// Shapes the packet path cannot take (cols not a multiple of the packet width, pointers not 16-byte
+// aligned, rows longer than 4096 packets) go to scalar kernels with the same arithmetic.
+
+#include "mgr_common.cuh"
+
+namespace mgr {
+namespace {
+
+// ------------------------------------------------------------------------------------------------
+// Packet ("reg") kernels: TPR threads cooperate on one row, each holds VPT 16-byte packets of it.
+// A CTA has max(256, TPR) threads and therefore works on G = BLOCK/TPR rows at a time.
+// ------------------------------------------------------------------------------------------------
+
+template <int TPR>
+struct RegGeom {
+    static constexpr int kBlock = TPR < 256 ? 256 : TPR;
+    static constexpr int kGroups = kBlock / TPR;
+    static constexpr int kWarpsPerRow = TPR / 32;
+    static constexpr int kWarps = kBlock / 32;
+};
+
+// Sum of `v` over the TPR threads that share a row. `red` is a [2][kWarps] shared array used
+// alternately (`buf`), which makes one __syncthreads per reduction sufficient.
+template <int TPR>
+__device__ __forceinline__ float row_sum(float v, float (*red)[RegGeom<TPR>::kWarps], int& buf, int group) {
+    v = warp_sum(v);
+    if constexpr (RegGeom<TPR>::kWarpsPerRow > 1) {
+        constexpr int WPR = RegGeom<TPR>::kWarpsPerRow;
+        const int warp = threadIdx.x >> 5;
+        if ((threadIdx.x & 31) == 0) red[buf][warp] = v;
+        __syncthreads();
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < WPR; ++i) s += red[buf][group * WPR + i];
+        buf ^= 1;
+        v = s;
+    }
+    return v;
+}
+
+template <typename T, int TPR, int VPT>
+__global__ void __launch_bounds__(RegGeom<TPR>::kBlock)
+rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* __restrict__ x,
+            const T* __restrict__ w, int64_t rows, int cols, float eps) {
+    using Geo = RegGeom<TPR>;
+    constexpr int VEC = Elem<T>::kVec;
+    __shared__ float red[2][Geo::kWarps];
+    int buf = 0;
+
+    const int group = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int nvec = cols / VEC;
+
+    uint4 wv[VPT];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int v = t + k * TPR;
+        wv[k] = v < nvec ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
+    }
+
+    const float inv_cols = 1.0f / static_cast<float>(cols);
+    const int64_t ngroups = (rows + Geo::kGroups - 1) / Geo::kGroups;
+    for (int64_t rg = blockIdx.x; rg < ngroups; rg += gridDim.x) {
+        const int64_t r = rg * Geo::kGroups + group;
+        const bool live = r < rows;
+        const uint4* xr = reinterpret_cast<const uint4*>(x + (live ? r : 0) * static_cast<int64_t>(cols));
+        uint4 xv[VPT];
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int v = t + k * TPR;
+            xv[k] = (live && v < nvec) ? ld_stream16(xr + v) : make_uint4(0, 0, 0, 0);
+        }
+        float ss = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            float f[VEC];
+            unpack16<T>(xv[k], f);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) ss += f[i] * f[i];
+        }
+        ss = row_sum<TPR>(ss, red, buf, group);
+        const float inv = 1.0f / sqrtf(ss * inv_cols + eps);
+        if (live) {
+            if (t == 0 && inv_rms != nullptr) inv_rms[r] = inv;
+            uint4* yr = reinterpret_cast<uint4*>(y + r * static_cast<int64_t>(cols));
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int v = t + k * TPR;
+                if (v < nvec) {
+                    float f[VEC], g[VEC], o[VEC];
+                    unpack16<T>(xv[k], f);
+                    unpack16<T>(wv[k], g);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) o[i] = (f[i] * inv) * g[i];
+                    st_stream16(yr + v, pack16<T>(o));
+                }
+            }
+        }
+    }
+}
+
+// Backward. Each thread owns the same VPT*VEC columns for every row its CTA visits, so the dW
+// partial sums stay in registers until the CTA is done; the G row groups of a CTA are then folded in
+// shared memory (fixed order) and the CTA writes ONE fp32 partial row ws[blockIdx.x, :].
+template <typename T, int TPR, int VPT>
+__global__ void __launch_bounds__(RegGeom<TPR>::kBlock)
+rms_bwd_reg(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
+            const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int cols) {
+    using Geo = RegGeom<TPR>;
+    constexpr int VEC = Elem<T>::kVec;
+    constexpr int G = Geo::kGroups;
+    __shared__ float red[2][Geo::kWarps];
+    __shared__ __align__(16) float fold[G > 1 ? (G - 1) * TPR * VPT * VEC : 4];
+    int buf = 0;
+
+    const int group = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int nvec = cols / VEC;
+
+    uint4 wv[VPT];
+    float acc[VPT][VEC];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int v = t + k * TPR;
+        wv[k] = v < nvec ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[k][i] = 0.f;
+    }
+
+    const float inv_cols = 1.0f / static_cast<float>(cols);
+    const int64_t ngroups = (rows + G - 1) / G;
+    for (int64_t rg = blockIdx.x; rg < ngroups; rg += gridDim.x) {
+        const int64_t r = rg * G + group;
+        const bool live = r < rows;
+        const int64_t off = (live ? r : 0) * static_cast<int64_t>(cols);
+        const uint4* xr = reinterpret_cast<const uint4*>(x + off);
+        const uint4* gr = reinterpret_cast<const uint4*>(dy + off);
+        uint4 xv[VPT], gv[VPT];
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int v = t + k * TPR;
+            const bool on = live && v < nvec;
+            xv[k] = on ? ld_stream16(xr + v) : make_uint4(0, 0, 0, 0);
+            gv[k] = on ? ld_stream16(gr + v) : make_uint4(0, 0, 0, 0);
+        }
+        const float rinv = live ? __ldg(inv_rms + r) : 0.f;
+
+        float c = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            float fx[VEC], fg[VEC], fw[VEC];
+            unpack16<T>(xv[k], fx);
+            unpack16<T>(gv[k], fg);
+            unpack16<T>(wv[k], fw);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                c += (fg[i] * fw[i]) * fx[i];
+                acc[k][i] += (fg[i] * fx[i]) * rinv;
+            }
+        }
+        c = row_sum<TPR>(c, red, buf, group);
+        const float term2 = c * (rinv * rinv) * inv_cols;
+
+        if (live) {
+            uint4* dr = reinterpret_cast<uint4*>(dx + off);
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int v = t + k * TPR;
+                if (v < nvec) {
+                    float fx[VEC], fg[VEC], fw[VEC], o[VEC];
+                    unpack16<T>(xv[k], fx);
+                    unpack16<T>(gv[k], fg);
+                    unpack16<T>(wv[k], fw);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) o[i] = rinv * (fg[i] * fw[i] - fx[i] * term2);
+                    st_stream16(dr + v, pack16<T>(o));
+                }
+            }
+        }
+    }
+
+    // Fold the G groups of this CTA (group 0 adds groups 1..G-1 in order), then one partial row out.
+    if constexpr (G > 1) {
+        constexpr int kRow = TPR * VPT * VEC;
+        if (group > 0) {
+#pragma unroll
+            for (int k = 0; k < VPT; ++k)
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) fold[(group - 1) * kRow + (k * VEC + i) * TPR + t] = acc[k][i];
+        }
+        __syncthreads();
+        if (group == 0) {
+            for (int gidx = 0; gidx < G - 1; ++gidx)
+#pragma unroll
+                for (int k = 0; k < VPT; ++k)
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) acc[k][i] += fold[gidx * kRow + (k * VEC + i) * TPR + t];
+        }
+    }
+    if (group == 0) {
+        float* out = ws + static_cast<int64_t>(blockIdx.x) * cols;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int v = t + k * TPR;
+            if (v < nvec) {
+#pragma unroll
+                for (int i = 0; i < VEC; i += 4)
+                    *reinterpret_cast<float4*>(out + static_cast<int64_t>(v) * VEC + i) =
+                        make_float4(acc[k][i], acc[k][i + 1], acc[k][i + 2], acc[k][i + 3]);
+            }
+        }
+    }
+}
+
+// dw[j] = sum_{p<P} ws[p, j], summed in a fixed order: each of the 32 slices adds its rows
+// p = slice, slice+32, ... in increasing p, then the 32 slice sums are added in increasing slice.
+// One rounding to T at the end; the unrounded fp32 sum goes to dw_f32 when asked for.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+rms_dw_reduce(T* __restrict__ dw, float* __restrict__ dw_f32, const float* __restrict__ ws, int P, int cols) {
+    __shared__ float part[32][33];
+    const int col = blockIdx.x * 32 + threadIdx.x;
+    float a = 0.f;
+    if (col < cols) {
+        int p = threadIdx.y;
+        for (; p + 96 < P; p += 128) {
+            const float v0 = ws[static_cast<int64_t>(p) * cols + col];
+            const float v1 = ws[static_cast<int64_t>(p + 32) * cols + col];
+            const float v2 = ws[static_cast<int64_t>(p + 64) * cols + col];
+            const float v3 = ws[static_cast<int64_t>(p + 96) * cols + col];
+            a += v0;
+            a += v1;
+            a += v2;
+            a += v3;
+        }
+        for (; p < P; p += 32) a += ws[static_cast<int64_t>(p) * cols + col];
+    }
+    part[threadIdx.y][threadIdx.x] = a;
+    __syncthreads();
+    if (threadIdx.y == 0 && col < cols) {
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < 32; ++i) s += part[i][threadIdx.x];
+        if (dw != nullptr) dw[col] = from_f32<T>(s);
+        if (dw_f32 != nullptr) dw_f32[col] = s;
+    }
+}
+
+// ------------------------------------------------------------------------------------------------
+// Scalar kernels: any cols >= 1, any element-aligned pointers. One CTA per row, two passes.
+// ------------------------------------------------------------------------------------------------
+
+__device__ __forceinline__ float block_sum_256(float v, float* red /* [8] */) {
+    v = warp_sum(v);
+    __syncthreads();  // protects `red` from the previous use
+    if ((threadIdx.x & 31) == 0) red[threadIdx.x >> 5] = v;
+    __syncthreads();
+    float s = 0.f;
+#pragma unroll
+    for (int i = 0; i < 8; ++i) s += red[i];
+    return s;
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_fwd_scalar(T* __restrict__ y, float* __restrict__ inv_rms, const T* __restrict__ x,
+               const T* __restrict__ w, int64_t rows, int64_t cols, float eps) {
+    __shared__ float red[8];
+    const float inv_cols = 1.0f / static_cast<float>(cols);
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const T* xr = x + r * cols;
+        T* yr = y + r * cols;
+        float ss = 0.f;
+        for (int64_t j = threadIdx.x; j < cols; j += 256) {
+            const float f = to_f32(xr[j]);
+            ss += f * f;
+        }
+        ss = block_sum_256(ss, red);
+        const float inv = 1.0f / sqrtf(ss * inv_cols + eps);
+        if (threadIdx.x == 0 && inv_rms != nullptr) inv_rms[r] = inv;
+        for (int64_t j = threadIdx.x; j < cols; j += 256)
+            yr[j] = from_f32<T>((to_f32(xr[j]) * inv) * to_f32(w[j]));
+    }
+}
+
+template <typename T>
+__global__ void __launch_bounds__(256)
+rms_bwd_dx_scalar(T* __restrict__ dx, const T* __restrict__ dy, const T* __restrict__ x,
+                  const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int64_t cols) {
+    __shared__ float red[8];
+    const float inv_cols = 1.0f / static_cast<float>(cols);
+    for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
+        const T* xr = x + r * cols;
+        const T* gr = dy + r * cols;
+        T* dr = dx + r * cols;
+        const float rinv = inv_rms[r];
+        float c = 0.f;
+        for (int64_t j = threadIdx.x; j < cols; j += 256) c += (to_f32(gr[j]) * to_f32(w[j])) * to_f32(xr[j]);
+        c = block_sum_256(c, red);
+        const float term2 = c * (rinv * rinv) * inv_cols;
+        for (int64_t j = threadIdx.x; j < cols; j += 256)
+            dr[j] = from_f32<T>(rinv * (to_f32(gr[j]) * to_f32(w[j]) - to_f32(xr[j]) * term2));
+    }
+}
+
+// Partial column sums: slice s = blockIdx.y adds rows s, s+S, s+2S, ... (increasing) of column j.
+template <typename T>
+__global__ void __launch_bounds__(128)
+rms_bwd_dw_scalar(float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
+                  const float* __restrict__ inv_rms, int64_t rows, int64_t cols) {
+    const int64_t j = static_cast<int64_t>(blockIdx.x) * 128 + threadIdx.x;
+    if (j >= cols) return;
+    float a = 0.f;
+    for (int64_t r = blockIdx.y; r < rows; r += gridDim.y)
+        a += (to_f32(dy[r * cols + j]) * to_f32(x[r * cols + j])) * inv_rms[r];
+    ws[static_cast<int64_t>(blockIdx.y) * cols + j] = a;
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host: plan selection and launches
+// ------------------------------------------------------------------------------------------------
+
+struct RegShape {
+    int tpr, vpt;
+};
+constexpr RegShape kRegShapes[] = {{32, 1}, {32, 2}, {32, 4}, {128, 2}, {128, 4}, {256, 4}, {512, 4}, {1024, 4}};
+constexpr int kNumRegShapes = sizeof(kRegShapes) / sizeof(kRegShapes[0]);
+constexpr int kScalarDwSlices = 64;
+
+// Index of the smallest packet shape that holds a row of `nvec` packets, or -1.
+int reg_shape_for(int64_t nvec) {
+    for (int i = 0; i < kNumRegShapes; ++i)
+        if (nvec <= static_cast<int64_t>(kRegShapes[i].tpr) * kRegShapes[i].vpt) return i;
+    return -1;
+}
+
+template <typename K>
+int resident_ctas(K kernel, int block, int* cache /* [kMaxDevices] */, int device) {
+    int v = cache[device];
+    if (v > 0) return v;
+    int n = 0;
+    if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, block, 0) != cudaSuccess || n < 1) {
+        (void)cudaGetLastError();
+        n = 1;
+    }
+    cache[device] = n;
+    return n;
+}
+
+template <typename T, int I>
+struct RegKernels {
+    static constexpr int TPR = kRegShapes[I].tpr;
+    static constexpr int VPT = kRegShapes[I].vpt;
+    static constexpr int BLOCK = RegGeom<TPR>::kBlock;
+    static constexpr int G = RegGeom<TPR>::kGroups;
+
+    static int64_t fwd_grid(int64_t rows, const DeviceInfo& di) {
+        static int occ[kMaxDevices] = {0};
+        const int64_t ngroups = (rows + G - 1) / G;
+        const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_fwd_reg<T, TPR, VPT>, BLOCK, occ, di.device);
+        return ngroups < cap ? ngroups : cap;
+    }
+    static int64_t bwd_grid(int64_t rows, const DeviceInfo& di) {
+        static int occ[kMaxDevices] = {0};
+        const int64_t ngroups = (rows + G - 1) / G;
+        const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_bwd_reg<T, TPR, VPT>, BLOCK, occ, di.device);
+        return ngroups < cap ? ngroups : cap;
+    }
+    static void fwd(T* y, float* inv, const T* x, const T* w, int64_t rows, int cols, float eps,
+                    const DeviceInfo& di, cudaStream_t s) {
+        rms_fwd_reg<T, TPR, VPT><<<static_cast<unsigned>(fwd_grid(rows, di)), BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps);
+    }
+    static void bwd(T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv, int64_t rows,
+                    int cols, int64_t grid, cudaStream_t s) {
+        rms_bwd_reg<T, TPR, VPT><<<static_cast<unsigned>(grid), BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols);
+    }
+};
+
+template <typename T, int I = 0>
+struct RegDispatch {
+    static void fwd(int shape, T* y, float* inv, const T* x, const T* w, int64_t rows, int cols, float eps,
+                    const DeviceInfo& di, cudaStream_t s) {
+        if (shape == I) RegKernels<T, I>::fwd(y, inv, x, w, rows, cols, eps, di, s);
+        else if constexpr (I + 1 < kNumRegShapes) RegDispatch<T, I + 1>::fwd(shape, y, inv, x, w, rows, cols, eps, di, s);
+    }
+    static int64_t bwd_grid(int shape, int64_t rows, const DeviceInfo& di) {
+        if (shape == I) return RegKernels<T, I>::bwd_grid(rows, di);
+        if constexpr (I + 1 < kNumRegShapes) return RegDispatch<T, I + 1>::bwd_grid(shape, rows, di);
+        return 0;
+    }
+    static void bwd(int shape, T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv,
+                    int64_t rows, int cols, int64_t grid, cudaStream_t s) {
+        if (shape == I) RegKernels<T, I>::bwd(dx, ws, dy, x, w, inv, rows, cols, grid, s);
+        else if constexpr (I + 1 < kNumRegShapes) RegDispatch<T, I + 1>::bwd(shape, dx, ws, dy, x, w, inv, rows, cols, grid, s);
+    }
+};
+
+int64_t scalar_grid(int64_t rows, const DeviceInfo& di) {
+    const int64_t cap = static_cast<int64_t>(di.sm_count) * 8;
+    return rows < cap ? rows : cap;
+}
+
+template <typename T>
+int fwd_typed(void* y, float* inv, const void* x, const void* w, int64_t rows, int64_t cols, float eps,
+              const DeviceInfo& di, cudaStream_t s) {
+    constexpr int VEC = Elem<T>::kVec;
+    const bool packets = cols % VEC == 0 && aligned_to(y, 16) && aligned_to(x, 16) && aligned_to(w, 16);
+    const int shape = packets ? reg_shape_for(cols / VEC) : -1;
+    if (shape >= 0) {
+        RegDispatch<T>::fwd(shape, static_cast<T*>(y), inv, static_cast<const T*>(x), static_cast<const T*>(w), rows,
+                            static_cast<int>(cols), eps, di, s);
+    } else {
+        rms_fwd_scalar<T><<<static_cast<unsigned>(scalar_grid(rows, di)), 256, 0, s>>>(
+            static_cast<T*>(y), inv, static_cast<const T*>(x), static_cast<const T*>(w), rows, cols, eps);
+    }
+    return launch_status();
+}
+
+// Partial rows the backward of this problem writes: the larger of the packet path's grid and the
+// scalar path's slice count, so one workspace size serves whichever path the pointers select.
+template <typename T>
+int64_t bwd_partials(int64_t rows, int64_t cols, const DeviceInfo& di) {
+    constexpr int VEC = Elem<T>::kVec;
+    int64_t p = rows < kScalarDwSlices ? rows : kScalarDwSlices;
+    if (cols % VEC == 0) {
+        const int shape = reg_shape_for(cols / VEC);
+        if (shape >= 0) {
+            const int64_t g = RegDispatch<T>::bwd_grid(shape, rows, di);
+            if (g > p) p = g;
+        }
+    }
+    return p < 1 ? 1 : p;
+}
+
+template <typename T>
+int bwd_typed(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, const void* w, const float* inv,
+              int64_t rows, int64_t cols, float* ws, const DeviceInfo& di, cudaStream_t s) {
+    constexpr int VEC = Elem<T>::kVec;
+    const bool packets = cols % VEC == 0 && aligned_to(dx, 16) && aligned_to(dy, 16) && aligned_to(x, 16) &&
+                         aligned_to(w, 16);
+    const int shape = packets ? reg_shape_for(cols / VEC) : -1;
+    int64_t P;
+    if (shape >= 0) {
+        P = RegDispatch<T>::bwd_grid(shape, rows, di);
+        RegDispatch<T>::bwd(shape, static_cast<T*>(dx), ws, static_cast<const T*>(dy), static_cast<const T*>(x),
+                            static_cast<const T*>(w), inv, rows, static_cast<int>(cols), P, s);
+    } else {
+        P = rows < kScalarDwSlices ? rows : kScalarDwSlices;
+        rms_bwd_dx_scalar<T><<<static_cast<unsigned>(scalar_grid(rows, di)), 256, 0, s>>>(
+            static_cast<T*>(dx), static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(w), inv, rows, cols);
+        int st = launch_status();
+        if (st != MGR_OK) return st;
+        dim3 grid(static_cast<unsigned>((cols + 127) / 128), static_cast<unsigned>(P));
+        rms_bwd_dw_scalar<T><<<grid, 128, 0, s>>>(ws, static_cast<const T*>(dy), static_cast<const T*>(x), inv, rows, cols);
+    }
+    int st = launch_status();
+    if (st != MGR_OK) return st;
+    rms_dw_reduce<T><<<static_cast<unsigned>((cols + 31) / 32), dim3(32, 32), 0, s>>>(
+        static_cast<T*>(dw), dw_f32, ws, static_cast<int>(P), static_cast<int>(cols));
+    return launch_status();
+}
+
+int check_common(int64_t rows, int64_t cols, int dtype) {
+    if (dtype_size(dtype) == 0) return MGR_ERR_BAD_DTYPE;
+    if (rows < 0 || cols < 1) return MGR_ERR_BAD_SHAPE;
+    if (cols > (1ll << 30) || rows > (1ll << 40)) return MGR_ERR_TOO_LARGE;
+    return MGR_OK;
+}
+
+}  // namespace
+}  // namespace mgr
+
+using namespace mgr;
+
+extern "C" int mgr_rmsnorm_fwd(void* y, float* inv_rms, const void* x, const void* w, int64_t rows, int64_t cols,
+                               float eps, int dtype, void* stream) {
+    int st = check_common(rows, cols, dtype);
+    if (st != MGR_OK) return st;
+    if (rows == 0) return MGR_OK;
+    if (y == nullptr || x == nullptr || w == nullptr) return MGR_ERR_NULL_PTR;
+    const size_t es = dtype_size(dtype);
+    if (!aligned_to(y, es) || !aligned_to(x, es) || !aligned_to(w, es) || !aligned_to(inv_rms, 4)) return MGR_ERR_MISALIGNED;
+    const DeviceInfo di = current_device_info();
+    if (di.status != MGR_OK) return di.status;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    switch (dtype) {
+        case MGR_F32: return fwd_typed<float>(y, inv_rms, x, w, rows, cols, eps, di, s);
+        case MGR_F16: return fwd_typed<__half>(y, inv_rms, x, w, rows, cols, eps, di, s);
+        default: return fwd_typed<__nv_bfloat16>(y, inv_rms, x, w, rows, cols, eps, di, s);
+    }
+}
+
+extern "C" size_t mgr_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t cols, int dtype) {
+    if (check_common(rows, cols, dtype) != MGR_OK) return 0;
+    const DeviceInfo di = current_device_info();
+    if (di.status != MGR_OK) return 0;
+    int64_t p;
+    switch (dtype) {
+        case MGR_F32: p = bwd_partials<float>(rows, cols, di); break;
+        case MGR_F16: p = bwd_partials<__half>(rows, cols, di); break;
+        default: p = bwd_partials<__nv_bfloat16>(rows, cols, di); break;
+    }
+    return static_cast<size_t>(p) * static_cast<size_t>(cols) * sizeof(float);
+}
+
+extern "C" int mgr_rmsnorm_bwd(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, const void* w,
+                               const float* inv_rms, int64_t rows, int64_t cols, int dtype, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+    int st = check_common(rows, cols, dtype);
+    if (st != MGR_OK) return st;
+    if (dw == nullptr && dw_f32 == nullptr) return MGR_ERR_NULL_PTR;
+    const size_t es = dtype_size(dtype);
+    if (!aligned_to(dw, es) || !aligned_to(dw_f32, 4)) return MGR_ERR_MISALIGNED;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (rows == 0) {
+        if (dw != nullptr && cudaMemsetAsync(dw, 0, static_cast<size_t>(cols) * es, s) != cudaSuccess) return MGR_ERR_CUDA;
+        if (dw_f32 != nullptr && cudaMemsetAsync(dw_f32, 0, static_cast<size_t>(cols) * 4, s) != cudaSuccess) return MGR_ERR_CUDA;
+        return MGR_OK;
+    }
+    if (dx == nullptr || dy == nullptr || x == nullptr || w == nullptr || inv_rms == nullptr || workspace == nullptr)
+        return MGR_ERR_NULL_PTR;
+    if (!aligned_to(dx, es) || !aligned_to(dy, es) || !aligned_to(x, es) || !aligned_to(w, es) ||
+        !aligned_to(inv_rms, 4) || !aligned_to(workspace, 16))
+        return MGR_ERR_MISALIGNED;
+    const DeviceInfo di = current_device_info();
+    if (di.status != MGR_OK) return di.status;
+    if (workspace_bytes < mgr_rmsnorm_bwd_workspace_bytes(rows, cols, dtype)) return MGR_ERR_WORKSPACE_TOO_SMALL;
+    float* ws = static_cast<float*>(workspace);
+    switch (dtype) {
+        case MGR_F32: return bwd_typed<float>(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, ws, di, s);
+        case MGR_F16: return bwd_typed<__half>(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, ws, di, s);
+        default: return bwd_typed<__nv_bfloat16>(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, ws, di, s);
+    }
+}

@@ -1,0 +1,147 @@
+"""`rmsnorm_cuda_ops`: the extension module the reference's Python layer imports, on the new C ABI.
+
+Same Python-visible surface as pytorch_binding/binding.cpp:136-139:
+    rmsnorm_forward(input[R,H], weight[H], epsilon) -> [output[R,H], inv_rms[R] fp32]
+    rmsnorm_backward(grad_output[R,H], input[R,H], weight[H], inv_rms[R]) -> [grad_input, grad_weight]
+and the same duties as that binding: check the tensors (binding.cpp:9-11,17-24,79-82), allocate the
+outputs through torch (:29-30, :89-90), dispatch on the input dtype (:34-63, :94-129), raise
+RuntimeError on failure (:65, :131). Added, because the reference lacks them: a device guard and a
+launch on torch's current stream (the reference launches on the legacy default stream of whichever
+device is current, src/rmsnorm_kernel.cu:542,564).
+
+torch is used for device memory and streams only; all arithmetic is in libmgr_b200.so.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _capi
+
+_DTYPES = {torch.float32: _capi.MGR_F32, torch.float16: _capi.MGR_F16, torch.bfloat16: _capi.MGR_BF16}
+
+
+def _check_input(t: torch.Tensor, name: str) -> None:
+    if not isinstance(t, torch.Tensor):
+        raise TypeError(f"{name} must be a torch.Tensor")
+    if not t.is_cuda:
+        raise RuntimeError(f"{name} must be a CUDA tensor")
+    if not t.is_contiguous():
+        raise RuntimeError(f"{name} must be contiguous")
+
+
+def _dtype_code(t: torch.Tensor, what: str) -> int:
+    try:
+        return _DTYPES[t.dtype]
+    except KeyError:
+        raise RuntimeError(f"Unsupported dtype{what}. Use float32, float16, or bfloat16.") from None
+
+
+def _stream_ptr(device: torch.device) -> int:
+    return torch.cuda.current_stream(device).cuda_stream
+
+
+def rmsnorm_forward(input: torch.Tensor, weight: torch.Tensor, epsilon: float):
+    """[output, inv_rms] = RMSNorm forward of a 2-D tensor (binding.cpp:16-68)."""
+    _check_input(input, "input")
+    _check_input(weight, "weight")
+    if input.dim() != 2:
+        raise RuntimeError("Input must be 2D")
+    rows, cols = input.shape
+    if weight.dim() != 1 or weight.shape[0] != cols:
+        raise RuntimeError("Weight size must match hidden size")
+    code = _dtype_code(input, "")
+    if weight.dtype != input.dtype:
+        # binding.cpp:48,57: weight.data_ptr<T>() throws when the dtypes differ
+        raise RuntimeError(f"weight dtype {weight.dtype} must match input dtype {input.dtype}")
+    if weight.device != input.device:
+        raise RuntimeError("input and weight must be on the same device")
+    L = _capi.lib()
+    with torch.cuda.device(input.device):
+        inv_rms = torch.empty((rows,), dtype=torch.float32, device=input.device)
+        output = torch.empty_like(input)
+        st = L.mgr_rmsnorm_fwd(output.data_ptr(), inv_rms.data_ptr(), input.data_ptr(), weight.data_ptr(),
+                               rows, cols, float(epsilon), code, _stream_ptr(input.device))
+    _capi.check("RMSNorm Forward CUDA kernel", st)
+    return [output, inv_rms]
+
+
+def rmsnorm_backward_full(grad_output: torch.Tensor, input: torch.Tensor, weight: torch.Tensor,
+                          inv_rms: torch.Tensor, want_dw_f32: bool = False):
+    """[grad_input, grad_weight, grad_weight_fp32 | None]; the fp32 sum is what a row-sharded caller
+    all-reduces before rounding."""
+    for t, n in ((grad_output, "grad_output"), (input, "input"), (weight, "weight"), (inv_rms, "inv_rms")):
+        _check_input(t, n)
+    if input.dim() != 2:
+        raise RuntimeError("Input must be 2D")
+    rows, cols = input.shape
+    if grad_output.shape != input.shape:
+        raise RuntimeError("grad_output shape must match input shape")
+    if weight.dim() != 1 or weight.shape[0] != cols:
+        raise RuntimeError("Weight size must match hidden size")
+    if inv_rms.dtype != torch.float32 or inv_rms.numel() != rows:
+        raise RuntimeError("inv_rms must be a float32 tensor with one value per row")
+    code = _dtype_code(input, " for backward")
+    if grad_output.dtype != input.dtype or weight.dtype != input.dtype:
+        raise RuntimeError("grad_output, input and weight must share one dtype")
+    if not (grad_output.device == input.device == weight.device == inv_rms.device):
+        raise RuntimeError("all tensors must be on the same device")
+    L = _capi.lib()
+    with torch.cuda.device(input.device):
+        grad_input = torch.empty_like(input)
+        grad_weight = torch.empty_like(weight)
+        dw_f32 = torch.empty((cols,), dtype=torch.float32, device=input.device) if want_dw_f32 else None
+        ws_bytes = int(L.mgr_rmsnorm_bwd_workspace_bytes(rows, cols, code))
+        ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=input.device)
+        st = L.mgr_rmsnorm_bwd(grad_input.data_ptr(), grad_weight.data_ptr(),
+                               dw_f32.data_ptr() if dw_f32 is not None else None,
+                               grad_output.data_ptr(), input.data_ptr(), weight.data_ptr(), inv_rms.data_ptr(),
+                               rows, cols, code, ws.data_ptr(), ws.numel(), _stream_ptr(input.device))
+    _capi.check("RMSNorm Backward CUDA kernel", st)
+    return [grad_input, grad_weight, dw_f32]
+
+
+def rmsnorm_backward(grad_output: torch.Tensor, input: torch.Tensor, weight: torch.Tensor, inv_rms: torch.Tensor):
+    """[grad_input, grad_weight] (binding.cpp:73-134). grad_weight has the weight's dtype, as there."""
+    return rmsnorm_backward_full(grad_output, input, weight, inv_rms)[:2]
+
+
+# ---------------------------------------------------------------------------------------------------
+# SwiGLU entry points. The reference has no native code here (its activation is a Triton kernel inside
+# megagemm/swiglu.py); these are what that file calls instead.
+# ---------------------------------------------------------------------------------------------------
+
+def swiglu_act_forward(w12_out: torch.Tensor, hidden_dim: int) -> torch.Tensor:
+    """h[M, hidden] = silu(w12_out[:, :hidden]) * w12_out[:, hidden:] for a contiguous [M, 2*hidden]
+    tensor (the launch in megagemm/swiglu.py:96-107)."""
+    _check_input(w12_out, "w12_out")
+    if w12_out.dim() != 2 or w12_out.shape[1] != 2 * hidden_dim:
+        raise RuntimeError("w12_out must be [M, 2*hidden_dim]")
+    code = _dtype_code(w12_out, "")
+    m = w12_out.shape[0]
+    L = _capi.lib()
+    with torch.cuda.device(w12_out.device):
+        out = torch.empty((m, hidden_dim), device=w12_out.device, dtype=w12_out.dtype)
+        st = L.mgr_swiglu_act_fwd(out.data_ptr(), w12_out.data_ptr(), m, hidden_dim, code, _stream_ptr(w12_out.device))
+    _capi.check("SwiGLU activation forward kernel", st)
+    return out
+
+
+def swiglu_act_backward(grad_out: torch.Tensor, w12_out: torch.Tensor, hidden_dim: int) -> torch.Tensor:
+    """[d_gate | d_val] of shape [M, 2*hidden] (the launch in megagemm/swiglu.py:116-129)."""
+    _check_input(grad_out, "grad_out")
+    _check_input(w12_out, "w12_out")
+    if w12_out.dim() != 2 or w12_out.shape[1] != 2 * hidden_dim:
+        raise RuntimeError("w12_out must be [M, 2*hidden_dim]")
+    m = w12_out.shape[0]
+    if tuple(grad_out.shape) != (m, hidden_dim):
+        raise RuntimeError("grad_out must be [M, hidden_dim]")
+    if grad_out.dtype != w12_out.dtype or grad_out.device != w12_out.device:
+        raise RuntimeError("grad_out and w12_out must share dtype and device")
+    code = _dtype_code(w12_out, " for backward")
+    L = _capi.lib()
+    with torch.cuda.device(w12_out.device):
+        grad_in = torch.empty_like(w12_out)
+        st = L.mgr_swiglu_act_bwd(grad_in.data_ptr(), grad_out.data_ptr(), w12_out.data_ptr(), m, hidden_dim, code,
+                                  _stream_ptr(w12_out.device))
+    _capi.check("SwiGLU activation backward kernel", st)
+    return grad_in

@@ -1,0 +1,62 @@
+"""SwiGLU MLP module and activation Function: the host-side mirror of megagemm/swiglu.py.
+
+Same class names, constructor arguments, attributes (`w12`, `w3`, `hidden`) and parameter layout as
+the reference (megagemm/swiglu.py:86-172): `w12.weight` is [2*hidden, d_model] with the gate rows
+first and the value rows second (benchmark_swiglu.py:85-89), `w3.weight` is [d_model, hidden], no
+biases -- so the reference's state dicts load unchanged. The Triton kernels are gone: the
+activation runs in libmgr_b200.so.
+"""
+from __future__ import annotations
+
+import torch
+import torch.nn as nn
+from torch.autograd import Function
+
+from . import rmsnorm_cuda_ops
+
+
+class MegaGemmFunction(Function):
+    """silu(gate) * value on a projected tensor [..., 2*hidden] (megagemm/swiglu.py:86-131)."""
+
+    @staticmethod
+    def forward(ctx, w12_out: torch.Tensor, hidden_dim: int):
+        w12_out = w12_out.contiguous()
+        x_flat = w12_out.view(-1, 2 * hidden_dim)
+        out_flat = rmsnorm_cuda_ops.swiglu_act_forward(x_flat, hidden_dim)
+        ctx.save_for_backward(w12_out)
+        ctx.hidden_dim = hidden_dim
+        return out_flat.view(w12_out.shape[:-1] + (hidden_dim,))
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor):
+        (w12_out,) = ctx.saved_tensors
+        hidden_dim = ctx.hidden_dim
+        grad_out_flat = grad_output.contiguous().view(-1, hidden_dim)
+        x_flat = w12_out.contiguous().view(-1, 2 * hidden_dim)
+        grad_input_flat = rmsnorm_cuda_ops.swiglu_act_backward(grad_out_flat, x_flat, hidden_dim)
+        return grad_input_flat.view(w12_out.shape), None
+
+
+class MegaGemmTriton(nn.Module):
+    """SwiGLU MLP: y = w3( silu(x w1^T) * (x w2^T) ), w1|w2 stacked in `w12`.
+
+    Args (as megagemm/swiglu.py:156): d_model, multiple_of=256, hidden_multiple=5/3. `hidden` is
+    int(d_model*hidden_multiple) rounded up to a multiple of `multiple_of` (:158-160). The class keeps
+    the reference's name although nothing here uses Triton.
+    """
+
+    def __init__(self, d_model: int, multiple_of: int = 256, hidden_multiple: float = 5 / 3):
+        super().__init__()
+        hidden = int(d_model * hidden_multiple)
+        hidden = multiple_of * ((hidden + multiple_of - 1) // multiple_of)
+        self.hidden = hidden
+        self.w12 = nn.Linear(d_model, 2 * hidden, bias=False)
+        self.w3 = nn.Linear(hidden, d_model, bias=False)
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w12_out = self.w12(x)
+        hidden = MegaGemmFunction.apply(w12_out, self.hidden)
+        return self.w3(hidden)
+
+    def extra_repr(self) -> str:
+        return f"d_model={self.w12.in_features}, hidden={self.hidden} (sm_100a)"

@@ -1,0 +1,89 @@
+"""Pins the CPU oracle against vectors produced by the reference's own code (tests/golden/*.npz,
+written by tests/golden/make_golden.py). CPU only."""
+import numpy as np
+import pytest
+
+from oracle import oracle
+
+
+@pytest.fixture(scope="module")
+def rms(golden_dir):
+    return np.load(golden_dir / "rmsnorm.npz")
+
+
+@pytest.fixture(scope="module")
+def swi(golden_dir):
+    return np.load(golden_dir / "swiglu.npz")
+
+
+@pytest.mark.parametrize("case", ["f32_a", "f32_b", "f16", "bf16"])
+def test_forward_restatement_is_bit_exact_with_reference_cpu(rms, case):
+    """mgr_oracle_rmsnorm_fwd_f32seq vs the reference's rmsnorm_cpu output (rmsnorm_standalone.cu:17-30)."""
+    y = oracle.rmsnorm_fwd_f32seq(rms[f"{case}_x"], rms[f"{case}_w"], float(rms[f"{case}_eps"]))
+    assert np.array_equal(y, rms[f"{case}_y_refcpu"])
+
+
+@pytest.mark.parametrize("case", ["f32_a", "f32_b", "f16", "bf16"])
+def test_truth_matches_reference_formula(rms, case):
+    """fp64 oracle vs the formula the reference's test differentiates (test_rmsnorm.py:55-60), fwd and bwd."""
+    x, w, dy, eps = rms[f"{case}_x"], rms[f"{case}_w"], rms[f"{case}_dy"], float(rms[f"{case}_eps"])
+    y, _ = oracle.rmsnorm_fwd(x, w, eps)
+    dx, dw = oracle.rmsnorm_bwd(dy, x, w, eps)
+    np.testing.assert_allclose(y, rms[f"{case}_y"], rtol=1e-12, atol=1e-13)
+    np.testing.assert_allclose(dx, rms[f"{case}_dx"], rtol=1e-10, atol=1e-12)
+    np.testing.assert_allclose(dw, rms[f"{case}_dw"], rtol=1e-10, atol=1e-12)
+    # and the reference's fp32 CPU forward sits within fp32 rounding of that truth
+    np.testing.assert_allclose(rms[f"{case}_y_refcpu"], y, rtol=2e-6, atol=1e-6)
+
+
+def test_live_reference_library_agrees_with_fixture(rms):
+    """When oracle/_ref is present, its rmsnorm_cpu must reproduce the committed fixture bit for bit."""
+    ref = oracle.ref_lib()
+    if ref is None:
+        pytest.skip("oracle/_ref/libmgr_ref.so not built (no reference tree on this machine)")
+    y = ref.cpu_forward(rms["f32_a_x"], rms["f32_a_w"], float(rms["f32_a_eps"]))
+    assert np.array_equal(y, rms["f32_a_y_refcpu"])
+
+
+@pytest.mark.parametrize("case,tol", [("act_f32", 2e-6), ("act_f16", 2e-3), ("act_bf16", 1.6e-2)])
+def test_activation_matches_reference_triton_kernels(swi, case, tol):
+    """fp64 oracle vs _mg_swiglu_fwd_kernel / _mg_swiglu_bwd_kernel outputs (megagemm/swiglu.py:18-79).
+    The reference stores in the tensor dtype, so the half cases differ from the truth by one rounding."""
+    gv, dh = swi[f"{case}_gv"], swi[f"{case}_dh"]
+    f = gv.shape[1] // 2
+    h = oracle.swiglu_act_fwd(gv, f)
+    dgv = oracle.swiglu_act_bwd(dh, gv, f)
+    np.testing.assert_allclose(swi[f"{case}_h"], h, rtol=tol, atol=tol)
+    np.testing.assert_allclose(swi[f"{case}_dgv"], dgv, rtol=tol, atol=tol)
+
+
+def test_mlp_matches_reference_module(swi):
+    """fp64 MLP oracle vs MegaGemmTriton fwd+bwd and vs PyTorchSwiGLU (benchmark_swiglu.py:40-58, 85-89)."""
+    out = oracle.swiglu_mlp(swi["mlp_x"].reshape(-1, 64), swi["mlp_w12"], swi["mlp_w3"], dy=swi["mlp_dy"].reshape(-1, 64))
+    assert int(swi["mlp_hidden"]) == swi["mlp_w3"].shape[1] == 128
+    np.testing.assert_allclose(swi["mlp_y"].reshape(-1, 64), out["y"], rtol=1e-4, atol=2e-6)
+    np.testing.assert_allclose(swi["mlp_y_pytorchswiglu"].reshape(-1, 64), out["y"], rtol=1e-4, atol=2e-6)
+    np.testing.assert_allclose(swi["mlp_dx"].reshape(-1, 64), out["dx"], rtol=1e-4, atol=2e-6)
+    np.testing.assert_allclose(swi["mlp_dw12"], out["dw12"], rtol=1e-4, atol=5e-6)
+    np.testing.assert_allclose(swi["mlp_dw3"], out["dw3"], rtol=1e-4, atol=5e-6)
+
+
+def test_linear_c_restatement(swi):
+    a = swi["mlp_x"].reshape(-1, 64)
+    b = swi["mlp_w12"]
+    c = np.empty((a.shape[0], b.shape[0]), np.float64)
+    oracle.lib().mgr_oracle_linear_f64(c.ctypes.data, np.ascontiguousarray(a).ctypes.data,
+                                       np.ascontiguousarray(b).ctypes.data, a.shape[0], b.shape[0], a.shape[1])
+    np.testing.assert_allclose(c, oracle.linear(a, b), rtol=1e-12, atol=1e-14)
+
+
+def test_round_to_matches_torch():
+    import torch
+
+    rng = np.random.default_rng(0)
+    a = (rng.standard_normal(10000) * 10 ** rng.uniform(-6, 4, 10000)).astype(np.float32)
+    t = torch.from_numpy(a)
+    assert np.array_equal(oracle.round_to(a, "bf16"), t.to(torch.bfloat16).float().numpy())
+    assert np.array_equal(oracle.round_to(a, "f16"), t.to(torch.float16).float().numpy())
+    assert oracle.ulp_of(np.array([1.0]), "bf16")[0] == 2.0 ** -7
+    assert oracle.ulp_of(np.array([5.0]), "f16")[0] == 2.0 ** -8
