@@ -202,10 +202,10 @@ def reference_arm(args) -> int:
     return 0
 
 
-def workload_config(n_gpus: int) -> dict:
-    return {"workload": f"RMSNorm bf16 forward+backward, {ROWS_PER_GPU} rows x hidden {HIDDEN} per GPU, eps 1e-6 "
-                        "(x~N(0,2), w=1+0.1N(0,1), dy~N(0,1))",
-            "rows_per_gpu": ROWS_PER_GPU, "hidden": HIDDEN, "sharding": f"rows x{n_gpus}, fp32 dW all-reduce" if n_gpus > 1 else "none",
+def workload_config(n_gpus: int, rows: int = ROWS_PER_GPU) -> dict:
+    return {"workload": f"RMSNorm bf16 forward+backward, {rows} rows x hidden {HIDDEN} per GPU, eps 1e-6 "
+                        "(x~N(0,2), w=1+0.1N(0,1), dy~N(0,1))" + ("" if rows == ROWS_PER_GPU else " [REDUCED CASE, not the benchmark]"),
+            "rows_per_gpu": rows, "hidden": HIDDEN, "sharding": f"rows x{n_gpus}, fp32 dW all-reduce" if n_gpus > 1 else "none",
             "l2": "inputs larger than L2 (1 GiB per tensor, 126 MB L2)", "seed": SEED}
 
 
@@ -394,6 +394,9 @@ def main(argv=None) -> int:
     ap.add_argument("--e2e-steps", type=int, default=3)
     ap.add_argument("--no-side", action="store_true", help="skip the other configurations (N=1 extras)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
+    ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
+    ap.add_argument("--rows", type=int, default=ROWS_PER_GPU,
+                    help="rows per GPU; anything but the default is a reduced case for profiler captures, not a bench value")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm(args)
@@ -424,19 +427,21 @@ def main(argv=None) -> int:
     peaks, peak_kind = measured_peaks()
     peak_gbs = float(peaks["hbm_gbs"])
 
-    main_buf = RmsBuffers(L, ROWS_PER_GPU, HIDDEN, torch.bfloat16, device, SEED + rank, x_scale=2.0 ** 0.5)
+    main_buf = RmsBuffers(L, args.rows, HIDDEN, torch.bfloat16, device, SEED + rank, x_scale=2.0 ** 0.5)
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
     r = time_device_resident([main_buf], args.steps, warmup, world)
     if sampler:
         sampler.stop()
-    nb = rms_bytes(ROWS_PER_GPU, HIDDEN, 2)
+    nb = rms_bytes(args.rows, HIDDEN, 2)
     ms_per_step = r["total_ms"] / args.steps
     value = world * nb["total"] / (ms_per_step * 1e-3) / 1e9
 
-    e2e = time_e2e(ROWS_PER_GPU, HIDDEN, device, args.e2e_steps, 1, world, main_buf)
-    e2e_value = world * nb["total"] / (e2e["ms_per_step"] * 1e-3) / 1e9
+    e2e = None
+    if not args.no_e2e:
+        e2e = time_e2e(args.rows, HIDDEN, device, args.e2e_steps, 1, world, main_buf)
+        e2e_value = world * nb["total"] / (e2e["ms_per_step"] * 1e-3) / 1e9
 
     side = {}
     if world == 1 and not args.no_side:
@@ -453,7 +458,7 @@ def main(argv=None) -> int:
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
-            "dtype": "bf16", "data": "synthetic", "config": workload_config(world),
+            "dtype": "bf16", "data": "synthetic", "config": workload_config(world, args.rows),
             "frac_of_hbm_peak": value / world / peak_gbs,
             "roofline": {"bound": "hbm", "kernel": "rms_bwd_reg + rms_dw_reduce (one mgr_rmsnorm_bwd call)",
                          "achieved": bwd_gbs, "peak": peak_gbs, "unit": "GB/s", "frac": bwd_gbs / peak_gbs,
@@ -462,9 +467,10 @@ def main(argv=None) -> int:
                          "traffic": (TRAFFIC_PER_ALGO_BYTE * nb["bwd"]) if TRAFFIC_PER_ALGO_BYTE else None},
             "roofline_fwd": {"bound": "hbm", "kernel": "rms_fwd_reg", "achieved": fwd_gbs, "peak": peak_gbs, "unit": "GB/s",
                              "frac": fwd_gbs / peak_gbs, "algorithmic_bytes_per_launch": nb["fwd"], "avg_launch_ms": r["fwd_ms"]},
-            "e2e": {"value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
-                    "ms_per_step": e2e["ms_per_step"], "steps": e2e["steps"],
-                    "path": "pinned host -> RMSNorm module fwd+bwd -> pinned host (y, dx, dW)"},
+            "e2e": None if e2e is None else {
+                "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                "ms_per_step": e2e["ms_per_step"], "steps": e2e["steps"],
+                "path": "pinned host -> RMSNorm module fwd+bwd -> pinned host (y, dx, dW)"},
             "gpu_launches": 3 * args.steps,
             "clocks": sampler.summary(*r["window"]) if sampler else None,
             "sm_count": sms.value,

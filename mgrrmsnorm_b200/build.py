@@ -82,7 +82,7 @@ def build(force: bool = False, verbose: bool = False) -> Path:
             print(log)
     newest = max(o.stat().st_mtime for o in objs)
     if force or not LIB_PATH.exists() or LIB_PATH.stat().st_mtime < newest:
-        cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs), "-lcudart", "-lcuda"]
+        cmd = [nvcc, "-shared", "-o", str(LIB_PATH), *map(str, objs)]
         proc = subprocess.run(cmd, capture_output=True, text=True)
         if proc.returncode != 0:
             raise RuntimeError(f"link failed:\n{proc.stdout}\n{proc.stderr}")
