@@ -63,6 +63,14 @@ const char* mgr_status_str(int status);
  * receives the SM count. No reference counterpart (the reference never asks the device). */
 int mgr_device_check(int* sm_count);
 
+/* Status the kernels themselves left on the current device: MGR_OK, or MGR_ERR_DEVICE_TIMEOUT if a
+ * bounded wait inside a kernel (an mbarrier wait of a bulk-copy or tensor-core pipeline) ran out since
+ * the last clearing read. clear != 0 resets it. This is the ONLY entry point that synchronises (it
+ * copies one word from the device); the launch entry points never do. No reference counterpart: the
+ * reference's kernels have no device-side waits and its wrappers only see launch errors
+ * (src/rmsnorm_kernel.cu:544-548). */
+int mgr_device_status(int clear);
+
 /* ------------------------------------------------------------------------------------------------
  * RMSNorm forward.   y[r,j] = round_dtype((x[r,j] * inv[r]) * w[j]),  inv[r] = 1/sqrt(mean_j x[r,j]^2 + eps)
  *

@@ -37,6 +37,7 @@ SIGNATURES = {
     "mgr_abi_version": (_int, []),
     "mgr_status_str": (ctypes.c_char_p, [_int]),
     "mgr_device_check": (_int, [ctypes.POINTER(_int)]),
+    "mgr_device_status": (_int, [_int]),
     "mgr_rmsnorm_fwd": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _int, _vp]),
     "mgr_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "mgr_rmsnorm_bwd": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _sz, _vp]),

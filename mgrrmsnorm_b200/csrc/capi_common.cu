@@ -29,7 +29,15 @@ DeviceInfo current_device_info() {
     return di;
 }
 
+int rmsnorm_status_fetch(int clear);  // rmsnorm_sm100.cu
+
 }  // namespace mgr
+
+extern "C" int mgr_device_status(int clear) {
+    const mgr::DeviceInfo di = mgr::current_device_info();
+    if (di.status != MGR_OK) return di.status;
+    return mgr::rmsnorm_status_fetch(clear);
+}
 
 extern "C" int mgr_abi_version(void) { return MGR_ABI_VERSION; }
 

@@ -128,6 +128,13 @@ __device__ __forceinline__ float warp_sum(float v) {
     return v;
 }
 
+// Tells the compiler the packet may have changed. Used on loop-invariant packed operands (the weight
+// row) at the top of a row loop so that their fp32 expansion is redone per row instead of being
+// hoisted into 2-4x as many live registers.
+__device__ __forceinline__ void keep_packed(uint4& p) {
+    asm volatile("" : "+r"(p.x), "+r"(p.y), "+r"(p.z), "+r"(p.w));
+}
+
 // Streaming (read-once / write-once) 16-byte global accesses.
 __device__ __forceinline__ uint4 ld_stream16(const uint4* p) { return __ldcs(p); }
 __device__ __forceinline__ void st_stream16(uint4* p, const uint4& v) { __stcs(p, v); }

@@ -12,10 +12,17 @@
 // Shapes the packet path cannot take (cols not a multiple of the packet width, pointers not 16-byte
 // aligned, rows longer than 4096 packets) go to scalar kernels with the same arithmetic.
 
+#include <cstdlib>
+#include <cstring>
+
 #include "mgr_common.cuh"
+#include "rmsnorm_ring.cuh"
 
 namespace mgr {
 namespace {
+
+// Set by a kernel whose bounded wait ran out (MGR_ERR_DEVICE_TIMEOUT); read by mgr_device_status().
+__device__ int g_rms_status = 0;
 
 // ------------------------------------------------------------------------------------------------
 // Packet ("reg") kernels: TPR threads cooperate on one row, each holds VPT 16-byte packets of it.
@@ -28,6 +35,10 @@ struct RegGeom {
     static constexpr int kGroups = kBlock / TPR;
     static constexpr int kWarpsPerRow = TPR / 32;
     static constexpr int kWarps = kBlock / 32;
+    // resident CTAs per SM the register allocation is held to (forward: 64 registers per thread;
+    // backward: 128, which still holds the row packets and the dW partials without spilling)
+    static constexpr int kFwdMinBlocks = 1024 / kBlock < 1 ? 1 : 1024 / kBlock;
+    static constexpr int kBwdMinBlocks = 512 / kBlock < 1 ? 1 : 512 / kBlock;
 };
 
 // Sum of `v` over the TPR threads that share a row. `red` is a [2][kWarps] shared array used
@@ -50,7 +61,7 @@ __device__ __forceinline__ float row_sum(float v, float (*red)[RegGeom<TPR>::kWa
 }
 
 template <typename T, int TPR, int VPT>
-__global__ void __launch_bounds__(RegGeom<TPR>::kBlock)
+__global__ void __launch_bounds__(RegGeom<TPR>::kBlock, RegGeom<TPR>::kFwdMinBlocks)
 rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* __restrict__ x,
             const T* __restrict__ w, int64_t rows, int cols, float eps) {
     using Geo = RegGeom<TPR>;
@@ -80,6 +91,7 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* __restrict_
         for (int k = 0; k < VPT; ++k) {
             const int v = t + k * TPR;
             xv[k] = (live && v < nvec) ? ld_stream16(xr + v) : make_uint4(0, 0, 0, 0);
+            keep_packed(wv[k]);
         }
         float ss = 0.f;
 #pragma unroll
@@ -114,7 +126,7 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* __restrict_
 // partial sums stay in registers until the CTA is done; the G row groups of a CTA are then folded in
 // shared memory (fixed order) and the CTA writes ONE fp32 partial row ws[blockIdx.x, :].
 template <typename T, int TPR, int VPT>
-__global__ void __launch_bounds__(RegGeom<TPR>::kBlock)
+__global__ void __launch_bounds__(RegGeom<TPR>::kBlock, RegGeom<TPR>::kBwdMinBlocks)
 rms_bwd_reg(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
             const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int cols) {
     using Geo = RegGeom<TPR>;
@@ -153,6 +165,7 @@ rms_bwd_reg(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy
             const bool on = live && v < nvec;
             xv[k] = on ? ld_stream16(xr + v) : make_uint4(0, 0, 0, 0);
             gv[k] = on ? ld_stream16(gr + v) : make_uint4(0, 0, 0, 0);
+            keep_packed(wv[k]);
         }
         const float rinv = live ? __ldg(inv_rms + r) : 0.f;
 
@@ -411,11 +424,143 @@ int64_t scalar_grid(int64_t rows, const DeviceInfo& di) {
     return rows < cap ? rows : cap;
 }
 
+// ---- ring (bulk-copy) path ------------------------------------------------------------------------
+
+enum class Path { kAuto, kReg, kRing, kScalar };
+
+// MGR_RMSNORM_PATH=reg|ring|scalar pins the kernel family (benchmarking and tests); unset = automatic.
+Path forced_path() {
+    const char* e = std::getenv("MGR_RMSNORM_PATH");
+    if (e == nullptr) return Path::kAuto;
+    if (std::strcmp(e, "reg") == 0) return Path::kReg;
+    if (std::strcmp(e, "ring") == 0) return Path::kRing;
+    if (std::strcmp(e, "scalar") == 0) return Path::kScalar;
+    return Path::kAuto;
+}
+
+int* rms_status_ptr(const DeviceInfo& di) {
+    static int* cache[kMaxDevices] = {nullptr};
+    if (cache[di.device] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_rms_status) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        cache[di.device] = static_cast<int*>(p);
+    }
+    return cache[di.device];
+}
+
+template <typename K>
+bool allow_big_smem(K kernel, bool* done /* [kMaxDevices] */, int device) {
+    if (done[device]) return true;
+    if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBudget)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return false;
+    }
+    done[device] = true;
+    return true;
+}
+
+// Returns MGR_OK if launched, 1 if the ring path does not apply (caller falls back), < 0 on error.
+template <typename T>
+int fwd_ring_try(T* y, float* inv, const T* x, const T* w, int64_t rows, int64_t cols, float eps, const DeviceInfo& di,
+                 cudaStream_t s) {
+    static bool attr[kMaxDevices] = {false};
+    const RingPlan plan = fwd_ring_plan(rows, cols, sizeof(T));
+    if (!plan.ok) return 1;
+    int* status = rms_status_ptr(di);
+    if (status == nullptr || !allow_big_smem(rms_fwd_ring<T, kFwdRingWarps>, attr, di.device)) return 1;
+    const int64_t nchunks = (rows + plan.rows_per_slot - 1) / plan.rows_per_slot;
+    const unsigned grid = static_cast<unsigned>(nchunks < di.sm_count ? nchunks : di.sm_count);
+    rms_fwd_ring<T, kFwdRingWarps><<<grid, (kFwdRingWarps + 1) * 32, plan.smem_bytes, s>>>(
+        y, inv, x, w, rows, static_cast<int>(cols), eps, plan.rows_per_slot, plan.nslots, plan.w_bytes, plan.slot_bytes, status);
+    return launch_status();
+}
+
+struct RingShape {
+    int tpr, vpt;
+};
+constexpr RingShape kRingShapes[] = {{32, 1}, {32, 2}, {64, 2}, {128, 2}, {256, 2}, {512, 2}, {512, 4}};
+constexpr int kNumRingShapes = sizeof(kRingShapes) / sizeof(kRingShapes[0]);
+
+int ring_shape_for(int64_t nvec) {
+    for (int i = 0; i < kNumRingShapes; ++i)
+        if (nvec <= static_cast<int64_t>(kRingShapes[i].tpr) * kRingShapes[i].vpt) return i;
+    return -1;
+}
+
+struct BwdRingPlan {
+    int ok, shape, nslots;
+    uint32_t slot_bytes, smem_bytes;
+    int64_t grid;
+};
+
+BwdRingPlan bwd_ring_plan(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& di) {
+    BwdRingPlan p{};
+    const int64_t vec = 16 / static_cast<int64_t>(elem);
+    if (cols % vec != 0) return p;
+    p.shape = ring_shape_for(cols / vec);
+    if (p.shape < 0) return p;
+    const int G = kBwdRingThreads / kRingShapes[p.shape].tpr;
+    const uint64_t slot = 2ull * G * cols * elem;
+    const uint32_t fixed = 2 * 8 * kRingMaxSlots + 256;
+    if (fixed + 3 * slot > kSmemBudget) return p;
+    int n = static_cast<int>((kSmemBudget - fixed) / slot);
+    if (n > kRingMaxSlots) n = kRingMaxSlots;
+    const uint64_t fold = static_cast<uint64_t>(G - 1) * kRingShapes[p.shape].tpr * kRingShapes[p.shape].vpt * 16 * 4 / elem;
+    if (fold > n * slot) return p;
+    p.nslots = n;
+    p.slot_bytes = static_cast<uint32_t>(slot);
+    p.smem_bytes = static_cast<uint32_t>(n * slot + 2 * 8 * n);
+    const int64_t ngroups = (rows + G - 1) / G;
+    p.grid = ngroups < di.sm_count ? ngroups : di.sm_count;
+    p.ok = 1;
+    return p;
+}
+
+template <typename T, int I = 0>
+struct RingDispatch {
+    static int bwd(const BwdRingPlan& plan, T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv,
+                   int64_t rows, int cols, int* status, const DeviceInfo& di, cudaStream_t s) {
+        if (plan.shape == I) {
+            constexpr int TPR = kRingShapes[I].tpr, VPT = kRingShapes[I].vpt;
+            static bool attr[kMaxDevices] = {false};
+            if (!allow_big_smem(rms_bwd_ring<T, TPR, VPT>, attr, di.device)) return 1;
+            rms_bwd_ring<T, TPR, VPT><<<static_cast<unsigned>(plan.grid), kBwdRingThreads, plan.smem_bytes, s>>>(
+                dx, ws, dy, x, w, inv, rows, cols, plan.nslots, plan.slot_bytes, status);
+            return launch_status();
+        }
+        if constexpr (I + 1 < kNumRingShapes)
+            return RingDispatch<T, I + 1>::bwd(plan, dx, ws, dy, x, w, inv, rows, cols, status, di, s);
+        return 1;
+    }
+};
+
+// Automatic choice between the register and the ring family, from back-to-back timings on B200
+// (fraction of the measured 6.55 TB/s copy bandwidth, register / ring):
+//   forward : 2-4 KB rows 0.83 / 1.00; 8 KB 0.97 / 0.95; 16 KB 0.99 / 0.92; 32 KB 0.97 / 0.89
+//   backward: 2 KB rows 0.90 / 0.80; 4 KB 0.76 / 0.84; 8 KB 0.85 / 0.83; 16 KB 0.92 / 0.82; 32 KB 0.84-0.87 / 0.90-0.94
+// The ring needs enough rows to fill its pipeline, hence the row-count floor.
+bool prefer_ring_fwd(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& di) {
+    const int64_t row_bytes = cols * static_cast<int64_t>(elem);
+    return rows >= 8ll * di.sm_count && row_bytes > 2048 && row_bytes <= 4096;
+}
+bool prefer_ring_bwd(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& di) {
+    const int64_t row_bytes = cols * static_cast<int64_t>(elem);
+    return rows >= 8ll * di.sm_count && ((row_bytes > 2048 && row_bytes <= 4096) || row_bytes > 16384);
+}
+
 template <typename T>
 int fwd_typed(void* y, float* inv, const void* x, const void* w, int64_t rows, int64_t cols, float eps,
               const DeviceInfo& di, cudaStream_t s) {
     constexpr int VEC = Elem<T>::kVec;
-    const bool packets = cols % VEC == 0 && aligned_to(y, 16) && aligned_to(x, 16) && aligned_to(w, 16);
+    const Path forced = forced_path();
+    const bool packets = forced != Path::kScalar && cols % VEC == 0 && aligned_to(y, 16) && aligned_to(x, 16) && aligned_to(w, 16);
+    if (packets && forced != Path::kReg && (forced == Path::kRing || prefer_ring_fwd(rows, cols, sizeof(T), di))) {
+        const int st = fwd_ring_try<T>(static_cast<T*>(y), inv, static_cast<const T*>(x), static_cast<const T*>(w), rows, cols, eps, di, s);
+        if (st <= 0) return st;
+    }
     const int shape = packets ? reg_shape_for(cols / VEC) : -1;
     if (shape >= 0) {
         RegDispatch<T>::fwd(shape, static_cast<T*>(y), inv, static_cast<const T*>(x), static_cast<const T*>(w), rows,
@@ -427,8 +572,8 @@ int fwd_typed(void* y, float* inv, const void* x, const void* w, int64_t rows, i
     return launch_status();
 }
 
-// Partial rows the backward of this problem writes: the larger of the packet path's grid and the
-// scalar path's slice count, so one workspace size serves whichever path the pointers select.
+// Partial rows the backward of this problem may write: the largest over the three kernel families,
+// so one workspace size serves whichever family the pointers and the policy select.
 template <typename T>
 int64_t bwd_partials(int64_t rows, int64_t cols, const DeviceInfo& di) {
     constexpr int VEC = Elem<T>::kVec;
@@ -439,6 +584,8 @@ int64_t bwd_partials(int64_t rows, int64_t cols, const DeviceInfo& di) {
             const int64_t g = RegDispatch<T>::bwd_grid(shape, rows, di);
             if (g > p) p = g;
         }
+        const BwdRingPlan rp = bwd_ring_plan(rows, cols, sizeof(T), di);
+        if (rp.ok && rp.grid > p) p = rp.grid;
     }
     return p < 1 ? 1 : p;
 }
@@ -447,25 +594,38 @@ template <typename T>
 int bwd_typed(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, const void* w, const float* inv,
               int64_t rows, int64_t cols, float* ws, const DeviceInfo& di, cudaStream_t s) {
     constexpr int VEC = Elem<T>::kVec;
-    const bool packets = cols % VEC == 0 && aligned_to(dx, 16) && aligned_to(dy, 16) && aligned_to(x, 16) &&
-                         aligned_to(w, 16);
-    const int shape = packets ? reg_shape_for(cols / VEC) : -1;
-    int64_t P;
-    if (shape >= 0) {
-        P = RegDispatch<T>::bwd_grid(shape, rows, di);
-        RegDispatch<T>::bwd(shape, static_cast<T*>(dx), ws, static_cast<const T*>(dy), static_cast<const T*>(x),
-                            static_cast<const T*>(w), inv, rows, static_cast<int>(cols), P, s);
-    } else {
-        P = rows < kScalarDwSlices ? rows : kScalarDwSlices;
-        rms_bwd_dx_scalar<T><<<static_cast<unsigned>(scalar_grid(rows, di)), 256, 0, s>>>(
-            static_cast<T*>(dx), static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(w), inv, rows, cols);
+    const Path forced = forced_path();
+    const bool packets = forced != Path::kScalar && cols % VEC == 0 && aligned_to(dx, 16) && aligned_to(dy, 16) &&
+                         aligned_to(x, 16) && aligned_to(w, 16);
+    int64_t P = -1;
+    if (packets && forced != Path::kReg && (forced == Path::kRing || prefer_ring_bwd(rows, cols, sizeof(T), di))) {
+        const BwdRingPlan plan = bwd_ring_plan(rows, cols, sizeof(T), di);
+        int* status = plan.ok ? rms_status_ptr(di) : nullptr;
+        if (status != nullptr) {
+            const int st = RingDispatch<T>::bwd(plan, static_cast<T*>(dx), ws, static_cast<const T*>(dy), static_cast<const T*>(x),
+                                                static_cast<const T*>(w), inv, rows, static_cast<int>(cols), status, di, s);
+            if (st < 0) return st;
+            if (st == 0) P = plan.grid;
+        }
+    }
+    if (P < 0) {
+        const int shape = packets ? reg_shape_for(cols / VEC) : -1;
+        if (shape >= 0) {
+            P = RegDispatch<T>::bwd_grid(shape, rows, di);
+            RegDispatch<T>::bwd(shape, static_cast<T*>(dx), ws, static_cast<const T*>(dy), static_cast<const T*>(x),
+                                static_cast<const T*>(w), inv, rows, static_cast<int>(cols), P, s);
+        } else {
+            P = rows < kScalarDwSlices ? rows : kScalarDwSlices;
+            rms_bwd_dx_scalar<T><<<static_cast<unsigned>(scalar_grid(rows, di)), 256, 0, s>>>(
+                static_cast<T*>(dx), static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(w), inv, rows, cols);
+            int st = launch_status();
+            if (st != MGR_OK) return st;
+            dim3 grid(static_cast<unsigned>((cols + 127) / 128), static_cast<unsigned>(P));
+            rms_bwd_dw_scalar<T><<<grid, 128, 0, s>>>(ws, static_cast<const T*>(dy), static_cast<const T*>(x), inv, rows, cols);
+        }
         int st = launch_status();
         if (st != MGR_OK) return st;
-        dim3 grid(static_cast<unsigned>((cols + 127) / 128), static_cast<unsigned>(P));
-        rms_bwd_dw_scalar<T><<<grid, 128, 0, s>>>(ws, static_cast<const T*>(dy), static_cast<const T*>(x), inv, rows, cols);
     }
-    int st = launch_status();
-    if (st != MGR_OK) return st;
     rms_dw_reduce<T><<<static_cast<unsigned>((cols + 31) / 32), dim3(32, 32), 0, s>>>(
         static_cast<T*>(dw), dw_f32, ws, static_cast<int>(P), static_cast<int>(cols));
     return launch_status();
@@ -543,3 +703,19 @@ extern "C" int mgr_rmsnorm_bwd(void* dx, void* dw, float* dw_f32, const void* dy
         default: return bwd_typed<__nv_bfloat16>(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, ws, di, s);
     }
 }
+
+// Defined here, declared for capi_common.cu: reads (and optionally clears) this file's status word.
+namespace mgr {
+int rmsnorm_status_fetch(int clear) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_rms_status, sizeof(int)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return MGR_ERR_CUDA;
+    }
+    if (clear && v != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_rms_status, &zero, sizeof(int)) != cudaSuccess) (void)cudaGetLastError();
+    }
+    return v;
+}
+}  // namespace mgr

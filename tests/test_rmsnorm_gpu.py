@@ -287,16 +287,52 @@ def test_against_reference_cuda_kernels(ops, dtype):
             scale = b.double().abs().max()
             assert bool((err <= 1e-5 * b.double().abs() + 2e-6 * scale).all()), f"{name}: max err {float(err.max())}"
     else:
-        for a, b, name in ((y, ry, "y"), (dx, rdx, "dx")):
-            # both round an fp32 value next to the same truth, so they sit at most one output ulp apart
-            # (ulp taken at the larger magnitude: the two may straddle a power of two); the reference's
-            # --use_fast_math reciprocal/rsqrt can add one more on elements that cancel (dx)
+        ty, _ = oracle.rmsnorm_fwd(to_np(x), to_np(w), eps)
+        for a, b, truth, name in ((y, ry, ty, "y"), (dx, rdx, tdx, "dx")):
+            # Both sides round an fp32 value next to the same truth, so nearly every element is at most
+            # one output ulp apart (ulp at the larger magnitude: the two may straddle a power of two).
+            # The reference's --use_fast_math reciprocal/rsqrt moves a few cancelling elements of dx
+            # further, so the hard statement is against the truth: this library is never further from
+            # it than the reference's own kernel is.
             err = (a.float() - b.float()).abs()
             big = torch.maximum(a.float().abs(), b.float().abs())
             ulp = torch.from_numpy(oracle.ulp_of(to_np(big), dtype)).cuda().float()
-            assert bool((err <= 2 * ulp).all()), f"{name}: more than two ulp from the reference kernel"
-            assert float((err > ulp).float().mean()) < 1e-4, f"{name}: too many elements beyond one ulp"
-            assert float(err[ulp <= 5e-3].max()) <= 1e-2
+            assert float((err > ulp).float().mean()) < 1e-3, f"{name}: too many elements beyond one ulp of the reference"
+            assert float(err[ulp <= 5e-3].max()) <= 1e-2, f"{name}: more than 1e-2 from the reference kernel"
+            e_ours = np.abs(to_np(a).astype(np.float64) - truth).max()
+            e_ref = np.abs(to_np(b).astype(np.float64) - truth).max()
+            assert e_ours <= e_ref + 1e-9, f"{name}: max error {e_ours} vs the reference kernel's {e_ref}"
         ours = np.abs(to_np(dw).astype(np.float64) - tdw).max()
         theirs = np.abs(to_np(rdw).astype(np.float64) - tdw).max()
         assert ours <= theirs + 1e-9, f"dW error {ours} vs reference {theirs}"
+
+
+# ---- every kernel family on the same inputs --------------------------------------------------------
+
+@pytest.mark.parametrize("path", ["reg", "ring", "scalar"])
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("rows,cols", [(3, 8), (129, 128), (1200, 1024), (2500, 2048), (1531, 4096), (777, 5120), (1300, 8192),
+                                        (600, 16384)])
+def test_each_kernel_family_matches_oracle(ops, built_lib, monkeypatch, path, dtype, rows, cols):
+    """MGR_RMSNORM_PATH pins the register, bulk-copy-ring or scalar kernels (a family that cannot take
+    the shape falls through to the next one); all must meet the same tolerances."""
+    monkeypatch.setenv("MGR_RMSNORM_PATH", path)
+    check_against_oracle(ops, rows, cols, dtype, 1e-6, seed=rows + cols)
+    assert built_lib.mgr_device_status(1) == 0
+
+
+@pytest.mark.parametrize("path", ["reg", "ring"])
+def test_families_are_each_bit_reproducible(ops, monkeypatch, path):
+    monkeypatch.setenv("MGR_RMSNORM_PATH", path)
+    x, w, dy = seeded_rmsnorm_inputs(5000, 4096, "bf16", 17)
+    xd, wd, dyd = x.cuda(), w.cuda(), dy.cuda()
+    first = None
+    for _ in range(10):
+        y, inv = ops.rmsnorm_forward(xd, wd, 1e-6)
+        dx, dw, dw32 = ops.rmsnorm_backward_full(dyd, xd, wd, inv, want_dw_f32=True)
+        torch.cuda.synchronize()
+        cur = [t.clone() for t in (y, inv, dx, dw32)]
+        if first is None:
+            first = cur
+        else:
+            assert all(torch.equal(a, b) for a, b in zip(first, cur))
