@@ -130,6 +130,25 @@ int mgr_rmsnorm_bwd(void* dx, void* dw, float* dw_f32, const void* dy, const voi
 int mgr_swiglu_act_fwd(void* h, const void* gv, int64_t m, int64_t f, int dtype, void* stream);
 int mgr_swiglu_act_bwd(void* dgv, const void* dh, const void* gv, int64_t m, int64_t f, int dtype, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * SwiGLU MLP on tensor cores (tcgen05 / TMEM / TMA). fp16 and bf16 only, fp32 accumulation.
+ *
+ * mgr_swiglu_fused_fwd: h[m, f] = round_dtype( silu(x w12[0:f]^T) * (x w12[f:2f]^T) ) in one kernel.
+ *   x [m, d] row-major; w12 [2f, d] row-major with the gate rows first and the value rows second (the
+ *   layout of MegaGemmTriton.w12.weight, megagemm/swiglu.py:163, benchmark_swiglu.py:85-89).
+ *   Replaces `self.w12(x)` followed by MegaGemmFunction (megagemm/swiglu.py:167-168): the [m, 2f]
+ *   projection is never written to memory, and the activation sees the fp32 accumulator instead of a
+ *   value already rounded to fp16/bf16.
+ * mgr_gemm_tn: c[m, n] = round_dtype( a[m, k] b[n, k]^T ), leading dimensions in elements. Replaces an
+ *   nn.Linear without bias (`self.w3(hidden)`, megagemm/swiglu.py:169).
+ * Requirements: d, f, n, k and the leading dimensions multiples of 8; pointers 16-byte aligned.
+ * m == 0 is a no-op. Shapes outside these limits return MGR_ERR_BAD_SHAPE (the caller then keeps
+ * the library GEMM it would have used with the reference).
+ */
+int mgr_swiglu_fused_fwd(void* h, const void* x, const void* w12, int64_t m, int64_t d, int64_t f, int dtype, void* stream);
+int mgr_gemm_tn(void* c, const void* a, const void* b, int64_t m, int64_t n, int64_t k,
+                int64_t lda, int64_t ldb, int64_t ldc, int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -30,13 +30,16 @@ DeviceInfo current_device_info() {
 }
 
 int rmsnorm_status_fetch(int clear);  // rmsnorm_sm100.cu
+int gemm_status_fetch(int clear);     // gemm_sm100.cu
 
 }  // namespace mgr
 
 extern "C" int mgr_device_status(int clear) {
     const mgr::DeviceInfo di = mgr::current_device_info();
     if (di.status != MGR_OK) return di.status;
-    return mgr::rmsnorm_status_fetch(clear);
+    const int a = mgr::rmsnorm_status_fetch(clear);
+    const int b = mgr::gemm_status_fetch(clear);
+    return a != MGR_OK ? a : b;
 }
 
 extern "C" int mgr_abi_version(void) { return MGR_ABI_VERSION; }

@@ -1,0 +1,383 @@
+// Tensor-core GEMM family for the SwiGLU MLP on sm_100a: tcgen05.mma with accumulators in tensor
+// memory (TMEM), operands staged in shared memory by TMA, fused epilogues.
+//
+// Replaces, on the MLP hot path, the two library GEMMs and the Triton activation kernel of
+// MegaGemmTriton.forward (megagemm/swiglu.py:166-169: w12(x) -> MegaGemmFunction -> w3(h)):
+//   * mgr_swiglu_fused_fwd : h = silu(x Wg^T) * (x Wv^T) in ONE kernel; each CTA tile owns 128 gate
+//     columns and the matching 128 value columns (two B boxes of w12: rows n0.. and F+n0..), so the
+//     [M, 2F] projection never reaches HBM;
+//   * mgr_gemm_tn          : C = A B^T (nn.Linear without bias), used for w3(h).
+//
+// Kernel shape (one CTA per SM, persistent over output tiles, 192 threads):
+//   warp 0    : TMA producer  -- cp.async.bulk.tensor.2d into a 4-stage ring (A 128x64, B 256x64, 128B swizzle)
+//   warp 1    : MMA issuer    -- one elected thread issues tcgen05.mma (M128 N256 K16, fp32 accumulate);
+//               also owns the TMEM allocation (512 columns = two 128x256 accumulators)
+//   warps 2-5 : epilogue      -- tcgen05.ld the finished accumulator, apply the epilogue, store; the second
+//               accumulator lets the next tile's main loop run meanwhile.
+// No cluster, no multicast. Every mbarrier wait is bounded (mgr_ptx.cuh).
+
+#include <cuda.h>
+
+#include <type_traits>
+
+#include "mgr_common.cuh"
+#include "mgr_ptx.cuh"
+
+namespace mgr {
+namespace {
+
+__device__ int g_gemm_status = 0;
+
+constexpr int kBM = 128;         // tile rows (UMMA M)
+constexpr int kBN = 256;         // accumulator columns per tile (UMMA N)
+constexpr int kBK = 64;          // K per stage: 64 x 2 B = one 128-byte swizzle row
+constexpr int kStages = 4;
+constexpr int kUmmaK = 16;       // K of one tcgen05.mma for 16-bit operands
+constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB
+constexpr uint32_t kBBytes = kBN * kBK * 2;   // 32 KB
+constexpr uint32_t kStageBytes = kABytes + kBBytes;
+constexpr uint32_t kGemmSmem = kStages * kStageBytes + 1024;  // + slack to align the ring to 1024 B
+constexpr int kGemmThreads = 192;
+constexpr uint32_t kTmemCols = 512;
+
+enum Epilogue { kEpiPlain = 0, kEpiSwiglu = 1 };
+
+// Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes with the
+// 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups are 1024 B apart
+// (stride byte offset), leading byte offset is unused for swizzled K-major layouts (encoded 1),
+// descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B). Addresses are in 16-byte units.
+__device__ __forceinline__ uint64_t smem_desc_k_major_sw128(uint32_t smem_addr) {
+    uint64_t d = 0;
+    d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
+    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(1024 >> 4) << 32;
+    d |= static_cast<uint64_t>(1) << 46;
+    d |= static_cast<uint64_t>(2) << 61;
+    return d;
+}
+
+// Instruction descriptor, kind::f16: fp32 accumulator, A and B both K-major, M=128, N=256.
+// `fmt` = 0 for fp16 operands, 1 for bf16.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(kBN >> 3) << 17) |
+           (static_cast<uint32_t>(kBM >> 4) << 24);
+}
+
+__device__ __forceinline__ float silu_mul(float g, float v) { return (g * (1.0f / (1.0f + __expf(-g)))) * v; }
+
+template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
+template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
+    __half2 h = __floats2half2_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, float b) {
+    __nv_bfloat162 h = __floats2bfloat162_rn(a, b);
+    return *reinterpret_cast<uint32_t*>(&h);
+}
+
+// C tile coordinates of linear tile index t: M index runs fastest so that the CTAs running at the same
+// time share a few B (weight) tiles and all of A through L2.
+struct TileCoord {
+    int m0, n0;
+};
+__device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_step) {
+    return TileCoord{(t % m_tiles) * kBM, (t / m_tiles) * n_step};
+}
+
+// A: [M, K] row-major (tmA, box 64 x 128). B: [Nb, K] row-major (tmB, box 64 x 128).
+// kEpiPlain : C[M, n_out] = A B^T; a tile covers 256 columns of C (B rows n0 .. n0+255).
+// kEpiSwiglu: C[M, n_out] = silu(A Bg^T) * (A Bv^T) with Bg = B rows [0, n_out), Bv = B rows
+//             [n_out, 2 n_out); a tile covers 128 columns of C (B rows n0.. and n_out+n0..).
+template <int EPI, typename T>
+__global__ void __launch_bounds__(kGemmThreads, 1)
+gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, T* __restrict__ C,
+               int M, int n_out, int K, int64_t ldc, int* __restrict__ status) {
+    constexpr int kNStep = EPI == kEpiSwiglu ? kBN / 2 : kBN;  // output columns per tile
+    extern __shared__ unsigned char smem_raw[];
+    __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_tfull[2], bar_tempty[2];
+    __shared__ uint32_t tmem_base_slot;
+    __shared__ int abort_flag;
+
+    const uint32_t ring = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
+    const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+    const int m_tiles = (M + kBM - 1) / kBM;
+    const int n_tiles = (n_out + kNStep - 1) / kNStep;
+    const int num_tiles = m_tiles * n_tiles;
+    const int num_kb = (K + kBK - 1) / kBK;
+
+    if (threadIdx.x == 0) {
+        abort_flag = 0;
+        for (int s = 0; s < kStages; ++s) {
+            ptx::mbar_init(ptx::smem_addr(&bar_full[s]), 1);
+            ptx::mbar_init(ptx::smem_addr(&bar_empty[s]), 1);
+        }
+        for (int a = 0; a < 2; ++a) {
+            ptx::mbar_init(ptx::smem_addr(&bar_tfull[a]), 1);
+            ptx::mbar_init(ptx::smem_addr(&bar_tempty[a]), 4);
+        }
+        ptx::fence_mbar_init();
+        ptx::prefetch_tmap(&tmA);
+        ptx::prefetch_tmap(&tmB);
+    }
+    if (warp == 1) {
+        ptx::tmem_alloc(ptx::smem_addr(&tmem_base_slot), kTmemCols);
+        ptx::tmem_relinquish();
+    }
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    ptx::tc_fence_after_sync();
+    const uint32_t tmem_base = tmem_base_slot;
+
+    if (warp == 0) {
+        // ---------------- TMA producer ----------------
+        if (ptx::elect_one()) {
+            int stage = 0;
+            uint32_t phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+                const TileCoord tc = tile_coord(t, m_tiles, kNStep);
+                const int b_row1 = EPI == kEpiSwiglu ? n_out + tc.n0 : tc.n0 + kBN / 2;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_addr(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    const uint32_t full = ptx::smem_addr(&bar_full[stage]);
+                    const uint32_t sa = ring + stage * kStageBytes;
+                    const uint32_t sb = sa + kABytes;
+                    ptx::mbar_arrive_expect_tx(full, kStageBytes);
+                    ptx::tma_load_2d(sa, &tmA, kb * kBK, tc.m0, full);
+                    ptx::tma_load_2d(sb, &tmB, kb * kBK, tc.n0, full);
+                    ptx::tma_load_2d(sb + kBBytes / 2, &tmB, kb * kBK, b_row1, full);
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+            }
+        }
+    } else if (warp == 1) {
+        // ---------------- MMA issuer ----------------
+        if (ptx::elect_one()) {
+            constexpr uint32_t idesc = instr_desc(sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u);
+            int stage = 0, acc = 0;
+            uint32_t phase = 0, acc_phase = 0;
+            bool ok = true;
+            for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+                if (!ptx::mbar_wait(ptx::smem_addr(&bar_tempty[acc]), acc_phase ^ 1u, &abort_flag)) break;
+                ptx::tc_fence_after_sync();
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * kBN;
+                for (int kb = 0; kb < num_kb; ++kb) {
+                    if (!ptx::mbar_wait(ptx::smem_addr(&bar_full[stage]), phase, &abort_flag)) {
+                        ok = false;
+                        break;
+                    }
+                    ptx::tc_fence_after_sync();
+                    const uint32_t sa = ring + stage * kStageBytes;
+                    const uint64_t da = smem_desc_k_major_sw128(sa);
+                    const uint64_t db = smem_desc_k_major_sw128(sa + kABytes);
+#pragma unroll
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        // advance both start addresses by k * 16 elements * 2 B = 32 B (2 x 16-byte units)
+                        ptx::umma_f16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    ptx::umma_commit(ptx::smem_addr(&bar_empty[stage]));  // stage free once these MMAs retire
+                    if (++stage == kStages) {
+                        stage = 0;
+                        phase ^= 1u;
+                    }
+                }
+                if (ok) ptx::umma_commit(ptx::smem_addr(&bar_tfull[acc]));  // accumulator complete
+                acc ^= 1;
+                if (acc == 0) acc_phase ^= 1u;
+            }
+        }
+    } else {
+        // ---------------- epilogue (warps 2..5) ----------------
+        const int q = warp & 3;  // TMEM lane quarter this warp may read: lanes [32q, 32q+32)
+        int acc = 0;
+        uint32_t acc_phase = 0;
+        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
+            const TileCoord tc = tile_coord(t, m_tiles, kNStep);
+            if (!ptx::mbar_wait(ptx::smem_addr(&bar_tfull[acc]), acc_phase, &abort_flag)) break;
+            ptx::tc_fence_after_sync();
+            const int row = tc.m0 + q * 32 + lane;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * kBN;
+            T* crow = C + static_cast<int64_t>(row) * ldc + tc.n0;
+#pragma unroll 1
+            for (int c = 0; c < kNStep / 32; ++c) {
+                uint32_t out[16];
+                if constexpr (EPI == kEpiSwiglu) {
+                    uint32_t g[32], v[32];
+                    ptx::tmem_ld_32x32(t_row + c * 32, g);
+                    ptx::tmem_ld_32x32(t_row + kBN / 2 + c * 32, v);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j)
+                        out[j] = pack2<T>(silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(v[2 * j])),
+                                          silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(v[2 * j + 1])));
+                } else {
+                    uint32_t a[32];
+                    ptx::tmem_ld_32x32(t_row + c * 32, a);
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 16; ++j) out[j] = pack2<T>(__uint_as_float(a[2 * j]), __uint_as_float(a[2 * j + 1]));
+                }
+                if (row < M) {
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const int col = tc.n0 + c * 32 + j * 8;
+                        if (col < n_out)  // n_out is a multiple of 8: a 16-byte vector is entirely in or out
+                            *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) =
+                                make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+                    }
+                }
+            }
+            ptx::tc_fence_before_sync();
+            __syncwarp();
+            if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&bar_tempty[acc]));
+            acc ^= 1;
+            if (acc == 0) acc_phase ^= 1u;
+        }
+    }
+
+    ptx::tc_fence_before_sync();
+    __syncthreads();
+    if (warp == 1) {
+        ptx::tc_fence_after_sync();
+        ptx::tmem_dealloc(tmem_base, kTmemCols);
+    }
+    if (threadIdx.x == 0 && abort_flag != 0) atomicExch(status, MGR_ERR_DEVICE_TIMEOUT);
+}
+
+// ------------------------------------------------------------------------------------------------
+// Host side
+// ------------------------------------------------------------------------------------------------
+
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*,
+                                   const cuuint64_t*, const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave,
+                                   CUtensorMapSwizzle, CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+
+// cuTensorMapEncodeTiled through the runtime's driver entry-point lookup: the library does not link
+// libcuda, so it still loads (for its host-side checks) on a machine without a driver.
+EncodeTiledFn encode_tiled_fn() {
+    static EncodeTiledFn fn = nullptr;
+    if (fn == nullptr) {
+        void* p = nullptr;
+        cudaDriverEntryPointQueryResult q;
+        if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
+            q != cudaDriverEntryPointSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        fn = reinterpret_cast<EncodeTiledFn>(p);
+    }
+    return fn;
+}
+
+// Tensor map over a row-major [rows, k] matrix of 16-bit elements with leading dimension ld (elements):
+// box = 64 (k) x 128 (rows), 128-byte swizzle, out-of-range elements read as zero.
+bool make_tmap(CUtensorMap* tm, const void* base, int64_t rows, int64_t k, int64_t ld, int dtype) {
+    EncodeTiledFn enc = encode_tiled_fn();
+    if (enc == nullptr) return false;
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
+    const cuuint32_t box[2] = {kBK, 128};
+    const cuuint32_t estr[2] = {1, 1};
+    const CUtensorMapDataType dt = dtype == MGR_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
+    return enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
+               CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_256B, CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) == CUDA_SUCCESS;
+}
+
+int* gemm_status_ptr(const DeviceInfo& di) {
+    static int* cache[kMaxDevices] = {nullptr};
+    if (cache[di.device] == nullptr) {
+        void* p = nullptr;
+        if (cudaGetSymbolAddress(&p, g_gemm_status) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        cache[di.device] = static_cast<int*>(p);
+    }
+    return cache[di.device];
+}
+
+template <int EPI, typename T>
+int launch_gemm(void* c, const void* a, const void* b, int64_t m, int64_t n_out, int64_t k, int64_t lda, int64_t ldb,
+                int64_t ldc, int64_t b_rows, int dtype, const DeviceInfo& di, cudaStream_t s) {
+    static bool attr[kMaxDevices] = {false};
+    if (!attr[di.device]) {
+        if (cudaFuncSetAttribute(gemm_tn_kernel<EPI, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem)) !=
+            cudaSuccess) {
+            (void)cudaGetLastError();
+            return MGR_ERR_CUDA;
+        }
+        attr[di.device] = true;
+    }
+    CUtensorMap tmA, tmB;
+    if (!make_tmap(&tmA, a, m, k, lda, dtype) || !make_tmap(&tmB, b, b_rows, k, ldb, dtype)) return MGR_ERR_CUDA;
+    int* status = gemm_status_ptr(di);
+    if (status == nullptr) return MGR_ERR_CUDA;
+    constexpr int n_step = EPI == kEpiSwiglu ? kBN / 2 : kBN;
+    const int64_t tiles = ((m + kBM - 1) / kBM) * ((n_out + n_step - 1) / n_step);
+    const unsigned grid = static_cast<unsigned>(tiles < di.sm_count ? tiles : di.sm_count);
+    gemm_tn_kernel<EPI, T><<<grid, kGemmThreads, kGemmSmem, s>>>(tmA, tmB, static_cast<T*>(c), static_cast<int>(m),
+                                                                 static_cast<int>(n_out), static_cast<int>(k), ldc, status);
+    return launch_status();
+}
+
+int gemm_check(int64_t m, int64_t n, int64_t k, int dtype) {
+    if (dtype != MGR_F16 && dtype != MGR_BF16) return MGR_ERR_BAD_DTYPE;
+    if (m < 0 || n < 1 || k < 1) return MGR_ERR_BAD_SHAPE;
+    if (n % 8 != 0 || k % 8 != 0) return MGR_ERR_BAD_SHAPE;  // 16-byte rows for TMA and for the vector stores
+    if (m > (1ll << 30) || n > (1ll << 30) || k > (1ll << 30)) return MGR_ERR_TOO_LARGE;
+    return MGR_OK;
+}
+
+}  // namespace
+
+int gemm_status_fetch(int clear) {
+    int v = 0;
+    if (cudaMemcpyFromSymbol(&v, g_gemm_status, sizeof(int)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return MGR_ERR_CUDA;
+    }
+    if (clear && v != 0) {
+        const int zero = 0;
+        if (cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int)) != cudaSuccess) (void)cudaGetLastError();
+    }
+    return v;
+}
+
+}  // namespace mgr
+
+using namespace mgr;
+
+extern "C" int mgr_gemm_tn(void* c, const void* a, const void* b, int64_t m, int64_t n, int64_t k, int64_t lda,
+                           int64_t ldb, int64_t ldc, int dtype, void* stream) {
+    int st = gemm_check(m, n, k, dtype);
+    if (st != MGR_OK) return st;
+    if (lda < k || ldb < k || ldc < n || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) return MGR_ERR_BAD_SHAPE;
+    if (m == 0) return MGR_OK;
+    if (c == nullptr || a == nullptr || b == nullptr) return MGR_ERR_NULL_PTR;
+    if (!aligned_to(c, 16) || !aligned_to(a, 16) || !aligned_to(b, 16)) return MGR_ERR_MISALIGNED;
+    const DeviceInfo di = current_device_info();
+    if (di.status != MGR_OK) return di.status;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == MGR_F16) return launch_gemm<kEpiPlain, __half>(c, a, b, m, n, k, lda, ldb, ldc, n, dtype, di, s);
+    return launch_gemm<kEpiPlain, __nv_bfloat16>(c, a, b, m, n, k, lda, ldb, ldc, n, dtype, di, s);
+}
+
+extern "C" int mgr_swiglu_fused_fwd(void* h, const void* x, const void* w12, int64_t m, int64_t d, int64_t f, int dtype,
+                                    void* stream) {
+    int st = gemm_check(m, f, d, dtype);
+    if (st != MGR_OK) return st;
+    if (m == 0) return MGR_OK;
+    if (h == nullptr || x == nullptr || w12 == nullptr) return MGR_ERR_NULL_PTR;
+    if (!aligned_to(h, 16) || !aligned_to(x, 16) || !aligned_to(w12, 16)) return MGR_ERR_MISALIGNED;
+    const DeviceInfo di = current_device_info();
+    if (di.status != MGR_OK) return di.status;
+    cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (dtype == MGR_F16) return launch_gemm<kEpiSwiglu, __half>(h, x, w12, m, f, d, d, d, f, 2 * f, dtype, di, s);
+    return launch_gemm<kEpiSwiglu, __nv_bfloat16>(h, x, w12, m, f, d, d, d, f, 2 * f, dtype, di, s);
+}

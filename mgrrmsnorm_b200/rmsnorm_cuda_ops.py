@@ -145,3 +145,56 @@ def swiglu_act_backward(grad_out: torch.Tensor, w12_out: torch.Tensor, hidden_di
                                   _stream_ptr(w12_out.device))
     _capi.check("SwiGLU activation backward kernel", st)
     return grad_in
+
+
+def _gemm_ok(*tensors: torch.Tensor) -> bool:
+    """True when the tensor-core kernels can take these operands: CUDA, fp16/bf16, contiguous 2-D with
+    every dimension a multiple of 8 and 16-byte aligned storage."""
+    dt = tensors[0].dtype
+    if dt not in (torch.float16, torch.bfloat16):
+        return False
+    for t in tensors:
+        if not (t.is_cuda and t.dtype == dt and t.dim() == 2 and t.is_contiguous() and t.data_ptr() % 16 == 0):
+            return False
+        if t.shape[0] < 0 or t.shape[1] % 8 != 0:
+            return False
+    return True
+
+
+def swiglu_fused_forward(x: torch.Tensor, w12: torch.Tensor, hidden_dim: int) -> torch.Tensor:
+    """h[M, hidden] = silu(x w12[:hidden]^T) * (x w12[hidden:]^T) in one tensor-core kernel: what
+    `self.w12(x)` followed by MegaGemmFunction computes (megagemm/swiglu.py:167-168), without the
+    [M, 2*hidden] intermediate."""
+    _check_input(x, "x")
+    _check_input(w12, "w12")
+    if x.dim() != 2 or w12.dim() != 2 or w12.shape[0] != 2 * hidden_dim or w12.shape[1] != x.shape[1]:
+        raise RuntimeError("expected x [M, d_model] and w12 [2*hidden_dim, d_model]")
+    if x.dtype != w12.dtype or x.device != w12.device:
+        raise RuntimeError("x and w12 must share dtype and device")
+    code = _dtype_code(x, "")
+    m, d = x.shape
+    L = _capi.lib()
+    with torch.cuda.device(x.device):
+        h = torch.empty((m, hidden_dim), device=x.device, dtype=x.dtype)
+        st = L.mgr_swiglu_fused_fwd(h.data_ptr(), x.data_ptr(), w12.data_ptr(), m, d, hidden_dim, code, _stream_ptr(x.device))
+    _capi.check("fused SwiGLU projection kernel", st)
+    return h
+
+
+def linear_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
+    """a [M, K] x b [N, K]^T -> [M, N] on the tensor-core kernel (an nn.Linear without bias)."""
+    _check_input(a, "a")
+    _check_input(b, "b")
+    if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
+        raise RuntimeError("expected a [M, K] and b [N, K]")
+    if a.dtype != b.dtype or a.device != b.device:
+        raise RuntimeError("a and b must share dtype and device")
+    code = _dtype_code(a, "")
+    m, k = a.shape
+    n = b.shape[0]
+    L = _capi.lib()
+    with torch.cuda.device(a.device):
+        c = torch.empty((m, n), device=a.device, dtype=a.dtype)
+        st = L.mgr_gemm_tn(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, k, k, n, code, _stream_ptr(a.device))
+    _capi.check("tensor-core GEMM kernel", st)
+    return c

@@ -37,6 +37,46 @@ class MegaGemmFunction(Function):
         return grad_input_flat.view(w12_out.shape), None
 
 
+class SwiGLUMLPFunction(Function):
+    """The whole MLP, y = w3(silu(x w1^T) * (x w2^T)), on the tensor-core kernels.
+
+    Forward: one fused kernel produces h = silu(gate) * value straight from the accumulators (the
+    [M, 2*hidden] projection the reference materialises between megagemm/swiglu.py:167 and :168 never
+    exists), then the w3 GEMM. Saved for backward: x, the weights and h -- not the projection, which
+    backward recomputes.
+    Backward follows the reference's autograd graph (Linear(w3) -> MegaGemmFunction -> Linear(w12)):
+    dh = dy w3, dW3 = dy^T h, [d_gate | d_val] from the recomputed projection and dh, dx = dGV w12,
+    dW12 = dGV^T x.
+    """
+
+    @staticmethod
+    def forward(ctx, x: torch.Tensor, w12: torch.Tensor, w3: torch.Tensor):
+        hidden = w3.shape[1]
+        x2d = x.reshape(-1, x.shape[-1])
+        if not x2d.is_contiguous():
+            x2d = x2d.contiguous()
+        h = rmsnorm_cuda_ops.swiglu_fused_forward(x2d, w12, hidden)
+        y = rmsnorm_cuda_ops.linear_tn(h, w3)
+        ctx.save_for_backward(x2d, w12, w3, h)
+        ctx.x_shape = x.shape
+        return y.view(x.shape[:-1] + (w3.shape[0],))
+
+    @staticmethod
+    def backward(ctx, grad_output: torch.Tensor):
+        x2d, w12, w3, h = ctx.saved_tensors
+        hidden = w3.shape[1]
+        dy = grad_output.reshape(-1, grad_output.shape[-1])
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+        dh = torch.matmul(dy, w3)                       # [M, hidden]
+        dw3 = torch.matmul(dy.t(), h) if ctx.needs_input_grad[2] else None
+        gv = torch.nn.functional.linear(x2d, w12)       # recomputed projection [M, 2*hidden]
+        dgv = rmsnorm_cuda_ops.swiglu_act_backward(dh, gv, hidden)
+        dx = torch.matmul(dgv, w12).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+        dw12 = torch.matmul(dgv.t(), x2d) if ctx.needs_input_grad[1] else None
+        return dx, dw12, dw3
+
+
 class MegaGemmTriton(nn.Module):
     """SwiGLU MLP: y = w3( silu(x w1^T) * (x w2^T) ), w1|w2 stacked in `w12`.
 
@@ -54,6 +94,12 @@ class MegaGemmTriton(nn.Module):
         self.w3 = nn.Linear(hidden, d_model, bias=False)
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w12, w3 = self.w12.weight, self.w3.weight
+        if x.is_cuda and x.dtype == w12.dtype and x.numel() > 0 and x.shape[-1] % 8 == 0 and \
+                rmsnorm_cuda_ops._gemm_ok(w12, w3):
+            return SwiGLUMLPFunction.apply(x, w12, w3)
+        # fp32 modules and shapes the tensor-core kernels do not take keep the reference's own
+        # structure (megagemm/swiglu.py:166-169): library GEMM, activation kernel, library GEMM.
         w12_out = self.w12(x)
         hidden = MegaGemmFunction.apply(w12_out, self.hidden)
         return self.w3(hidden)

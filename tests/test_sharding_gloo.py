@@ -1,0 +1,127 @@
+"""Host-side logic of the multi-GPU wrappers on CPU: index arithmetic, and the collectives run as two
+gloo ranks. The CUDA compute they wrap is covered by the GPU tests; here the per-shard arithmetic is
+done by the oracle so that the partitioning itself is what is checked."""
+import os
+import socket
+
+import numpy as np
+import pytest
+import torch
+import torch.distributed as dist
+import torch.multiprocessing as mp
+
+from mgrrmsnorm_b200 import sharding
+from oracle import oracle
+
+
+def test_row_shard_covers_all_rows_once():
+    for rows in (0, 1, 7, 65536, 65537, 100003):
+        for world in (1, 2, 3, 4, 8):
+            spans = [sharding.row_shard(rows, world, r) for r in range(world)]
+            assert spans[0][0] == 0 and spans[-1][1] == rows
+            assert all(a[1] == b[0] for a, b in zip(spans, spans[1:]))
+            sizes = [b - a for a, b in spans]
+            assert max(sizes) - min(sizes) <= 1
+    assert sharding.row_shard(65536, 8, 3) == (24576, 32768)
+    with pytest.raises(ValueError):
+        sharding.row_shard(8, 2, 2)
+
+
+def test_tp_weight_shards_roundtrip_and_layout():
+    d, f = 16, 24
+    w12 = torch.arange(2 * f * d, dtype=torch.float32).view(2 * f, d)
+    w3 = torch.arange(d * f, dtype=torch.float32).view(d, f)
+    for world in (1, 2, 4):
+        s12 = [sharding.tp_shard_w12(w12, world, r) for r in range(world)]
+        s3 = [sharding.tp_shard_w3(w3, world, r) for r in range(world)]
+        per = f // world
+        for r in range(world):
+            assert s12[r].shape == (2 * per, d) and s3[r].shape == (d, per)
+            assert torch.equal(s12[r][:per], w12[r * per:(r + 1) * per])                 # gate rows of this rank
+            assert torch.equal(s12[r][per:], w12[f + r * per:f + (r + 1) * per])         # value rows of this rank
+        assert torch.equal(sharding.tp_unshard_w12(s12), w12)
+        assert torch.equal(sharding.tp_unshard_w3(s3), w3)
+    with pytest.raises(ValueError):
+        sharding.tp_hidden_slice(10, 4, 0)
+    # the configuration sizes: d_ff 28672 over 2/4/8 ranks
+    assert [sharding.tp_hidden_slice(28672, p, p - 1) for p in (2, 4, 8)] == [(14336, 28672), (21504, 28672), (25088, 28672)]
+
+
+def test_partial_sums_of_tp_shards_equal_the_full_mlp():
+    """sum over ranks of w3_r( silu(x Wg_r^T) * (x Wv_r^T) ) == the unsharded MLP (oracle arithmetic)."""
+    rng = np.random.default_rng(0)
+    m, d, f = 6, 16, 24
+    x = rng.standard_normal((m, d)).astype(np.float32)
+    w12 = (rng.standard_normal((2 * f, d)) / 4).astype(np.float32)
+    w3 = (rng.standard_normal((d, f)) / 4).astype(np.float32)
+    dy = rng.standard_normal((m, d)).astype(np.float32)
+    full = oracle.swiglu_mlp(x, w12, w3, dy=dy)
+    for world in (2, 4):
+        y = np.zeros((m, d))
+        dx = np.zeros((m, d))
+        dw12, dw3 = [], []
+        for r in range(world):
+            o = oracle.swiglu_mlp(x, sharding.tp_shard_w12(torch.from_numpy(w12), world, r).numpy(),
+                                  sharding.tp_shard_w3(torch.from_numpy(w3), world, r).numpy(), dy=dy)
+            y += o["y"]
+            dx += o["dx"]
+            dw12.append(torch.from_numpy(o["dw12"]))
+            dw3.append(torch.from_numpy(o["dw3"]))
+        np.testing.assert_allclose(y, full["y"], rtol=1e-12, atol=1e-12)
+        np.testing.assert_allclose(dx, full["dx"], rtol=1e-12, atol=1e-12)
+        np.testing.assert_allclose(sharding.tp_unshard_w12(dw12).numpy(), full["dw12"], rtol=1e-12, atol=1e-12)
+        np.testing.assert_allclose(sharding.tp_unshard_w3(dw3).numpy(), full["dw3"], rtol=1e-12, atol=1e-12)
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _gloo_worker(rank: int, world: int, port: int, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        rows, cols = 10, 8
+        rng = np.random.default_rng(5)
+        x = rng.standard_normal((rows, cols)).astype(np.float32)
+        w = (1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+        dy = rng.standard_normal((rows, cols)).astype(np.float32)
+        r0, r1 = sharding.row_shard(rows, world, rank)
+        # each rank's fp32 dW partial over its own rows (oracle arithmetic), summed across ranks
+        _, dw_local = oracle.rmsnorm_bwd(dy[r0:r1], x[r0:r1], w, 1e-6)
+        dw = sharding.allreduce_dw(torch.from_numpy(dw_local.astype(np.float32)), torch.bfloat16)
+        _, dw_full = oracle.rmsnorm_bwd(dy, x, w, 1e-6)
+        ok_dw = dw.dtype == torch.bfloat16 and np.allclose(dw.float().numpy(), dw_full, rtol=1e-2, atol=1e-2)
+        with pytest.raises(TypeError):
+            sharding.allreduce_dw(torch.zeros(4, dtype=torch.float16), torch.float16)
+
+        # forward-reduce / backward-reduce pair around a rank-local linear map
+        t = torch.full((3,), float(rank + 1), requires_grad=True)
+        a = sharding._ReduceBackward.apply(t, None)
+        out = sharding._ReduceForward.apply(a * (rank + 1), None)
+        out.sum().backward()
+        total = sum((r + 1) ** 2 for r in range(world))
+        ok_fwd = torch.allclose(out, torch.full((3,), float(total)))
+        # d(out_sum)/dt on this rank is (rank+1); the backward all-reduce sums that over ranks
+        ok_bwd = torch.allclose(t.grad, torch.full((3,), float(sum(r + 1 for r in range(world)))))
+        q.put((rank, bool(ok_dw), bool(ok_fwd), bool(ok_bwd)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_collectives_on_two_gloo_ranks():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_gloo_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(r[0] for r in results) == [0, 1]
+    assert all(r[1] and r[2] and r[3] for r in results), results

@@ -1,0 +1,166 @@
+"""SwiGLU MLP on the tensor-core kernels: the tcgen05 GEMM against exact references on structured
+inputs and against the fp64 oracle on random ones; the whole module against the oracle and the golden
+vectors of the reference module."""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests.util import TORCH_DTYPES, to_np
+
+pytestmark = pytest.mark.gpu
+
+
+@pytest.fixture(scope="module")
+def ops(built_lib):
+    import rmsnorm_cuda_ops
+
+    return rmsnorm_cuda_ops
+
+
+def gemm_tolerance(k: int, dtype: str, scale: float) -> float:
+    """fp32 accumulation of K products of 16-bit inputs, one rounding to the 16-bit output."""
+    half_ulp = 2.0 ** (-11 if dtype == "f16" else -8)
+    return scale * (half_ulp + 4e-7 * k ** 0.5) + 1e-6
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("m,n,k", [(128, 256, 64), (128, 256, 256), (256, 512, 128), (100, 40, 72), (384, 264, 4096),
+                                    (1, 8, 8), (300, 1000, 520)])
+def test_gemm_integer_inputs_are_exact(ops, built_lib, dtype, m, n, k):
+    """Small-integer operands: every product and partial sum is exactly representable, so any tile,
+    swizzle or descriptor error shows up as a wrong integer, and the right answer has zero error."""
+    g = torch.Generator().manual_seed(m + n + k)
+    td = TORCH_DTYPES[dtype]
+    a = torch.randint(-2, 3, (m, k), generator=g).to(td)
+    b = torch.randint(-2, 3, (n, k), generator=g).to(td)
+    c = ops.linear_tn(a.cuda(), b.cuda())
+    torch.cuda.synchronize()
+    want = a.double() @ b.double().t()
+    assert float(want.abs().max()) <= 256      # exactly representable in bf16 as well
+    assert torch.equal(c.cpu().double(), want)
+    assert built_lib.mgr_device_status(1) == 0
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_gemm_identity_and_one_hot(ops, dtype):
+    """B = identity copies A; a one-hot B row picks one column of A: exact, and position-revealing."""
+    td = TORCH_DTYPES[dtype]
+    g = torch.Generator().manual_seed(3)
+    a = torch.randn(200, 512, generator=g).to(td)
+    eye = torch.eye(512).to(td)
+    assert torch.equal(ops.linear_tn(a.cuda(), eye.cuda()).cpu(), a)
+    perm = torch.randperm(512, generator=g)
+    assert torch.equal(ops.linear_tn(a.cuda(), eye[perm].cuda()).cpu(), a[:, perm])
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("m,n,k", [(256, 512, 1024), (520, 264, 4096), (4096, 512, 6912)])
+def test_gemm_random_matches_oracle(ops, dtype, m, n, k):
+    g = torch.Generator().manual_seed(k)
+    td = TORCH_DTYPES[dtype]
+    a = torch.randn(m, k, generator=g).to(td)
+    b = (torch.randn(n, k, generator=g) / k ** 0.5).to(td)
+    c = to_np(ops.linear_tn(a.cuda(), b.cuda())).astype(np.float64)
+    want = oracle.linear(to_np(a), to_np(b))
+    err = np.abs(c - want)
+    assert float(err.max()) <= gemm_tolerance(k, dtype, float(np.abs(want).max())), float(err.max())
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("m,d,f", [(128, 64, 128), (200, 256, 384), (64, 72, 40), (1024, 4096, 6912), (300, 512, 1000)])
+def test_fused_projection_matches_oracle(ops, built_lib, dtype, m, d, f):
+    """h = silu(x Wg^T) * (x Wv^T): the fused epilogue against the fp64 formulas (megagemm/swiglu.py:35-41)."""
+    g = torch.Generator().manual_seed(m + d + f)
+    td = TORCH_DTYPES[dtype]
+    x = torch.randn(m, d, generator=g).to(td)
+    w12 = (torch.randn(2 * f, d, generator=g) / d ** 0.5).to(td)
+    h = to_np(ops.swiglu_fused_forward(x.cuda(), w12.cuda(), f)).astype(np.float64)
+    gv = oracle.linear(to_np(x), to_np(w12))
+    want = oracle.swiglu_act_fwd(gv, f)
+    err = np.abs(h - want)
+    assert float(err.max()) <= gemm_tolerance(d, dtype, float(np.abs(want).max())) + 1e-5, float(err.max())
+    assert built_lib.mgr_device_status(1) == 0
+
+
+def test_fused_projection_gate_value_layout(ops):
+    """Gate rows are w12[:F], value rows w12[F:] (benchmark_swiglu.py:85-89). With value weights that
+    make val == 1 the output is silu(gate); swapping the halves must change it."""
+    f, d, m = 256, 128, 128
+    x = torch.zeros(m, d)
+    x[:, 0] = 1.0
+    x[:, 1] = torch.linspace(-4, 4, m)
+    w12 = torch.zeros(2 * f, d)
+    w12[:f, 1] = 1.0        # gate = x[:, 1]
+    w12[f:, 0] = 1.0        # value = 1
+    h = ops.swiglu_fused_forward(x.half().cuda(), w12.half().cuda(), f).float().cpu()
+    gate = x[:, 1].half().float()
+    want = (gate * torch.sigmoid(gate)).half().float()
+    assert torch.allclose(h, want[:, None].expand(m, f), atol=2e-3, rtol=2e-3)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_module_forward_backward_matches_oracle(dtype):
+    from megagemm import MegaGemmTriton
+
+    td = TORCH_DTYPES[dtype]
+    torch.manual_seed(7)
+    mlp = MegaGemmTriton(512, multiple_of=128).cuda().to(td)      # hidden 896
+    g = torch.Generator().manual_seed(8)
+    x = torch.randn(4, 96, 512, generator=g).to(td)
+    dy = torch.randn(4, 96, 512, generator=g).to(td)
+    xin = x.cuda().requires_grad_(True)
+    y = mlp(xin)
+    y.backward(dy.cuda())
+    torch.cuda.synchronize()
+    out = oracle.swiglu_mlp(to_np(x).reshape(-1, 512), to_np(mlp.w12.weight), to_np(mlp.w3.weight), dy=to_np(dy).reshape(-1, 512))
+    # fp16/bf16 MLP against the fp64 truth: 1e-2 max-abs (the bound the reference's own check uses,
+    # benchmark_swiglu.py:121-129); weight gradients sum 384 rows and are held to their own scale
+    for got, key in ((y.view(-1, 512), "y"), (xin.grad.view(-1, 512), "dx")):
+        assert float(np.abs(to_np(got) - out[key]).max()) < 1e-2, key
+    for got, key in ((mlp.w12.weight.grad, "dw12"), (mlp.w3.weight.grad, "dw3")):
+        err = float(np.abs(to_np(got) - out[key]).max())
+        assert err < 1e-2 * max(1.0, float(np.abs(out[key]).max())), (key, err)
+
+
+def test_module_matches_reference_module_vectors(golden_dir):
+    """The fp32 fixture of the reference's MegaGemmTriton (d_model 64, hidden 128), run here in fp16:
+    within the reference benchmark's own 1e-2 check of the fp32 outputs."""
+    from megagemm import MegaGemmTriton
+
+    g = np.load(golden_dir / "swiglu.npz")
+    mlp = MegaGemmTriton(64, multiple_of=32)
+    mlp.load_state_dict({"w12.weight": torch.from_numpy(g["mlp_w12"]), "w3.weight": torch.from_numpy(g["mlp_w3"])})
+    mlp = mlp.cuda().half()
+    x = torch.from_numpy(g["mlp_x"]).half().cuda().requires_grad_(True)
+    y = mlp(x)
+    y.backward(torch.from_numpy(g["mlp_dy"]).half().cuda())
+    assert float((y.float().cpu() - torch.from_numpy(g["mlp_y"])).abs().max()) < 1e-2
+    assert float((x.grad.float().cpu() - torch.from_numpy(g["mlp_dx"])).abs().max()) < 1e-2
+    assert float((mlp.w12.weight.grad.float().cpu() - torch.from_numpy(g["mlp_dw12"])).abs().max()) < 2e-2
+    assert float((mlp.w3.weight.grad.float().cpu() - torch.from_numpy(g["mlp_dw3"])).abs().max()) < 2e-2
+
+
+def test_fp32_module_keeps_the_reference_structure():
+    from megagemm import MegaGemmTriton
+
+    torch.manual_seed(1)
+    mlp = MegaGemmTriton(64, multiple_of=32).cuda()
+    x = torch.randn(10, 64, device="cuda", requires_grad=True)
+    y = mlp(x)
+    y.sum().backward()
+    out = oracle.swiglu_mlp(to_np(x), to_np(mlp.w12.weight), to_np(mlp.w3.weight))
+    assert float(np.abs(to_np(y) - out["y"]).max()) < 1e-3    # TF32-capable library GEMMs in fp32 mode
+
+
+def test_gemm_argument_errors(built_lib):
+    from mgrrmsnorm_b200 import _capi
+
+    P = 0x10000
+    assert built_lib.mgr_gemm_tn(P, P, P, 8, 8, 8, 8, 8, 8, _capi.MGR_F32, None) == _capi.MGR_ERR_BAD_DTYPE
+    assert built_lib.mgr_gemm_tn(P, P, P, 8, 7, 8, 8, 8, 8, _capi.MGR_F16, None) == _capi.MGR_ERR_BAD_SHAPE
+    assert built_lib.mgr_gemm_tn(P, P, P, 8, 8, 8, 4, 8, 8, _capi.MGR_F16, None) == _capi.MGR_ERR_BAD_SHAPE
+    assert built_lib.mgr_gemm_tn(None, P, P, 8, 8, 8, 8, 8, 8, _capi.MGR_F16, None) == _capi.MGR_ERR_NULL_PTR
+    assert built_lib.mgr_gemm_tn(P + 2, P, P, 8, 8, 8, 8, 8, 8, _capi.MGR_F16, None) == _capi.MGR_ERR_MISALIGNED
+    assert built_lib.mgr_swiglu_fused_fwd(P, P, P, 8, 12, 8, _capi.MGR_BF16, None) == _capi.MGR_ERR_BAD_SHAPE
+    assert built_lib.mgr_swiglu_fused_fwd(P, P, P, 0, 8, 8, _capi.MGR_BF16, None) == _capi.MGR_OK
