@@ -149,6 +149,29 @@ int mgr_swiglu_fused_fwd(void* h, const void* x, const void* w12, int64_t m, int
 int mgr_gemm_tn(void* c, const void* a, const void* b, int64_t m, int64_t n, int64_t k,
                 int64_t lda, int64_t ldb, int64_t ldc, int dtype, void* stream);
 
+/* The backward GEMMs of the MLP. The reference gets them from autograd of its two nn.Linear layers
+ * (Linear(w3).backward and Linear(w12).backward, implicit after megagemm/swiglu.py:167,169) and its
+ * Triton backward kernel (megagemm/swiglu.py:111-131); here they are the same tensor-core kernel family.
+ *
+ * mgr_gemm: c[m, n] = round_dtype( op(a) op(b)^T ) where each operand is stored either K-major
+ *   (a: [m, k] row-major, b: [n, k] row-major; *_mn_major = 0) or MN-major (a: [k, m] row-major,
+ *   b: [k, n] row-major; *_mn_major = 1). lda / ldb are the row pitches of the stored matrices in
+ *   elements. So, with dy [M, D], h [M, F], dgv [M, 2F], x [M, D], w3 [D, F], w12 [2F, D]:
+ *     dh   = dy w3       : mgr_gemm(dh,   dy,  w3,  M,  F, D,  ..., 0, 1)
+ *     dw3  = dy^T h      : mgr_gemm(dw3,  dy,  h,   D,  F, M,  ..., 1, 1)
+ *     dx   = dgv w12     : mgr_gemm(dx,   dgv, w12, M,  D, 2F, ..., 0, 1)
+ *     dw12 = dgv^T x     : mgr_gemm(dw12, dgv, x,   2F, D, M,  ..., 1, 1)
+ *   No operand is ever transposed in memory. m (for an MN-major a), n and k multiples of 8.
+ * mgr_swiglu_fused_bwd: dgv[m, 2f] = [d_gate | d_val] from dh[m, f], recomputing the projection
+ *   x w12^T tile by tile in TMEM (it is not stored by the forward):
+ *     d_val = dh*gate*sig(gate),  d_gate = dh*val*sig(gate)*(1 + gate*(1 - sig(gate)))
+ *   i.e. `w12(x)` recomputed + _mg_swiglu_bwd_kernel (megagemm/swiglu.py:46-79) in one kernel.
+ */
+int mgr_gemm(void* c, const void* a, const void* b, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+             int64_t ldc, int a_mn_major, int b_mn_major, int dtype, void* stream);
+int mgr_swiglu_fused_bwd(void* dgv, const void* dh, const void* x, const void* w12, int64_t m, int64_t d, int64_t f,
+                         int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

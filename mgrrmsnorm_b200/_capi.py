@@ -45,6 +45,8 @@ SIGNATURES = {
     "mgr_swiglu_act_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp]),
     "mgr_swiglu_fused_fwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "mgr_gemm_tn": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _int, _vp]),
+    "mgr_gemm": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _vp]),
+    "mgr_swiglu_fused_bwd": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
 }
 
 

@@ -6,7 +6,13 @@
 //   * mgr_swiglu_fused_fwd : h = silu(x Wg^T) * (x Wv^T) in ONE kernel; each CTA tile owns 128 gate
 //     columns and the matching 128 value columns (two B boxes of w12: rows n0.. and F+n0..), so the
 //     [M, 2F] projection never reaches HBM;
-//   * mgr_gemm_tn          : C = A B^T (nn.Linear without bias), used for w3(h).
+//   * mgr_gemm_tn          : C = A B^T (nn.Linear without bias), used for w3(h);
+// and the four GEMMs autograd runs for the two nn.Linear layers in backward plus the Triton backward
+// kernel (megagemm/swiglu.py:111-131):
+//   * mgr_gemm              : C = op(A) op(B)^T with either operand stored K-major or MN-major, which
+//     covers dh = dy W3, dW3 = dy^T h, dx = dGV W12 and dW12 = dGV^T x without any transposed copy;
+//   * mgr_swiglu_fused_bwd  : recomputes the projection tile by tile and turns it, with the matching
+//     dh tile, into [d_gate | d_val] in the epilogue -- the projection is not stored in forward.
 //
 // Kernel shape (one CTA per SM, persistent over output tiles, 192 threads):
 //   warp 0    : TMA producer  -- cp.async.bulk.tensor.2d into a 4-stage ring (A 128x64, B 256x64, 128B swizzle)
@@ -40,30 +46,39 @@ constexpr uint32_t kGemmSmem = kStages * kStageBytes + 1024;  // + slack to alig
 constexpr int kGemmThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 
-enum Epilogue { kEpiPlain = 0, kEpiSwiglu = 1 };
+enum Epilogue { kEpiPlain = 0, kEpiSwiglu = 1, kEpiSwigluBwd = 2 };
 
-// Shared-memory matrix descriptor for a K-major operand tile stored as rows of 128 bytes with the
-// 128-byte swizzle (what TMA writes with CU_TENSOR_MAP_SWIZZLE_128B): 8-row groups are 1024 B apart
-// (stride byte offset), leading byte offset is unused for swizzled K-major layouts (encoded 1),
-// descriptor version 1 (sm_100), layout type 2 (SWIZZLE_128B). Addresses are in 16-byte units.
-__device__ __forceinline__ uint64_t smem_desc_k_major_sw128(uint32_t smem_addr) {
+// Shared-memory matrix descriptors (64-bit, addresses in 16-byte units): start address [0,14),
+// leading byte offset [16,30), stride byte offset [32,46), descriptor version 1 at [46,48) (sm_100),
+// layout type 2 = SWIZZLE_128B at [61,64). Both operand layouts are what TMA writes with
+// CU_TENSOR_MAP_SWIZZLE_128B: rows of 128 bytes, swizzled in 1024-byte groups of 8 rows.
+//   K-major  (operand stored [rows, K]):  a smem row is one operand row, 64 K-elements. 8-row groups are
+//            1024 B apart (stride offset); the leading offset is unused for swizzled K-major (encoded 1).
+//            The next K=16 slice starts 32 B further along the row.
+//   MN-major (operand stored [K, rows]):  a smem row is one K index, 64 consecutive operand rows. The tile
+//            is a sequence of 64-row chunks, each [64 K x 128 B] = 8192 B: leading offset = 8192 B between
+//            chunks, stride offset = 1024 B between groups of 8 K indices. The next K=16 slice starts
+//            16 rows = 2048 B further.
+__device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr, bool mn_major) {
     uint64_t d = 0;
     d |= static_cast<uint64_t>((smem_addr >> 4) & 0x3FFFu);
-    d |= static_cast<uint64_t>(1) << 16;
+    d |= static_cast<uint64_t>(mn_major ? (8192 >> 4) : 1) << 16;
     d |= static_cast<uint64_t>(1024 >> 4) << 32;
     d |= static_cast<uint64_t>(1) << 46;
     d |= static_cast<uint64_t>(2) << 61;
     return d;
 }
 
-// Instruction descriptor, kind::f16: fp32 accumulator, A and B both K-major, M=128, N=256.
-// `fmt` = 0 for fp16 operands, 1 for bf16.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt) {
-    return (1u << 4) | (fmt << 7) | (fmt << 10) | (static_cast<uint32_t>(kBN >> 3) << 17) |
-           (static_cast<uint32_t>(kBM >> 4) << 24);
+// Instruction descriptor, kind::f16: fp32 accumulator (bits [4,6) = 1), operand formats at [7,10) and
+// [10,13) (0 = fp16, 1 = bf16), A / B major-ness at bits 15 / 16 (1 = MN-major), N>>3 at [17,23),
+// M>>4 at [24,29). M=128, N=256.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, bool a_mn, bool b_mn) {
+    return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u) |
+           (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
 }
 
-__device__ __forceinline__ float silu_mul(float g, float v) { return (g * (1.0f / (1.0f + __expf(-g)))) * v; }
+__device__ __forceinline__ float sigmoid_(float g) { return 1.0f / (1.0f + __expf(-g)); }
+__device__ __forceinline__ float silu_mul(float g, float v) { return (g * sigmoid_(g)) * v; }
 
 template <typename T> __device__ __forceinline__ uint32_t pack2(float a, float b);
 template <> __device__ __forceinline__ uint32_t pack2<__half>(float a, float b) {
@@ -84,15 +99,20 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_step) 
     return TileCoord{(t % m_tiles) * kBM, (t / m_tiles) * n_step};
 }
 
-// A: [M, K] row-major (tmA, box 64 x 128). B: [Nb, K] row-major (tmB, box 64 x 128).
-// kEpiPlain : C[M, n_out] = A B^T; a tile covers 256 columns of C (B rows n0 .. n0+255).
-// kEpiSwiglu: C[M, n_out] = silu(A Bg^T) * (A Bv^T) with Bg = B rows [0, n_out), Bv = B rows
-//             [n_out, 2 n_out); a tile covers 128 columns of C (B rows n0.. and n_out+n0..).
-template <int EPI, typename T>
+// C = op(A) op(B)^T on one 128 x 256 accumulator tile per step.
+//   A: K-major = stored [M, K] (tmA box 64(K) x 128);  MN-major = stored [K, M] (tmA box 64(M) x 64(K)).
+//   B: K-major = stored [Nb, K] (tmB box 64(K) x 128); MN-major = stored [K, Nb] (tmB box 64(N) x 64(K)).
+// kEpiPlain    : C[M, n_out] = acc; a tile covers 256 columns of C (B rows n0 .. n0+255).
+// kEpiSwiglu   : B K-major = [gate rows | value rows] of n_out rows each. C[M, n_out] = silu(G) * V; a tile
+//                covers 128 columns of C (B rows n0.. and n_out+n0..).
+// kEpiSwigluBwd: same tile; aux = dh [M, n_out]. C = [d_gate | d_val] of shape [M, 2 n_out]:
+//                d_val = dh * G * sig(G), d_gate = dh * V * sig(G) * (1 + G * (1 - sig(G))).
+template <int EPI, bool A_MN, bool B_MN, typename T>
 __global__ void __launch_bounds__(kGemmThreads, 1)
-gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, T* __restrict__ C,
-               int M, int n_out, int K, int64_t ldc, int* __restrict__ status) {
-    constexpr int kNStep = EPI == kEpiSwiglu ? kBN / 2 : kBN;  // output columns per tile
+gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, T* __restrict__ C,
+            const T* __restrict__ aux, int M, int n_out, int K, int64_t ldc, int64_t ld_aux, int* __restrict__ status) {
+    static_assert(EPI == kEpiPlain || !B_MN, "the gate/value split reads w12 K-major");
+    constexpr int kNStep = EPI == kEpiPlain ? kBN : kBN / 2;  // output columns per tile
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_tfull[2], bar_tempty[2];
     __shared__ uint32_t tmem_base_slot;
@@ -136,7 +156,7 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             bool ok = true;
             for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
                 const TileCoord tc = tile_coord(t, m_tiles, kNStep);
-                const int b_row1 = EPI == kEpiSwiglu ? n_out + tc.n0 : tc.n0 + kBN / 2;
+                const int b_row1 = EPI == kEpiPlain ? tc.n0 + kBN / 2 : n_out + tc.n0;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(ptx::smem_addr(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
                         ok = false;
@@ -145,10 +165,21 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     const uint32_t full = ptx::smem_addr(&bar_full[stage]);
                     const uint32_t sa = ring + stage * kStageBytes;
                     const uint32_t sb = sa + kABytes;
+                    const int k0 = kb * kBK;
                     ptx::mbar_arrive_expect_tx(full, kStageBytes);
-                    ptx::tma_load_2d(sa, &tmA, kb * kBK, tc.m0, full);
-                    ptx::tma_load_2d(sb, &tmB, kb * kBK, tc.n0, full);
-                    ptx::tma_load_2d(sb + kBBytes / 2, &tmB, kb * kBK, b_row1, full);
+                    if constexpr (!A_MN) {
+                        ptx::tma_load_2d(sa, &tmA, k0, tc.m0, full);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < kBM / 64; ++c) ptx::tma_load_2d(sa + c * 8192u, &tmA, tc.m0 + 64 * c, k0, full);
+                    }
+                    if constexpr (!B_MN) {
+                        ptx::tma_load_2d(sb, &tmB, k0, tc.n0, full);
+                        ptx::tma_load_2d(sb + kBBytes / 2, &tmB, k0, b_row1, full);
+                    } else {
+#pragma unroll
+                        for (int c = 0; c < kBN / 64; ++c) ptx::tma_load_2d(sb + c * 8192u, &tmB, tc.n0 + 64 * c, k0, full);
+                    }
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
@@ -159,7 +190,9 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (ptx::elect_one()) {
-            constexpr uint32_t idesc = instr_desc(sizeof(T) == 2 && std::is_same<T, __nv_bfloat16>::value ? 1u : 0u);
+            constexpr uint32_t idesc = instr_desc(std::is_same<T, __nv_bfloat16>::value ? 1u : 0u, A_MN, B_MN);
+            constexpr uint32_t a_step = A_MN ? (2048u >> 4) : (32u >> 4);  // start-address step per K=16 slice
+            constexpr uint32_t b_step = B_MN ? (2048u >> 4) : (32u >> 4);
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
@@ -174,13 +207,11 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
                     }
                     ptx::tc_fence_after_sync();
                     const uint32_t sa = ring + stage * kStageBytes;
-                    const uint64_t da = smem_desc_k_major_sw128(sa);
-                    const uint64_t db = smem_desc_k_major_sw128(sa + kABytes);
+                    const uint64_t da = smem_desc_sw128(sa, A_MN);
+                    const uint64_t db = smem_desc_sw128(sa + kABytes, B_MN);
 #pragma unroll
-                    for (int k = 0; k < kBK / kUmmaK; ++k) {
-                        // advance both start addresses by k * 16 elements * 2 B = 32 B (2 x 16-byte units)
-                        ptx::umma_f16(d_tmem, da + 2u * k, db + 2u * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                    }
+                    for (int k = 0; k < kBK / kUmmaK; ++k)
+                        ptx::umma_f16(d_tmem, da + a_step * k, db + b_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
                     ptx::umma_commit(ptx::smem_addr(&bar_empty[stage]));  // stage free once these MMAs retire
                     if (++stage == kStages) {
                         stage = 0;
@@ -206,30 +237,75 @@ gemm_tn_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ 
             T* crow = C + static_cast<int64_t>(row) * ldc + tc.n0;
 #pragma unroll 1
             for (int c = 0; c < kNStep / 32; ++c) {
-                uint32_t out[16];
-                if constexpr (EPI == kEpiSwiglu) {
+                if constexpr (EPI == kEpiSwigluBwd) {
                     uint32_t g[32], v[32];
                     ptx::tmem_ld_32x32(t_row + c * 32, g);
                     ptx::tmem_ld_32x32(t_row + kBN / 2 + c * 32, v);
-                    ptx::tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j)
-                        out[j] = pack2<T>(silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(v[2 * j])),
-                                          silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(v[2 * j + 1])));
-                } else {
-                    uint32_t a[32];
-                    ptx::tmem_ld_32x32(t_row + c * 32, a);
-                    ptx::tmem_ld_wait();
-#pragma unroll
-                    for (int j = 0; j < 16; ++j) out[j] = pack2<T>(__uint_as_float(a[2 * j]), __uint_as_float(a[2 * j + 1]));
-                }
-                if (row < M) {
+                    uint4 dhp[4];
+                    const T* arow = aux + static_cast<int64_t>(row) * ld_aux + tc.n0 + c * 32;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const int col = tc.n0 + c * 32 + j * 8;
-                        if (col < n_out)  // n_out is a multiple of 8: a 16-byte vector is entirely in or out
-                            *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) =
-                                make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+                        const bool on = row < M && tc.n0 + c * 32 + j * 8 < n_out;
+                        dhp[j] = on ? *reinterpret_cast<const uint4*>(arow + j * 8) : make_uint4(0, 0, 0, 0);
+                    }
+                    ptx::tmem_ld_wait();
+                    uint32_t og[16], ov[16];
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float dh[8];
+                        unpack16<T>(dhp[j], dh);
+#pragma unroll
+                        for (int e = 0; e < 8; e += 2) {
+                            float dg2[2], dv2[2];
+#pragma unroll
+                            for (int u = 0; u < 2; ++u) {
+                                const float gg = __uint_as_float(g[j * 8 + e + u]), vv = __uint_as_float(v[j * 8 + e + u]);
+                                const float sig = sigmoid_(gg);
+                                dv2[u] = dh[e + u] * (gg * sig);
+                                dg2[u] = dh[e + u] * vv * (sig * (1.0f + gg * (1.0f - sig)));
+                            }
+                            og[j * 4 + e / 2] = pack2<T>(dg2[0], dg2[1]);
+                            ov[j * 4 + e / 2] = pack2<T>(dv2[0], dv2[1]);
+                        }
+                    }
+                    if (row < M) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int col = tc.n0 + c * 32 + j * 8;
+                            if (col < n_out) {
+                                *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) =
+                                    make_uint4(og[4 * j], og[4 * j + 1], og[4 * j + 2], og[4 * j + 3]);
+                                *reinterpret_cast<uint4*>(crow + n_out + c * 32 + j * 8) =
+                                    make_uint4(ov[4 * j], ov[4 * j + 1], ov[4 * j + 2], ov[4 * j + 3]);
+                            }
+                        }
+                    }
+                } else {
+                    uint32_t out[16];
+                    if constexpr (EPI == kEpiSwiglu) {
+                        uint32_t g[32], v[32];
+                        ptx::tmem_ld_32x32(t_row + c * 32, g);
+                        ptx::tmem_ld_32x32(t_row + kBN / 2 + c * 32, v);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j)
+                            out[j] = pack2<T>(silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(v[2 * j])),
+                                              silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(v[2 * j + 1])));
+                    } else {
+                        uint32_t a[32];
+                        ptx::tmem_ld_32x32(t_row + c * 32, a);
+                        ptx::tmem_ld_wait();
+#pragma unroll
+                        for (int j = 0; j < 16; ++j) out[j] = pack2<T>(__uint_as_float(a[2 * j]), __uint_as_float(a[2 * j + 1]));
+                    }
+                    if (row < M) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const int col = tc.n0 + c * 32 + j * 8;
+                            if (col < n_out)  // n_out is a multiple of 8: a 16-byte vector is entirely in or out
+                                *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) =
+                                    make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+                        }
                     }
                 }
             }
@@ -275,14 +351,16 @@ EncodeTiledFn encode_tiled_fn() {
     return fn;
 }
 
-// Tensor map over a row-major [rows, k] matrix of 16-bit elements with leading dimension ld (elements):
-// box = 64 (k) x 128 (rows), 128-byte swizzle, out-of-range elements read as zero.
-bool make_tmap(CUtensorMap* tm, const void* base, int64_t rows, int64_t k, int64_t ld, int dtype) {
+// Tensor map over a row-major [outer, inner] matrix of 16-bit elements with leading dimension ld
+// (elements): box = 64 (inner) x box_outer, 128-byte swizzle, out-of-range elements read as zero.
+// K-major operands pass (inner = K, outer = rows, box_outer = 128); MN-major operands are stored
+// [K, rows] and pass (inner = rows, outer = K, box_outer = 64).
+bool make_tmap(CUtensorMap* tm, const void* base, int64_t outer, int64_t inner, int64_t ld, uint32_t box_outer, int dtype) {
     EncodeTiledFn enc = encode_tiled_fn();
     if (enc == nullptr) return false;
-    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(k), static_cast<cuuint64_t>(rows)};
+    const cuuint64_t dims[2] = {static_cast<cuuint64_t>(inner), static_cast<cuuint64_t>(outer)};
     const cuuint64_t strides[1] = {static_cast<cuuint64_t>(ld) * 2};
-    const cuuint32_t box[2] = {kBK, 128};
+    const cuuint32_t box[2] = {64, box_outer};
     const cuuint32_t estr[2] = {1, 1};
     const CUtensorMapDataType dt = dtype == MGR_BF16 ? CU_TENSOR_MAP_DATA_TYPE_BFLOAT16 : CU_TENSOR_MAP_DATA_TYPE_FLOAT16;
     return enc(tm, dt, 2, const_cast<void*>(base), dims, strides, box, estr, CU_TENSOR_MAP_INTERLEAVE_NONE,
@@ -302,28 +380,47 @@ int* gemm_status_ptr(const DeviceInfo& di) {
     return cache[di.device];
 }
 
-template <int EPI, typename T>
-int launch_gemm(void* c, const void* a, const void* b, int64_t m, int64_t n_out, int64_t k, int64_t lda, int64_t ldb,
-                int64_t ldc, int64_t b_rows, int dtype, const DeviceInfo& di, cudaStream_t s) {
+struct GemmArgs {
+    void* c;
+    const void* a;
+    const void* b;
+    const void* aux;
+    int64_t m, n_out, k;       // problem: C tile grid covers m x n_out, contraction length k
+    int64_t b_rows;            // logical rows of B (n_out, or 2 n_out for the gate|value split)
+    int64_t lda, ldb, ldc, ld_aux;
+    int dtype;
+};
+
+template <int EPI, bool A_MN, bool B_MN, typename T>
+int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     static bool attr[kMaxDevices] = {false};
     if (!attr[di.device]) {
-        if (cudaFuncSetAttribute(gemm_tn_kernel<EPI, T>, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kGemmSmem)) !=
-            cudaSuccess) {
+        if (cudaFuncSetAttribute(gemm_kernel<EPI, A_MN, B_MN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+                                 static_cast<int>(kGemmSmem)) != cudaSuccess) {
             (void)cudaGetLastError();
             return MGR_ERR_CUDA;
         }
         attr[di.device] = true;
     }
     CUtensorMap tmA, tmB;
-    if (!make_tmap(&tmA, a, m, k, lda, dtype) || !make_tmap(&tmB, b, b_rows, k, ldb, dtype)) return MGR_ERR_CUDA;
+    const bool okA = A_MN ? make_tmap(&tmA, g.a, g.k, g.m, g.lda, 64, g.dtype) : make_tmap(&tmA, g.a, g.m, g.k, g.lda, 128, g.dtype);
+    const bool okB = B_MN ? make_tmap(&tmB, g.b, g.k, g.b_rows, g.ldb, 64, g.dtype) : make_tmap(&tmB, g.b, g.b_rows, g.k, g.ldb, 128, g.dtype);
+    if (!okA || !okB) return MGR_ERR_CUDA;
     int* status = gemm_status_ptr(di);
     if (status == nullptr) return MGR_ERR_CUDA;
-    constexpr int n_step = EPI == kEpiSwiglu ? kBN / 2 : kBN;
-    const int64_t tiles = ((m + kBM - 1) / kBM) * ((n_out + n_step - 1) / n_step);
+    constexpr int n_step = EPI == kEpiPlain ? kBN : kBN / 2;
+    const int64_t tiles = ((g.m + kBM - 1) / kBM) * ((g.n_out + n_step - 1) / n_step);
     const unsigned grid = static_cast<unsigned>(tiles < di.sm_count ? tiles : di.sm_count);
-    gemm_tn_kernel<EPI, T><<<grid, kGemmThreads, kGemmSmem, s>>>(tmA, tmB, static_cast<T*>(c), static_cast<int>(m),
-                                                                 static_cast<int>(n_out), static_cast<int>(k), ldc, status);
+    gemm_kernel<EPI, A_MN, B_MN, T><<<grid, kGemmThreads, kGemmSmem, s>>>(
+        tmA, tmB, static_cast<T*>(g.c), static_cast<const T*>(g.aux), static_cast<int>(g.m), static_cast<int>(g.n_out),
+        static_cast<int>(g.k), g.ldc, g.ld_aux, status);
     return launch_status();
+}
+
+template <int EPI, bool A_MN, bool B_MN>
+int launch_gemm_dtype(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
+    if (g.dtype == MGR_F16) return launch_gemm<EPI, A_MN, B_MN, __half>(g, di, s);
+    return launch_gemm<EPI, A_MN, B_MN, __nv_bfloat16>(g, di, s);
 }
 
 int gemm_check(int64_t m, int64_t n, int64_t k, int dtype) {
@@ -353,19 +450,34 @@ int gemm_status_fetch(int clear) {
 
 using namespace mgr;
 
-extern "C" int mgr_gemm_tn(void* c, const void* a, const void* b, int64_t m, int64_t n, int64_t k, int64_t lda,
-                           int64_t ldb, int64_t ldc, int dtype, void* stream) {
+// Leading dimension of an operand with `rows` logical rows and contraction length k.
+static int check_ld(int64_t ld, int64_t rows, int64_t k, int mn_major) {
+    const int64_t need = mn_major ? rows : k;
+    return ld >= need && ld % 8 == 0;
+}
+
+extern "C" int mgr_gemm(void* c, const void* a, const void* b, int64_t m, int64_t n, int64_t k, int64_t lda, int64_t ldb,
+                        int64_t ldc, int a_mn_major, int b_mn_major, int dtype, void* stream) {
     int st = gemm_check(m, n, k, dtype);
     if (st != MGR_OK) return st;
-    if (lda < k || ldb < k || ldc < n || lda % 8 != 0 || ldb % 8 != 0 || ldc % 8 != 0) return MGR_ERR_BAD_SHAPE;
+    if (m % 8 != 0 && a_mn_major) return MGR_ERR_BAD_SHAPE;  // rows of an MN-major A are its inner dimension
+    if (!check_ld(lda, m, k, a_mn_major) || !check_ld(ldb, n, k, b_mn_major) || ldc < n || ldc % 8 != 0) return MGR_ERR_BAD_SHAPE;
     if (m == 0) return MGR_OK;
     if (c == nullptr || a == nullptr || b == nullptr) return MGR_ERR_NULL_PTR;
     if (!aligned_to(c, 16) || !aligned_to(a, 16) || !aligned_to(b, 16)) return MGR_ERR_MISALIGNED;
     const DeviceInfo di = current_device_info();
     if (di.status != MGR_OK) return di.status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == MGR_F16) return launch_gemm<kEpiPlain, __half>(c, a, b, m, n, k, lda, ldb, ldc, n, dtype, di, s);
-    return launch_gemm<kEpiPlain, __nv_bfloat16>(c, a, b, m, n, k, lda, ldb, ldc, n, dtype, di, s);
+    const GemmArgs g{c, a, b, nullptr, m, n, k, n, lda, ldb, ldc, 0, dtype};
+    if (!a_mn_major && !b_mn_major) return launch_gemm_dtype<kEpiPlain, false, false>(g, di, s);
+    if (!a_mn_major && b_mn_major) return launch_gemm_dtype<kEpiPlain, false, true>(g, di, s);
+    if (a_mn_major && !b_mn_major) return launch_gemm_dtype<kEpiPlain, true, false>(g, di, s);
+    return launch_gemm_dtype<kEpiPlain, true, true>(g, di, s);
+}
+
+extern "C" int mgr_gemm_tn(void* c, const void* a, const void* b, int64_t m, int64_t n, int64_t k, int64_t lda,
+                           int64_t ldb, int64_t ldc, int dtype, void* stream) {
+    return mgr_gemm(c, a, b, m, n, k, lda, ldb, ldc, 0, 0, dtype, stream);
 }
 
 extern "C" int mgr_swiglu_fused_fwd(void* h, const void* x, const void* w12, int64_t m, int64_t d, int64_t f, int dtype,
@@ -377,7 +489,19 @@ extern "C" int mgr_swiglu_fused_fwd(void* h, const void* x, const void* w12, int
     if (!aligned_to(h, 16) || !aligned_to(x, 16) || !aligned_to(w12, 16)) return MGR_ERR_MISALIGNED;
     const DeviceInfo di = current_device_info();
     if (di.status != MGR_OK) return di.status;
-    cudaStream_t s = static_cast<cudaStream_t>(stream);
-    if (dtype == MGR_F16) return launch_gemm<kEpiSwiglu, __half>(h, x, w12, m, f, d, d, d, f, 2 * f, dtype, di, s);
-    return launch_gemm<kEpiSwiglu, __nv_bfloat16>(h, x, w12, m, f, d, d, d, f, 2 * f, dtype, di, s);
+    const GemmArgs g{h, x, w12, nullptr, m, f, d, 2 * f, d, d, f, 0, dtype};
+    return launch_gemm_dtype<kEpiSwiglu, false, false>(g, di, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mgr_swiglu_fused_bwd(void* dgv, const void* dh, const void* x, const void* w12, int64_t m, int64_t d,
+                                    int64_t f, int dtype, void* stream) {
+    int st = gemm_check(m, f, d, dtype);
+    if (st != MGR_OK) return st;
+    if (m == 0) return MGR_OK;
+    if (dgv == nullptr || dh == nullptr || x == nullptr || w12 == nullptr) return MGR_ERR_NULL_PTR;
+    if (!aligned_to(dgv, 16) || !aligned_to(dh, 16) || !aligned_to(x, 16) || !aligned_to(w12, 16)) return MGR_ERR_MISALIGNED;
+    const DeviceInfo di = current_device_info();
+    if (di.status != MGR_OK) return di.status;
+    const GemmArgs g{dgv, x, w12, dh, m, f, d, 2 * f, d, d, 2 * f, f, dtype};
+    return launch_gemm_dtype<kEpiSwigluBwd, false, false>(g, di, static_cast<cudaStream_t>(stream));
 }

@@ -198,3 +198,47 @@ def linear_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
         st = L.mgr_gemm_tn(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, k, k, n, code, _stream_ptr(a.device))
     _capi.check("tensor-core GEMM kernel", st)
     return c
+
+
+def gemm(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool = False, b_mn_major: bool = False) -> torch.Tensor:
+    """c[m, n] = op(a) op(b)^T on the tensor-core kernel. K-major operands are stored [m, k] / [n, k];
+    MN-major ones are stored [k, m] / [k, n] (the transposed matrix as it already lies in memory), so
+    the backward GEMMs of an nn.Linear need no transposed copy."""
+    _check_input(a, "a")
+    _check_input(b, "b")
+    if a.dim() != 2 or b.dim() != 2:
+        raise RuntimeError("operands must be 2-D")
+    k, m = (a.shape if a_mn_major else a.shape[::-1])
+    kb, n = (b.shape if b_mn_major else b.shape[::-1])
+    if k != kb:
+        raise RuntimeError("contraction lengths differ")
+    if a.dtype != b.dtype or a.device != b.device:
+        raise RuntimeError("operands must share dtype and device")
+    code = _dtype_code(a, "")
+    L = _capi.lib()
+    with torch.cuda.device(a.device):
+        c = torch.empty((m, n), device=a.device, dtype=a.dtype)
+        st = L.mgr_gemm(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, a.shape[1], b.shape[1], n,
+                        int(a_mn_major), int(b_mn_major), code, _stream_ptr(a.device))
+    _capi.check("tensor-core GEMM kernel", st)
+    return c
+
+
+def swiglu_fused_backward(dh: torch.Tensor, x: torch.Tensor, w12: torch.Tensor, hidden_dim: int) -> torch.Tensor:
+    """[d_gate | d_val] of shape [M, 2*hidden] from dh [M, hidden], recomputing x w12^T inside the kernel
+    (the recomputed `self.w12(x)` plus the launch at megagemm/swiglu.py:125-129, fused)."""
+    for t, nme in ((dh, "dh"), (x, "x"), (w12, "w12")):
+        _check_input(t, nme)
+    m, d = x.shape
+    if tuple(dh.shape) != (m, hidden_dim) or tuple(w12.shape) != (2 * hidden_dim, d):
+        raise RuntimeError("expected dh [M, hidden], x [M, d_model], w12 [2*hidden, d_model]")
+    if not (dh.dtype == x.dtype == w12.dtype) or not (dh.device == x.device == w12.device):
+        raise RuntimeError("dh, x and w12 must share dtype and device")
+    code = _dtype_code(x, " for backward")
+    L = _capi.lib()
+    with torch.cuda.device(x.device):
+        dgv = torch.empty((m, 2 * hidden_dim), device=x.device, dtype=x.dtype)
+        st = L.mgr_swiglu_fused_bwd(dgv.data_ptr(), dh.data_ptr(), x.data_ptr(), w12.data_ptr(), m, d, hidden_dim, code,
+                                    _stream_ptr(x.device))
+    _capi.check("fused SwiGLU backward kernel", st)
+    return dgv

@@ -68,12 +68,22 @@ class SwiGLUMLPFunction(Function):
         dy = grad_output.reshape(-1, grad_output.shape[-1])
         if not dy.is_contiguous():
             dy = dy.contiguous()
-        dh = torch.matmul(dy, w3)                       # [M, hidden]
-        dw3 = torch.matmul(dy.t(), h) if ctx.needs_input_grad[2] else None
-        gv = torch.nn.functional.linear(x2d, w12)       # recomputed projection [M, 2*hidden]
-        dgv = rmsnorm_cuda_ops.swiglu_act_backward(dh, gv, hidden)
-        dx = torch.matmul(dgv, w12).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
-        dw12 = torch.matmul(dgv.t(), x2d) if ctx.needs_input_grad[1] else None
+        ops = rmsnorm_cuda_ops
+        m = x2d.shape[0]
+        if m % 8 != 0:
+            # dW = (.)^T (.) contracts over the M rows; the tensor-core kernel wants that length to be a
+            # multiple of 8. Ragged batches keep the library GEMMs for backward.
+            dh = torch.matmul(dy, w3)
+            dw3 = torch.matmul(dy.t(), h) if ctx.needs_input_grad[2] else None
+            dgv = ops.swiglu_act_backward(dh, torch.nn.functional.linear(x2d, w12), hidden)
+            dx = torch.matmul(dgv, w12).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
+            dw12 = torch.matmul(dgv.t(), x2d) if ctx.needs_input_grad[1] else None
+            return dx, dw12, dw3
+        dh = ops.gemm(dy, w3, False, True)                                   # dy [M,D] x w3 [D,F]      -> [M, F]
+        dw3 = ops.gemm(dy, h, True, True) if ctx.needs_input_grad[2] else None        # dy^T h     -> [D, F]
+        dgv = ops.swiglu_fused_backward(dh, x2d, w12, hidden)                # [d_gate | d_val]         -> [M, 2F]
+        dx = ops.gemm(dgv, w12, False, True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None   # -> [M, D]
+        dw12 = ops.gemm(dgv, x2d, True, True) if ctx.needs_input_grad[1] else None    # dgv^T x   -> [2F, D]
         return dx, dw12, dw3
 
 
