@@ -116,6 +116,29 @@ int mgr_rmsnorm_bwd(void* dx, void* dw, float* dw_f32, const void* dy, const voi
                     const float* inv_rms, int64_t rows, int64_t cols, int dtype,
                     void* workspace, size_t workspace_bytes, void* stream);
 
+/* RMSNorm backward without a caller-provided workspace. It has no counterpart in the reference (whose
+ * backward needs no scratch because it accumulates dW with atomics, src/rmsnorm_kernel.cu:315-325).
+ *
+ * Same arguments, arithmetic, kernels and results as mgr_rmsnorm_bwd, minus `workspace`: the partial
+ * rows of dW go to a fixed MGR_NOALLOC_SCRATCH_BYTES array inside the library's device image. It is for
+ * hosts that cannot obtain device memory at call time: a C/C++ program without a stream-ordered
+ * allocator, or a running service that keeps cudaMalloc/cudaFree out of its steady state because both
+ * synchronise the device and may fail once memory is fragmented. The call itself allocates nothing
+ * (no cudaMalloc, no cudaFree, no allocating library routine).
+ *   - Limit: problems whose mgr_rmsnorm_bwd_workspace_bytes(rows, cols, dtype) exceeds
+ *     MGR_NOALLOC_SCRATCH_BYTES return MGR_ERR_TOO_LARGE before anything is launched (on a 148-SM B200
+ *     every problem with cols <= 16384 fits, whatever the dtype and row count; fp16/bf16 rows of 32768
+ *     columns, whose packet kernel writes 148 partial rows of 128 KiB, do not).
+ *   - Every GPU whose context loads the library holds the array until the process ends.
+ *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per
+ *     device, with that device current). Make that first call before starting any stream capture.
+ *   - All calls on a device share the array; it keeps the last call's contents and needs no clearing.
+ *     Calls that may overlap on the GPU (different streams without an ordering) race: serialise them.
+ */
+#define MGR_NOALLOC_SCRATCH_BYTES (16u << 20)
+int mgr_rmsnorm_bwd_noalloc(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, const void* w,
+                            const float* inv_rms, int64_t rows, int64_t cols, int dtype, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * SwiGLU activation on an already-projected tensor: gv = [gate | val] of shape [m, 2f] (gate =
  * columns [0,f), val = columns [f,2f): the layout nn.Linear(d, 2*hidden) produces and

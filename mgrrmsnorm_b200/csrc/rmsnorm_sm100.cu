@@ -719,3 +719,59 @@ int rmsnorm_status_fetch(int clear) {
     return v;
 }
 }  // namespace mgr
+
+// ------------------------------------------------------------------------------------------------
+// Backward for callers that cannot allocate device memory.
+//
+// mgr_rmsnorm_bwd takes its scratch (the per-CTA fp32 partial rows of dW) from the caller. A caller
+// that has no allocator to ask -- a plain C/C++ host without torch's caching allocator, or a serving
+// loop that must not call cudaMalloc once it is running, because cudaMalloc and cudaFree synchronise
+// the whole device and can fail late through fragmentation -- uses this entry point instead: the
+// scratch is a fixed array that lives in the library's device image.
+//
+// The array is part of every context that loads the library (16 MiB per GPU until the process exits).
+// All calls on a device share it and it keeps the previous call's partial rows; nothing in it has to
+// start at zero, because the backward kernel overwrites every partial row the reduce kernel then reads.
+// Two calls that overlap on the GPU (different streams, no ordering between them) race on the array.
+// ------------------------------------------------------------------------------------------------
+
+static __device__ __align__(256) float g_noalloc_scratch[MGR_NOALLOC_SCRATCH_BYTES / sizeof(float)];
+
+namespace mgr {
+namespace {
+
+// Device address of g_noalloc_scratch on the CURRENT device. In host code the array's name is only a
+// handle for the runtime, not an address a kernel can use: the address comes from
+// cudaGetSymbolAddress, asked once per device with that device current, and is cached.
+float* noalloc_scratch(const DeviceInfo& di) {
+    static float* cache[kMaxDevices] = {nullptr};
+    if (cache[di.device] == nullptr) {
+        void* p = nullptr;
+        const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
+        if (e != cudaSuccess || p == nullptr) {
+            (void)cudaGetLastError();
+            return nullptr;
+        }
+        cache[di.device] = static_cast<float*>(p);
+    }
+    return cache[di.device];
+}
+
+}  // namespace
+}  // namespace mgr
+
+extern "C" int mgr_rmsnorm_bwd_noalloc(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, const void* w,
+                                       const float* inv_rms, int64_t rows, int64_t cols, int dtype, void* stream) {
+    const int st = check_common(rows, cols, dtype);
+    if (st != MGR_OK) return st;
+    if (rows == 0)  // nothing to reduce: the scratch is not touched
+        return mgr_rmsnorm_bwd(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, dtype, nullptr, 0, stream);
+    const DeviceInfo di = current_device_info();
+    if (di.status != MGR_OK) return di.status;
+    const size_t need = mgr_rmsnorm_bwd_workspace_bytes(rows, cols, dtype);
+    if (need == 0) return MGR_ERR_CUDA;
+    if (need > MGR_NOALLOC_SCRATCH_BYTES) return MGR_ERR_TOO_LARGE;
+    float* scratch = noalloc_scratch(di);
+    if (scratch == nullptr) return MGR_ERR_CUDA;
+    return mgr_rmsnorm_bwd(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, dtype, scratch, MGR_NOALLOC_SCRATCH_BYTES, stream);
+}
