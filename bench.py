@@ -38,9 +38,11 @@ HIDDEN = 8192
 EPS = 1e-6
 SEED = 1234
 CPU_SAMPLE_ROWS = 4096
-# DRAM bytes (read + write) per launch of the dominant kernel from one ncu capture, per algorithmic
-# byte; None until a capture has been summarised under profiles/.
-TRAFFIC_PER_ALGO_BYTE = None
+# DRAM bytes (dram__bytes_read.sum + dram__bytes_write.sum) per algorithmic byte of one backward launch,
+# from the ncu capture summarised in profiles/rmsnorm_bf16_h8192_reg_kernels.txt: 16384 rows x 8192 bf16,
+# 537.0 MB read + 235.7 MB written against 805.4 MB algorithmic. Traffic grows in proportion to the rows,
+# so the full-size figure is this ratio times the full launch's algorithmic bytes.
+TRAFFIC_PER_ALGO_BYTE = (536.965888 + 235.687424) / 805.404672
 
 
 def rms_bytes(rows: int, cols: int, s: int) -> dict:
@@ -382,7 +384,167 @@ def side_results(L, device, peak_gbs) -> dict:
         del b
         torch.cuda.empty_cache()
     out["rmsnorm_bf16_hidden_sweep_2^29_elements"] = sweep
+    out["swiglu_mlp_fp16_M4096_D4096_F6912"] = mlp_side_result(device)
     return out
+
+
+def mlp_side_result(device) -> dict:
+    """SwiGLU MLP forward+backward, fp16, x [32,128,4096], hidden 6912 (the module's default), through the
+    public module on the tensor-core kernels. 18*M*D*F algorithmic flops per step (the projection that
+    backward recomputes is not counted). Weights (162 MiB) and activations exceed L2 together."""
+    from mgrrmsnorm_b200 import MegaGemmTriton
+
+    peaks, _ = measured_peaks()
+    torch.manual_seed(SEED)
+    mlp = MegaGemmTriton(4096).to(device).half()
+    g = torch.Generator(device=device).manual_seed(SEED)
+    x = torch.randn(32, 128, 4096, device=device, generator=g).half().requires_grad_(True)
+    dy = torch.randn(32, 128, 4096, device=device, generator=g).half()
+    m, d, f = 4096, 4096, mlp.hidden
+
+    def step():
+        x.grad = None
+        mlp.w12.weight.grad = None
+        mlp.w3.weight.grad = None
+        mlp(x).backward(dy)
+
+    def fwd_only():
+        with torch.no_grad():
+            mlp(x)
+
+    res = {}
+    for name, fn, flops in (("fwd_bwd", step, 18 * m * d * f), ("fwd", fwd_only, 6 * m * d * f)):
+        for _ in range(5):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(20):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        ms = e0.elapsed_time(e1) / 20
+        res[name] = {"ms": ms, "TFLOPs": flops / ms / 1e9, "frac_of_bf16_burst_peak": flops / ms / 1e9 / float(peaks["bf16_tflops"])}
+    res["hidden"] = f
+    return res
+
+
+MLP_TOKENS = 4096
+MLP_D = 4096
+
+
+def run_mlp(args, L, device, warmup, peaks, peak_kind, sm_count) -> int:
+    """SwiGLU MLP forward+backward (config 4: fp16, x [32,128,4096], hidden = the module's default 6912,
+    nn.Linear default init from a seed) through the public module. One JSON line; the roofline entry is
+    the fused projection kernel (tensor-bound), timed in its own loop of launches in the same run."""
+    from mgrrmsnorm_b200 import MegaGemmTriton
+    from mgrrmsnorm_b200 import rmsnorm_cuda_ops as ops
+
+    m, d = args.tokens, MLP_D
+    torch.manual_seed(SEED)
+    mlp = MegaGemmTriton(d).to(device).half()
+    f = mlp.hidden
+    g = torch.Generator(device=device).manual_seed(SEED)
+    x = torch.randn(m, d, device=device, generator=g).half().requires_grad_(True)
+    dy = torch.randn(m, d, device=device, generator=g).half()
+    stream = torch.cuda.current_stream()
+
+    def step():
+        x.grad = None
+        mlp.w12.weight.grad = None
+        mlp.w3.weight.grad = None
+        y = mlp(x)
+        y.backward(dy)
+        return y
+
+    def timed(fn, n, w):
+        for _ in range(w):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        t0 = time.perf_counter()
+        e0.record(stream)
+        for _ in range(n):
+            fn()
+        e1.record(stream)
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n, (t0, time.perf_counter())
+
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    ms, window = timed(step, args.steps, warmup)
+    sampler.stop()
+    flops = 18 * m * d * f
+    xd = x.detach()
+    w12 = mlp.w12.weight.detach()
+    k_ms, _ = timed(lambda: ops.swiglu_fused_forward(xd, w12, f), max(args.steps, 20), warmup)
+    k_flops = 4 * m * d * f
+    peak_tf = float(peaks["bf16_tflops"])
+
+    e2e = None
+    if not args.no_e2e:
+        hx, hdy = xd.cpu().pin_memory(), dy.cpu().pin_memory()
+        hy, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
+
+        def e2e_step():
+            xx = hx.to(device, non_blocking=True).requires_grad_(True)
+            dd = hdy.to(device, non_blocking=True)
+            mlp.w12.weight.grad = None
+            mlp.w3.weight.grad = None
+            y = mlp(xx)
+            y.backward(dd)
+            hy.copy_(y.detach(), non_blocking=True)
+            hdx.copy_(xx.grad, non_blocking=True)
+
+        e_ms, _ = timed(e2e_step, max(args.e2e_steps, 3), 2)
+        e2e = {"value": flops / e_ms / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * m * d * 2, "d2h_bytes_per_step": 2 * m * d * 2,
+               "ms_per_step": e_ms, "path": "pinned host x, dy -> MegaGemmTriton fwd+bwd -> pinned host y, dx (weight grads stay on the device)"}
+    cpu = None
+    if not args.no_cpu:
+        cpu = time_cpu_mlp(mlp, f)
+    reduced = m != MLP_TOKENS
+    line = {
+        "metric": "SwiGLU MLP TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
+        "config": {"workload": f"SwiGLU MLP fp16 forward+backward, {m} tokens, d_model {d}, hidden {f} (MegaGemmTriton default), "
+                               "fused SiLU(gate)*value epilogue" + (" [REDUCED CASE, not the benchmark]" if reduced else ""),
+                   "tokens": m, "d_model": d, "hidden": f, "flops_per_step": flops,
+                   "l2": "weights 162 MiB + activations exceed the 126 MB L2", "seed": SEED},
+        "frac_of_bf16_peak": flops / ms / 1e9 / peak_tf,
+        "roofline": {"bound": "tensor", "kernel": "gemm_kernel<swiglu epilogue> (mgr_swiglu_fused_fwd: x w12^T -> silu(gate)*value)",
+                     "achieved": k_flops / k_ms / 1e9, "peak": peak_tf, "unit": "TFLOP/s", "frac": k_flops / k_ms / 1e9 / peak_tf,
+                     "peak_source": f"of {peak_kind} (cuBLAS bf16 burst)", "algorithmic_flops_per_launch": k_flops, "avg_launch_ms": k_ms,
+                     "timed": "own loop of launches in this run", "traffic": None},
+        "e2e": e2e, "gpu_launches": 7 * args.steps,
+        "clocks": sampler.summary(*window), "sm_count": sm_count,
+    }
+    if cpu:
+        line["cpu_baseline"] = cpu
+    print(json.dumps(line), flush=True)
+    return 0
+
+
+def time_cpu_mlp(mlp, f) -> dict:
+    """The reference's CPU path for the MLP: the PyTorchSwiGLU formula (benchmark_swiglu.py:40-58) in fp32
+    on the host cores, forward+backward, on a 128-token sample of the batch."""
+    from oracle import oracle
+
+    m = 128
+    g = torch.Generator().manual_seed(SEED)
+    x = torch.randn(m, MLP_D, generator=g)
+    dy = torch.randn(m, MLP_D, generator=g)
+    w12 = mlp.w12.weight.detach().float().cpu()
+    w3 = mlp.w3.weight.detach().float().cpu()
+    oracle.swiglu_formula_torch(x, w12, w3, dy)
+    times = []
+    t_begin = time.perf_counter()
+    while len(times) < 10 and time.perf_counter() - t_begin < 15.0:
+        t0 = time.perf_counter()
+        oracle.swiglu_formula_torch(x, w12, w3, dy)
+        times.append(time.perf_counter() - t0)
+    per = sum(times) / len(times)
+    return {"value": 18 * m * MLP_D * f / per / 1e12, "unit": "TFLOP/s", "cores": torch.get_num_threads(), "kind": "port",
+            "sample": f"PyTorchSwiGLU formula fwd+bwd in fp32 on {m} of the {MLP_TOKENS} tokens, {len(times)} steps"}
 
 
 def main(argv=None) -> int:
@@ -397,6 +559,10 @@ def main(argv=None) -> int:
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU,
                     help="rows per GPU; anything but the default is a reduced case for profiler captures, not a bench value")
+    ap.add_argument("--workload", choices=["rmsnorm", "mlp"], default="rmsnorm",
+                    help="rmsnorm (default, the headline) or mlp: SwiGLU MLP fp16 d_model 4096 hidden 6912 forward+backward, 1 GPU")
+    ap.add_argument("--tokens", type=int, default=MLP_TOKENS,
+                    help="tokens for --workload mlp; anything but the default is a reduced case for profiler captures")
     args = ap.parse_args(argv)
     if args.impl == "reference":
         return reference_arm(args)
@@ -426,6 +592,11 @@ def main(argv=None) -> int:
     warmup = max(args.warmup, 3)
     peaks, peak_kind = measured_peaks()
     peak_gbs = float(peaks["hbm_gbs"])
+    if args.workload == "mlp":
+        if world != 1:
+            print("--workload mlp runs on one GPU", file=sys.stderr)
+            return 2
+        return run_mlp(args, L, device, warmup, peaks, peak_kind, sms.value)
 
     main_buf = RmsBuffers(L, args.rows, HIDDEN, torch.bfloat16, device, SEED + rank, x_scale=2.0 ** 0.5)
     sampler = ClockSampler(local_rank) if rank == 0 else None
