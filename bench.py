@@ -524,6 +524,97 @@ def run_mlp(args, L, device, warmup, peaks, peak_kind, sm_count) -> int:
     return 0
 
 
+BLOCK_TOKENS = 16384
+BLOCK_D = 8192
+BLOCK_F = 28672
+
+
+def run_block(args, device, warmup, peaks, peak_kind, world, rank) -> int:
+    """Config 5: bf16 pre-norm MLP block, y = SwiGLU(RMSNorm(x)), d = 8192, d_ff = 28672, 16384 tokens.
+    Tensor-parallel over the ranks: w12 split by hidden units (gate and value rows of each rank), w3 by
+    columns, x and the norm replicated, one NCCL all-reduce of y in forward and one of dx in backward.
+    Strong scaling: the block is fixed, each GPU does 1/P of the GEMM work. Value = 18*M*D*F / time."""
+    import torch.distributed as dist
+
+    from mgrrmsnorm_b200 import MegaGemmTriton, RMSNorm, sharding
+
+    m, d, f = (args.tokens if args.tokens != MLP_TOKENS else BLOCK_TOKENS), BLOCK_D, BLOCK_F
+    dt = torch.bfloat16
+    f0, f1 = sharding.tp_hidden_slice(f, world, rank)
+    if world == 1:
+        mlp = MegaGemmTriton(d, hidden_multiple=3.5)
+        assert mlp.hidden == f
+        mlp = mlp.to(device).to(dt)
+        local = mlp
+    else:
+        mlp = sharding.TensorParallelSwiGLU(d, f, world, rank).to(device).to(dt)
+        local = mlp.local
+    # nn.Linear's default init, U(-1/sqrt(fan_in), 1/sqrt(fan_in)), drawn on the device; fan_in of w3 is the FULL d_ff
+    g = torch.Generator(device=device).manual_seed(SEED + 17 * rank)
+    with torch.no_grad():
+        local.w12.weight.copy_((torch.rand(local.w12.weight.shape, device=device, generator=g) * 2 - 1) / d ** 0.5)
+        local.w3.weight.copy_((torch.rand(local.w3.weight.shape, device=device, generator=g) * 2 - 1) / f ** 0.5)
+    norm = RMSNorm(d, epsilon=EPS).to(device).to(dt)
+    gx = torch.Generator(device=device).manual_seed(SEED)            # replicated input: same seed on every rank
+    with torch.no_grad():
+        norm.weight.copy_((1 + 0.1 * torch.randn(d, device=device, generator=gx)).to(dt))
+    x = torch.randn(m, d, device=device, generator=gx).to(dt).requires_grad_(True)
+    dy = torch.randn(m, d, device=device, generator=gx).to(dt)
+    stream = torch.cuda.current_stream()
+
+    def step():
+        x.grad = None
+        for p in list(mlp.parameters()) + [norm.weight]:
+            p.grad = None
+        mlp(norm(x)).backward(dy)
+
+    for _ in range(warmup):
+        step()
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    sampler = ClockSampler(device.index or 0) if rank == 0 else None
+    if sampler:
+        sampler.start()
+    if world > 1:
+        dist.barrier()
+    torch.cuda.synchronize()
+    t0 = time.perf_counter()
+    e0.record(stream)
+    for _ in range(args.steps):
+        step()
+    e1.record(stream)
+    torch.cuda.synchronize()
+    t1 = time.perf_counter()
+    if world > 1:
+        dist.barrier()
+    if sampler:
+        sampler.stop()
+    ms = e0.elapsed_time(e1)
+    if world > 1:
+        t = torch.tensor([ms], device=device, dtype=torch.float64)
+        dist.all_reduce(t, op=dist.ReduceOp.MAX)
+        ms = float(t.item())
+    ms /= args.steps
+    flops = 18 * m * d * f
+    if rank == 0:
+        peak_tf = float(peaks["bf16_tflops_sustained"])
+        line = {
+            "metric": "Pre-norm MLP block TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
+            "data": "synthetic",
+            "config": {"workload": f"bf16 pre-norm block RMSNorm({d}) -> SwiGLU(d_ff {f}) over {m} tokens, forward+backward, "
+                                   f"tensor-parallel x{world}" + (" [REDUCED CASE]" if m != BLOCK_TOKENS else ""),
+                       "tokens": m, "d_model": d, "d_ff": f, "d_ff_per_gpu": f1 - f0, "flops_per_step": flops,
+                       "allreduce_bytes_per_step": 0 if world == 1 else 2 * m * d * 2, "seed": SEED},
+            "tflops_per_gpu": flops / ms / 1e9 / world,
+            "frac_of_bf16_sustained_peak_per_gpu": flops / ms / 1e9 / world / peak_tf, "peak_source": f"of {peak_kind} (cuBLAS bf16 sustained)",
+            "gpu_launches": 8 * args.steps, "clocks": sampler.summary(t0, t1) if sampler else None,
+        }
+        print(json.dumps(line), flush=True)
+    if world > 1:
+        dist.destroy_process_group()
+    return 0
+
+
 def time_cpu_mlp(mlp, f) -> dict:
     """The reference's CPU path for the MLP: the PyTorchSwiGLU formula (benchmark_swiglu.py:40-58) in fp32
     on the host cores, forward+backward, on a 128-token sample of the batch."""
@@ -559,8 +650,9 @@ def main(argv=None) -> int:
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU,
                     help="rows per GPU; anything but the default is a reduced case for profiler captures, not a bench value")
-    ap.add_argument("--workload", choices=["rmsnorm", "mlp"], default="rmsnorm",
-                    help="rmsnorm (default, the headline) or mlp: SwiGLU MLP fp16 d_model 4096 hidden 6912 forward+backward, 1 GPU")
+    ap.add_argument("--workload", choices=["rmsnorm", "mlp", "block"], default="rmsnorm",
+                    help="rmsnorm (default, the headline); mlp: SwiGLU MLP fp16 d_model 4096 hidden 6912 forward+backward, 1 GPU; "
+                         "block: bf16 pre-norm block RMSNorm(8192) -> SwiGLU(d_ff 28672) over 16384 tokens, tensor-parallel over --gpus")
     ap.add_argument("--tokens", type=int, default=MLP_TOKENS,
                     help="tokens for --workload mlp; anything but the default is a reduced case for profiler captures")
     args = ap.parse_args(argv)
@@ -597,6 +689,8 @@ def main(argv=None) -> int:
             print("--workload mlp runs on one GPU", file=sys.stderr)
             return 2
         return run_mlp(args, L, device, warmup, peaks, peak_kind, sms.value)
+    if args.workload == "block":
+        return run_block(args, device, warmup, peaks, peak_kind, world, rank)
 
     main_buf = RmsBuffers(L, args.rows, HIDDEN, torch.bfloat16, device, SEED + rank, x_scale=2.0 ** 0.5)
     sampler = ClockSampler(local_rank) if rank == 0 else None

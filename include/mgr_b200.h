@@ -195,6 +195,20 @@ int mgr_gemm(void* c, const void* a, const void* b, int64_t m, int64_t n, int64_
 int mgr_swiglu_fused_bwd(void* dgv, const void* dh, const void* x, const void* w12, int64_t m, int64_t d, int64_t f,
                          int dtype, void* stream);
 
+/* The same forward/backward pair when the projection IS kept for backward, as the reference keeps
+ * w12_out (ctx.save_for_backward, megagemm/swiglu.py:98): one store of [m, 2f] in forward instead of a
+ * second projection GEMM in backward.
+ * mgr_swiglu_fused_fwd_save: mgr_swiglu_fused_fwd that also writes gv[m, 2f] = round_dtype([gate | val]).
+ *   h is still computed from the fp32 accumulators, not from the rounded gv.
+ * mgr_swiglu_dh_dgv: dgv[m, 2f] = [d_gate | d_val] from dy[m, d], w3[d, f] and the stored gv: the GEMM
+ *   dh = dy w3 (Linear(w3).backward) with _mg_swiglu_bwd_kernel (megagemm/swiglu.py:46-79) as its
+ *   epilogue; dh stays in fp32 in tensor memory and is never written.
+ */
+int mgr_swiglu_fused_fwd_save(void* h, void* gv, const void* x, const void* w12, int64_t m, int64_t d, int64_t f,
+                              int dtype, void* stream);
+int mgr_swiglu_dh_dgv(void* dgv, const void* dy, const void* w3, const void* gv, int64_t m, int64_t d, int64_t f,
+                      int dtype, void* stream);
+
 #ifdef __cplusplus
 }
 #endif

@@ -48,6 +48,8 @@ SIGNATURES = {
     "mgr_gemm_tn": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _int, _vp]),
     "mgr_gemm": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _vp]),
     "mgr_swiglu_fused_bwd": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "mgr_swiglu_fused_fwd_save": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "mgr_swiglu_dh_dgv": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
 }
 
 

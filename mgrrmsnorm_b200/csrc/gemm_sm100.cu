@@ -46,7 +46,11 @@ constexpr uint32_t kGemmSmem = kStages * kStageBytes + 1024;  // + slack to alig
 constexpr int kGemmThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 
-enum Epilogue { kEpiPlain = 0, kEpiSwiglu = 1, kEpiSwigluBwd = 2 };
+enum Epilogue { kEpiPlain = 0, kEpiSwiglu = 1, kEpiSwigluBwd = 2, kEpiSwigluSave = 3, kEpiDhDgv = 4 };
+
+// Output columns one tile covers: the full 256-column accumulator, or 128 when the accumulator holds a
+// gate half and a value half.
+__host__ __device__ constexpr int n_step_of(int epi) { return (epi == kEpiPlain || epi == kEpiDhDgv) ? kBN : kBN / 2; }
 
 // Shared-memory matrix descriptors (64-bit, addresses in 16-byte units): start address [0,14),
 // leading byte offset [16,30), stride byte offset [32,46), descriptor version 1 at [46,48) (sm_100),
@@ -107,12 +111,17 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_step) 
 //                covers 128 columns of C (B rows n0.. and n_out+n0..).
 // kEpiSwigluBwd: same tile; aux = dh [M, n_out]. C = [d_gate | d_val] of shape [M, 2 n_out]:
 //                d_val = dh * G * sig(G), d_gate = dh * V * sig(G) * (1 + G * (1 - sig(G))).
+// kEpiSwigluSave: kEpiSwiglu that also stores the projection, rounded to T, in C2 = [G | V] of shape
+//                [M, 2 n_out] (pitch ld_aux) -- the training forward, whose backward reads it back.
+// kEpiDhDgv    : plain tile (256 columns); acc = dh tile; aux = stored projection [G | V] (pitch ld_aux);
+//                C = [d_gate | d_val] of shape [M, 2 n_out]. dh itself is never written.
 template <int EPI, bool A_MN, bool B_MN, typename T>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, T* __restrict__ C,
-            const T* __restrict__ aux, int M, int n_out, int K, int64_t ldc, int64_t ld_aux, int* __restrict__ status) {
-    static_assert(EPI == kEpiPlain || !B_MN, "the gate/value split reads w12 K-major");
-    constexpr int kNStep = EPI == kEpiPlain ? kBN : kBN / 2;  // output columns per tile
+            T* __restrict__ C2, const T* __restrict__ aux, int M, int n_out, int K, int64_t ldc, int64_t ld_aux,
+            int* __restrict__ status) {
+    static_assert(n_step_of(EPI) == kBN || !B_MN, "the gate/value split reads w12 K-major");
+    constexpr int kNStep = n_step_of(EPI);  // output columns per tile
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_tfull[2], bar_tempty[2];
     __shared__ uint32_t tmem_base_slot;
@@ -156,7 +165,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             bool ok = true;
             for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
                 const TileCoord tc = tile_coord(t, m_tiles, kNStep);
-                const int b_row1 = EPI == kEpiPlain ? tc.n0 + kBN / 2 : n_out + tc.n0;
+                const int b_row1 = kNStep == kBN ? tc.n0 + kBN / 2 : n_out + tc.n0;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(ptx::smem_addr(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
                         ok = false;
@@ -280,9 +289,38 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             }
                         }
                     }
+                } else if constexpr (EPI == kEpiDhDgv) {
+                    uint32_t a[32];
+                    ptx::tmem_ld_32x32(t_row + c * 32, a);
+                    uint4 gp[4], vp[4];
+                    const T* grow = aux + static_cast<int64_t>(row) * ld_aux + tc.n0 + c * 32;
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        const bool on = row < M && tc.n0 + c * 32 + j * 8 < n_out;
+                        gp[j] = on ? *reinterpret_cast<const uint4*>(grow + j * 8) : make_uint4(0, 0, 0, 0);
+                        vp[j] = on ? *reinterpret_cast<const uint4*>(grow + n_out + j * 8) : make_uint4(0, 0, 0, 0);
+                    }
+                    ptx::tmem_ld_wait();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) {
+                        float gg[8], vv[8], dg[8], dv[8];
+                        unpack16<T>(gp[j], gg);
+                        unpack16<T>(vp[j], vv);
+#pragma unroll
+                        for (int e = 0; e < 8; ++e) {
+                            const float dh = __uint_as_float(a[j * 8 + e]);
+                            const float sig = sigmoid_(gg[e]);
+                            dv[e] = dh * (gg[e] * sig);
+                            dg[e] = dh * vv[e] * (sig * (1.0f + gg[e] * (1.0f - sig)));
+                        }
+                        if (row < M && tc.n0 + c * 32 + j * 8 < n_out) {
+                            *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) = pack16<T>(dg);
+                            *reinterpret_cast<uint4*>(crow + n_out + c * 32 + j * 8) = pack16<T>(dv);
+                        }
+                    }
                 } else {
                     uint32_t out[16];
-                    if constexpr (EPI == kEpiSwiglu) {
+                    if constexpr (EPI == kEpiSwiglu || EPI == kEpiSwigluSave) {
                         uint32_t g[32], v[32];
                         ptx::tmem_ld_32x32(t_row + c * 32, g);
                         ptx::tmem_ld_32x32(t_row + kBN / 2 + c * 32, v);
@@ -291,6 +329,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         for (int j = 0; j < 16; ++j)
                             out[j] = pack2<T>(silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(v[2 * j])),
                                               silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(v[2 * j + 1])));
+                        if constexpr (EPI == kEpiSwigluSave) {
+                            if (row < M) {
+                                T* prow = C2 + static_cast<int64_t>(row) * ld_aux + tc.n0 + c * 32;
+#pragma unroll
+                                for (int j = 0; j < 4; ++j) {
+                                    if (tc.n0 + c * 32 + j * 8 < n_out) {
+                                        uint32_t pg[4], pv[4];
+#pragma unroll
+                                        for (int e = 0; e < 4; ++e) {
+                                            pg[e] = pack2<T>(__uint_as_float(g[j * 8 + 2 * e]), __uint_as_float(g[j * 8 + 2 * e + 1]));
+                                            pv[e] = pack2<T>(__uint_as_float(v[j * 8 + 2 * e]), __uint_as_float(v[j * 8 + 2 * e + 1]));
+                                        }
+                                        *reinterpret_cast<uint4*>(prow + j * 8) = make_uint4(pg[0], pg[1], pg[2], pg[3]);
+                                        *reinterpret_cast<uint4*>(prow + n_out + j * 8) = make_uint4(pv[0], pv[1], pv[2], pv[3]);
+                                    }
+                                }
+                            }
+                        }
                     } else {
                         uint32_t a[32];
                         ptx::tmem_ld_32x32(t_row + c * 32, a);
@@ -381,6 +437,7 @@ int* gemm_status_ptr(const DeviceInfo& di) {
 }
 
 struct GemmArgs {
+    void* c2;   // second output (kEpiSwigluSave: the stored projection), else nullptr
     void* c;
     const void* a;
     const void* b;
@@ -408,11 +465,11 @@ int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     if (!okA || !okB) return MGR_ERR_CUDA;
     int* status = gemm_status_ptr(di);
     if (status == nullptr) return MGR_ERR_CUDA;
-    constexpr int n_step = EPI == kEpiPlain ? kBN : kBN / 2;
+    constexpr int n_step = n_step_of(EPI);
     const int64_t tiles = ((g.m + kBM - 1) / kBM) * ((g.n_out + n_step - 1) / n_step);
     const unsigned grid = static_cast<unsigned>(tiles < di.sm_count ? tiles : di.sm_count);
     gemm_kernel<EPI, A_MN, B_MN, T><<<grid, kGemmThreads, kGemmSmem, s>>>(
-        tmA, tmB, static_cast<T*>(g.c), static_cast<const T*>(g.aux), static_cast<int>(g.m), static_cast<int>(g.n_out),
+        tmA, tmB, static_cast<T*>(g.c), static_cast<T*>(g.c2), static_cast<const T*>(g.aux), static_cast<int>(g.m), static_cast<int>(g.n_out),
         static_cast<int>(g.k), g.ldc, g.ld_aux, status);
     return launch_status();
 }
@@ -468,7 +525,7 @@ extern "C" int mgr_gemm(void* c, const void* a, const void* b, int64_t m, int64_
     const DeviceInfo di = current_device_info();
     if (di.status != MGR_OK) return di.status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
-    const GemmArgs g{c, a, b, nullptr, m, n, k, n, lda, ldb, ldc, 0, dtype};
+    const GemmArgs g{nullptr, c, a, b, nullptr, m, n, k, n, lda, ldb, ldc, 0, dtype};
     if (!a_mn_major && !b_mn_major) return launch_gemm_dtype<kEpiPlain, false, false>(g, di, s);
     if (!a_mn_major && b_mn_major) return launch_gemm_dtype<kEpiPlain, false, true>(g, di, s);
     if (a_mn_major && !b_mn_major) return launch_gemm_dtype<kEpiPlain, true, false>(g, di, s);
@@ -489,7 +546,7 @@ extern "C" int mgr_swiglu_fused_fwd(void* h, const void* x, const void* w12, int
     if (!aligned_to(h, 16) || !aligned_to(x, 16) || !aligned_to(w12, 16)) return MGR_ERR_MISALIGNED;
     const DeviceInfo di = current_device_info();
     if (di.status != MGR_OK) return di.status;
-    const GemmArgs g{h, x, w12, nullptr, m, f, d, 2 * f, d, d, f, 0, dtype};
+    const GemmArgs g{nullptr, h, x, w12, nullptr, m, f, d, 2 * f, d, d, f, 0, dtype};
     return launch_gemm_dtype<kEpiSwiglu, false, false>(g, di, static_cast<cudaStream_t>(stream));
 }
 
@@ -502,6 +559,33 @@ extern "C" int mgr_swiglu_fused_bwd(void* dgv, const void* dh, const void* x, co
     if (!aligned_to(dgv, 16) || !aligned_to(dh, 16) || !aligned_to(x, 16) || !aligned_to(w12, 16)) return MGR_ERR_MISALIGNED;
     const DeviceInfo di = current_device_info();
     if (di.status != MGR_OK) return di.status;
-    const GemmArgs g{dgv, x, w12, dh, m, f, d, 2 * f, d, d, 2 * f, f, dtype};
+    const GemmArgs g{nullptr, dgv, x, w12, dh, m, f, d, 2 * f, d, d, 2 * f, f, dtype};
     return launch_gemm_dtype<kEpiSwigluBwd, false, false>(g, di, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mgr_swiglu_fused_fwd_save(void* h, void* gv, const void* x, const void* w12, int64_t m, int64_t d, int64_t f,
+                                         int dtype, void* stream) {
+    int st = gemm_check(m, f, d, dtype);
+    if (st != MGR_OK) return st;
+    if (m == 0) return MGR_OK;
+    if (h == nullptr || gv == nullptr || x == nullptr || w12 == nullptr) return MGR_ERR_NULL_PTR;
+    if (!aligned_to(h, 16) || !aligned_to(gv, 16) || !aligned_to(x, 16) || !aligned_to(w12, 16)) return MGR_ERR_MISALIGNED;
+    const DeviceInfo di = current_device_info();
+    if (di.status != MGR_OK) return di.status;
+    const GemmArgs g{gv, h, x, w12, nullptr, m, f, d, 2 * f, d, d, f, 2 * f, dtype};
+    return launch_gemm_dtype<kEpiSwigluSave, false, false>(g, di, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mgr_swiglu_dh_dgv(void* dgv, const void* dy, const void* w3, const void* gv, int64_t m, int64_t d, int64_t f,
+                                 int dtype, void* stream) {
+    int st = gemm_check(m, f, d, dtype);
+    if (st != MGR_OK) return st;
+    if (m == 0) return MGR_OK;
+    if (dgv == nullptr || dy == nullptr || w3 == nullptr || gv == nullptr) return MGR_ERR_NULL_PTR;
+    if (!aligned_to(dgv, 16) || !aligned_to(dy, 16) || !aligned_to(w3, 16) || !aligned_to(gv, 16)) return MGR_ERR_MISALIGNED;
+    const DeviceInfo di = current_device_info();
+    if (di.status != MGR_OK) return di.status;
+    // dh[m, f] = dy[m, d] w3[d, f]: A K-major (pitch d), B MN-major (stored [k = d, n = f], pitch f)
+    const GemmArgs g{nullptr, dgv, dy, w3, gv, m, f, d, f, d, f, 2 * f, 2 * f, dtype};
+    return launch_gemm_dtype<kEpiDhDgv, false, true>(g, di, static_cast<cudaStream_t>(stream));
 }

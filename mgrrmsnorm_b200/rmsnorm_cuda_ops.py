@@ -242,3 +242,44 @@ def swiglu_fused_backward(dh: torch.Tensor, x: torch.Tensor, w12: torch.Tensor, 
                                     _stream_ptr(x.device))
     _capi.check("fused SwiGLU backward kernel", st)
     return dgv
+
+
+def swiglu_fused_forward_save(x: torch.Tensor, w12: torch.Tensor, hidden_dim: int):
+    """(h[M, hidden], gv[M, 2*hidden]): the fused projection that also keeps the projection for backward,
+    as the reference keeps w12_out (megagemm/swiglu.py:98)."""
+    _check_input(x, "x")
+    _check_input(w12, "w12")
+    if x.dim() != 2 or w12.dim() != 2 or w12.shape[0] != 2 * hidden_dim or w12.shape[1] != x.shape[1]:
+        raise RuntimeError("expected x [M, d_model] and w12 [2*hidden_dim, d_model]")
+    if x.dtype != w12.dtype or x.device != w12.device:
+        raise RuntimeError("x and w12 must share dtype and device")
+    code = _dtype_code(x, "")
+    m, d = x.shape
+    L = _capi.lib()
+    with torch.cuda.device(x.device):
+        h = torch.empty((m, hidden_dim), device=x.device, dtype=x.dtype)
+        gv = torch.empty((m, 2 * hidden_dim), device=x.device, dtype=x.dtype)
+        st = L.mgr_swiglu_fused_fwd_save(h.data_ptr(), gv.data_ptr(), x.data_ptr(), w12.data_ptr(), m, d, hidden_dim, code,
+                                         _stream_ptr(x.device))
+    _capi.check("fused SwiGLU projection kernel", st)
+    return h, gv
+
+
+def swiglu_dh_dgv(dy: torch.Tensor, w3: torch.Tensor, gv: torch.Tensor, hidden_dim: int) -> torch.Tensor:
+    """[d_gate | d_val] of shape [M, 2*hidden] from dy [M, d_model], w3 [d_model, hidden] and the stored
+    projection gv: the dh = dy w3 GEMM with the activation backward as its epilogue."""
+    for t, nme in ((dy, "dy"), (w3, "w3"), (gv, "gv")):
+        _check_input(t, nme)
+    m, d = dy.shape
+    if tuple(w3.shape) != (d, hidden_dim) or tuple(gv.shape) != (m, 2 * hidden_dim):
+        raise RuntimeError("expected dy [M, d_model], w3 [d_model, hidden], gv [M, 2*hidden]")
+    if not (dy.dtype == w3.dtype == gv.dtype) or not (dy.device == w3.device == gv.device):
+        raise RuntimeError("dy, w3 and gv must share dtype and device")
+    code = _dtype_code(dy, " for backward")
+    L = _capi.lib()
+    with torch.cuda.device(dy.device):
+        dgv = torch.empty_like(gv)
+        st = L.mgr_swiglu_dh_dgv(dgv.data_ptr(), dy.data_ptr(), w3.data_ptr(), gv.data_ptr(), m, d, hidden_dim, code,
+                                 _stream_ptr(dy.device))
+    _capi.check("fused dh/dGV kernel", st)
+    return dgv

@@ -37,38 +37,54 @@ class MegaGemmFunction(Function):
         return grad_input_flat.view(w12_out.shape), None
 
 
+def _recompute_projection() -> bool:
+    """MGR_MLP_RECOMPUTE=1 trades one more projection GEMM in backward for not keeping [M, 2*hidden]."""
+    import os
+
+    return os.environ.get("MGR_MLP_RECOMPUTE", "0") not in ("", "0")
+
+
 class SwiGLUMLPFunction(Function):
     """The whole MLP, y = w3(silu(x w1^T) * (x w2^T)), on the tensor-core kernels.
 
-    Forward: one fused kernel produces h = silu(gate) * value straight from the accumulators (the
-    [M, 2*hidden] projection the reference materialises between megagemm/swiglu.py:167 and :168 never
-    exists), then the w3 GEMM. Saved for backward: x, the weights and h -- not the projection, which
-    backward recomputes.
-    Backward follows the reference's autograd graph (Linear(w3) -> MegaGemmFunction -> Linear(w12)):
-    dh = dy w3, dW3 = dy^T h, [d_gate | d_val] from the recomputed projection and dh, dx = dGV w12,
-    dW12 = dGV^T x.
+    Forward: one fused kernel produces h = silu(gate) * value straight from the fp32 accumulators, then
+    the w3 GEMM. Without autograd (inference) the [M, 2*hidden] projection the reference materialises
+    between megagemm/swiglu.py:167 and :168 never exists. With autograd it is written once by the same
+    kernel and kept for backward, as the reference keeps w12_out (:98) -- unless MGR_MLP_RECOMPUTE=1,
+    in which case backward recomputes it tile by tile instead.
+    Backward follows the reference's autograd graph (Linear(w3) -> MegaGemmFunction -> Linear(w12)) in
+    four GEMM launches: dW3 = dy^T h; [d_gate | d_val] as the epilogue of dh = dy w3 (dh itself is
+    never stored); dx = dGV w12; dW12 = dGV^T x. No operand is transposed in memory.
     """
 
     @staticmethod
     def forward(ctx, x: torch.Tensor, w12: torch.Tensor, w3: torch.Tensor):
+        ops = rmsnorm_cuda_ops
         hidden = w3.shape[1]
         x2d = x.reshape(-1, x.shape[-1])
         if not x2d.is_contiguous():
             x2d = x2d.contiguous()
-        h = rmsnorm_cuda_ops.swiglu_fused_forward(x2d, w12, hidden)
-        y = rmsnorm_cuda_ops.linear_tn(h, w3)
-        ctx.save_for_backward(x2d, w12, w3, h)
+        needs_grad = any(ctx.needs_input_grad)
+        keep = needs_grad and not _recompute_projection() and x2d.shape[0] % 8 == 0
+        if keep:
+            h, gv = ops.swiglu_fused_forward_save(x2d, w12, hidden)
+        else:
+            h, gv = ops.swiglu_fused_forward(x2d, w12, hidden), None
+        y = ops.linear_tn(h, w3)
+        if needs_grad:
+            ctx.save_for_backward(x2d, w12, w3, h, *([gv] if keep else []))
+        ctx.kept = keep
         ctx.x_shape = x.shape
         return y.view(x.shape[:-1] + (w3.shape[0],))
 
     @staticmethod
     def backward(ctx, grad_output: torch.Tensor):
-        x2d, w12, w3, h = ctx.saved_tensors
+        ops = rmsnorm_cuda_ops
+        x2d, w12, w3, h = ctx.saved_tensors[:4]
         hidden = w3.shape[1]
         dy = grad_output.reshape(-1, grad_output.shape[-1])
         if not dy.is_contiguous():
             dy = dy.contiguous()
-        ops = rmsnorm_cuda_ops
         m = x2d.shape[0]
         if m % 8 != 0:
             # dW = (.)^T (.) contracts over the M rows; the tensor-core kernel wants that length to be a
@@ -79,9 +95,12 @@ class SwiGLUMLPFunction(Function):
             dx = torch.matmul(dgv, w12).view(ctx.x_shape) if ctx.needs_input_grad[0] else None
             dw12 = torch.matmul(dgv.t(), x2d) if ctx.needs_input_grad[1] else None
             return dx, dw12, dw3
-        dh = ops.gemm(dy, w3, False, True)                                   # dy [M,D] x w3 [D,F]      -> [M, F]
         dw3 = ops.gemm(dy, h, True, True) if ctx.needs_input_grad[2] else None        # dy^T h     -> [D, F]
-        dgv = ops.swiglu_fused_backward(dh, x2d, w12, hidden)                # [d_gate | d_val]         -> [M, 2F]
+        if ctx.kept:
+            dgv = ops.swiglu_dh_dgv(dy, w3, ctx.saved_tensors[4], hidden)    # dh = dy w3, fused        -> [M, 2F]
+        else:
+            dh = ops.gemm(dy, w3, False, True)                               # dy [M,D] x w3 [D,F]      -> [M, F]
+            dgv = ops.swiglu_fused_backward(dh, x2d, w12, hidden)            # projection recomputed    -> [M, 2F]
         dx = ops.gemm(dgv, w12, False, True).view(ctx.x_shape) if ctx.needs_input_grad[0] else None   # -> [M, D]
         dw12 = ops.gemm(dgv, x2d, True, True) if ctx.needs_input_grad[1] else None    # dgv^T x   -> [2F, D]
         return dx, dw12, dw3

@@ -1,0 +1,98 @@
+"""Row-sharded RMSNorm and tensor-parallel SwiGLU on two real GPUs (NCCL), against the single-GPU
+result of the same library. Skipped with fewer than two devices. Ranks are child processes; they meet
+only in collectives between kernels, NVLS is switched off, and nothing waits on a peer inside a kernel."""
+import os
+import socket
+
+import pytest
+import torch
+import torch.multiprocessing as mp
+
+pytestmark = pytest.mark.gpu
+
+
+def _free_port() -> int:
+    with socket.socket() as s:
+        s.bind(("127.0.0.1", 0))
+        return s.getsockname()[1]
+
+
+def _worker(rank: int, world: int, port: int, q):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port), NCCL_NVLS_ENABLE="0")
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        from mgrrmsnorm_b200 import MegaGemmTriton, RMSNorm, sharding
+
+        # ---- row-sharded RMSNorm: 2 x 1500 rows of hidden 4096, bf16
+        g = torch.Generator().manual_seed(1234)
+        rows, cols = 3000, 4096
+        x = (2 ** 0.5 * torch.randn(rows, cols, generator=g)).bfloat16()
+        w = (1 + 0.1 * torch.randn(cols, generator=g)).bfloat16()
+        dy = torch.randn(rows, cols, generator=g).bfloat16()
+        full = RMSNorm(cols, epsilon=1e-6).to(dev).bfloat16()
+        shard = sharding.RowShardedRMSNorm(cols, epsilon=1e-6).to(dev).bfloat16()
+        with torch.no_grad():
+            full.weight.copy_(w.to(dev))
+            shard.weight.copy_(w.to(dev))
+        xf = x.to(dev).requires_grad_(True)
+        yf = full(xf)
+        yf.backward(dy.to(dev))
+        r0, r1 = sharding.row_shard(rows, world, rank)
+        xs = x[r0:r1].to(dev).requires_grad_(True)
+        ys = shard(xs)
+        ys.backward(dy[r0:r1].to(dev))
+        ok_rows = torch.equal(ys, yf[r0:r1]) and torch.equal(xs.grad, xf.grad[r0:r1])
+        # fp32 partial sums are added across ranks before the single rounding: at most one bf16 ulp from
+        # the one-GPU result (a different fp32 summation order next to a rounding boundary)
+        dws, dwf = shard.weight.grad.float(), full.weight.grad.float()
+        ulp = torch.maximum(dws.abs(), dwf.abs()) * 2.0 ** -7
+        ok_dw = bool(((dws - dwf).abs() <= ulp).all()) and float((dws != dwf).float().mean()) < 0.05
+
+        # ---- tensor-parallel MLP: d_model 512, hidden 1024 split over 2 ranks, fp16
+        torch.manual_seed(7)
+        mlp = MegaGemmTriton(512, multiple_of=256, hidden_multiple=2.0).to(dev).half()
+        for p in mlp.parameters():            # same weights on every rank
+            dist.broadcast(p.data, src=0)
+        tp = sharding.TensorParallelSwiGLU.from_full(mlp, world, rank)
+        xm = torch.randn(256, 512, generator=g).half()
+        dym = torch.randn(256, 512, generator=g).half()
+        a = xm.to(dev).requires_grad_(True)
+        ya = mlp(a)
+        ya.backward(dym.to(dev))
+        b = xm.to(dev).requires_grad_(True)
+        yb = tp(b)
+        yb.backward(dym.to(dev))
+        f0, f1 = sharding.tp_hidden_slice(mlp.hidden, world, rank)
+        tol = 2e-2
+        ok_y = float((ya.float() - yb.float()).abs().max()) < tol
+        ok_dx = float((a.grad.float() - b.grad.float()).abs().max()) < tol
+        gw12 = torch.cat([mlp.w12.weight.grad[f0:f1], mlp.w12.weight.grad[mlp.hidden + f0:mlp.hidden + f1]])
+        ok_w12 = float((gw12.float() - tp.local.w12.weight.grad.float()).abs().max()) < 5e-2
+        ok_w3 = float((mlp.w3.weight.grad[:, f0:f1].float() - tp.local.w3.weight.grad.float()).abs().max()) < 5e-2
+        torch.cuda.synchronize()
+        q.put((rank, ok_rows, ok_dw, ok_y, ok_dx, ok_w12, ok_w3))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_sharded_paths_on_two_gpus(built_lib):
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    for r in results:
+        assert all(r[1:]), f"rank {r[0]}: rows/dw/y/dx/dw12/dw3 = {r[1:]}"

@@ -234,3 +234,52 @@ def test_config4_shape_forward_backward(dtype):
     for got, want in ((mlp.w12.weight.grad, w12r.grad), (mlp.w3.weight.grad, w3r.grad)):
         scale = max(1.0, float(want.abs().max()))
         assert float((got.float() - want).abs().max()) < 1e-2 * scale
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("m,d,f", [(128, 64, 128), (200, 256, 384), (1024, 4096, 6912), (296, 512, 1000)])
+def test_kept_projection_forward_and_fused_dh_backward(ops, built_lib, dtype, m, d, f):
+    """Training pair: the forward that also stores [gate | val], and the dh = dy w3 GEMM whose epilogue
+    turns dh (fp32, in tensor memory) and the stored projection into [d_gate | d_val]."""
+    g = torch.Generator().manual_seed(m + d + f + 2)
+    td = TORCH_DTYPES[dtype]
+    x = torch.randn(m, d, generator=g).to(td)
+    w12 = (torch.randn(2 * f, d, generator=g) / d ** 0.5).to(td)
+    w3 = (torch.randn(d, f, generator=g) / f ** 0.5).to(td)
+    dy = torch.randn(m, d, generator=g).to(td)
+    h, gv = ops.swiglu_fused_forward_save(x.cuda(), w12.cuda(), f)
+    assert torch.equal(h, ops.swiglu_fused_forward(x.cuda(), w12.cuda(), f)), "h must not depend on whether gv is kept"
+    gv64 = oracle.linear(to_np(x), to_np(w12))
+    err = np.abs(to_np(gv).astype(np.float64) - gv64)
+    assert float(err.max()) <= gemm_tolerance(d, dtype, float(np.abs(gv64).max())), float(err.max())
+    # backward from the STORED (rounded) projection, like the reference's kernel reads w12_out
+    dgv = to_np(ops.swiglu_dh_dgv(dy.cuda(), w3.cuda(), gv, f)).astype(np.float64)
+    dh64 = to_np(dy).astype(np.float64) @ to_np(w3).astype(np.float64)
+    want = oracle._act_bwd_f64(dh64, to_np(gv).astype(np.float64), f)
+    err = np.abs(dgv - want)
+    assert float(err.max()) <= gemm_tolerance(d, dtype, float(np.abs(want).max())) + 1e-4, float(err.max())
+    assert built_lib.mgr_device_status(1) == 0
+
+
+@pytest.mark.parametrize("recompute", ["0", "1"])
+def test_module_backward_modes_agree_with_oracle(monkeypatch, recompute):
+    """MGR_MLP_RECOMPUTE selects between keeping the projection and recomputing it; both must meet the
+    same tolerances against the fp64 oracle."""
+    from megagemm import MegaGemmTriton
+
+    monkeypatch.setenv("MGR_MLP_RECOMPUTE", recompute)
+    torch.manual_seed(11)
+    mlp = MegaGemmTriton(256, multiple_of=128).cuda().bfloat16()
+    g = torch.Generator().manual_seed(12)
+    x = torch.randn(3, 64, 256, generator=g).bfloat16()
+    dy = torch.randn(3, 64, 256, generator=g).bfloat16()
+    xin = x.cuda().requires_grad_(True)
+    y = mlp(xin)
+    y.backward(dy.cuda())
+    out = oracle.swiglu_mlp(to_np(x).reshape(-1, 256), to_np(mlp.w12.weight), to_np(mlp.w3.weight), dy=to_np(dy).reshape(-1, 256))
+    assert float(np.abs(to_np(y).reshape(-1, 256) - out["y"]).max()) < 2e-2
+    assert float(np.abs(to_np(xin.grad).reshape(-1, 256) - out["dx"]).max()) < 2e-2
+    for got, key in ((mlp.w12.weight.grad, "dw12"), (mlp.w3.weight.grad, "dw3")):
+        assert float(np.abs(to_np(got) - out[key]).max()) < 2e-2 * max(1.0, float(np.abs(out[key]).max())), key
+    with torch.no_grad():
+        assert torch.equal(mlp(x.cuda()), y.detach()), "inference forward must equal the training forward"
