@@ -20,10 +20,11 @@
 //               also owns the TMEM allocation (512 columns = two 128x256 accumulators)
 //   warps 2-5 : epilogue      -- tcgen05.ld the finished accumulator, apply the epilogue, store; the second
 //               accumulator lets the next tile's main loop run meanwhile.
-// No cluster, no multicast. Every mbarrier wait is bounded (mgr_ptx.cuh).
+// Every CTA issues its own loads. Every mbarrier wait is bounded (mgr_ptx.cuh).
 
 #include <cuda.h>
 
+#include <cstdlib>
 #include <type_traits>
 
 #include "mgr_common.cuh"
@@ -37,12 +38,16 @@ __device__ int g_gemm_status = 0;
 constexpr int kBM = 128;         // tile rows (UMMA M)
 constexpr int kBN = 256;         // accumulator columns per tile (UMMA N)
 constexpr int kBK = 64;          // K per stage: 64 x 2 B = one 128-byte swizzle row
-constexpr int kStages = 4;
 constexpr int kUmmaK = 16;       // K of one tcgen05.mma for 16-bit operands
-constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB
-constexpr uint32_t kBBytes = kBN * kBK * 2;   // 32 KB
-constexpr uint32_t kStageBytes = kABytes + kBBytes;
-constexpr uint32_t kGemmSmem = kStages * kStageBytes + 1024;  // + slack to align the ring to 1024 B
+constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB: this CTA's 128 rows of A
+constexpr uint32_t kBBytes = kBN * kBK * 2;   // 32 KB: all 256 rows of B (a CTA pair holds half each)
+// CG = CTAs that share one MMA (tcgen05 cta_group): 1, or 2 = a pair of CTAs in one cluster working on a
+// 256 x 256 tile, each loading its own A rows and HALF of the B rows, which halves the B traffic per CTA
+// and deepens the ring from 4 to 7 stages.
+__host__ __device__ constexpr uint32_t stage_bytes(int cg) { return kABytes + kBBytes / cg; }
+__host__ __device__ constexpr int num_stages(int cg) { return cg == 1 ? 4 : 7; }
+__host__ __device__ constexpr uint32_t gemm_smem(int cg) { return num_stages(cg) * stage_bytes(cg) + 1024; }  // + slack to align to 1024 B
+constexpr int kMaxStages = 7;
 constexpr int kGemmThreads = 192;
 constexpr uint32_t kTmemCols = 512;
 
@@ -75,10 +80,10 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr, bool mn_
 
 // Instruction descriptor, kind::f16: fp32 accumulator (bits [4,6) = 1), operand formats at [7,10) and
 // [10,13) (0 = fp16, 1 = bf16), A / B major-ness at bits 15 / 16 (1 = MN-major), N>>3 at [17,23),
-// M>>4 at [24,29). M=128, N=256.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, bool a_mn, bool b_mn) {
+// M>>4 at [24,29). N=256; M=128, or 256 for a CTA pair.
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, bool a_mn, bool b_mn, int cg) {
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u) |
-           (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>(kBM >> 4) << 24);
+           (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>((kBM * cg) >> 4) << 24);
 }
 
 __device__ __forceinline__ float sigmoid_(float g) { return 1.0f / (1.0f + __expf(-g)); }
@@ -94,13 +99,24 @@ template <> __device__ __forceinline__ uint32_t pack2<__nv_bfloat16>(float a, fl
     return *reinterpret_cast<uint32_t*>(&h);
 }
 
-// C tile coordinates of linear tile index t: M index runs fastest so that the CTAs running at the same
-// time share a few B (weight) tiles and all of A through L2.
+// C tile coordinates of linear tile index t. Tiles are walked in bands of kBandRows rows of C: inside a
+// band the M index runs fastest, then N; then the next band. The CTAs running at one time therefore cover
+// a roughly square patch of C (about 2048 rows x 2300 columns on 148 SMs), so the A rows and B rows they
+// stream fit in L2 together and each is fetched from HBM about once per band instead of once per N tile
+// (which is what an M-fastest walk over a tall C costs, e.g. dW12 with 16384 rows).
+constexpr int kBandRows = 2048;
 struct TileCoord {
     int m0, n0;
 };
-__device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_step) {
-    return TileCoord{(t % m_tiles) * kBM, (t / m_tiles) * n_step};
+__device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_tiles, int n_step, int m_step) {
+    const int band = kBandRows / m_step;                 // M tiles per band
+    const int per_band = band * n_tiles;
+    const int b = t / per_band;
+    const int r = t - b * per_band;
+    const int rows_here = m_tiles - b * band < band ? m_tiles - b * band : band;   // the last band may be short
+    const int mi = b * band + r % rows_here;
+    const int ni = r / rows_here;
+    return TileCoord{mi * m_step, ni * n_step};
 }
 
 // C = op(A) op(B)^T on one 128 x 256 accumulator tile per step.
@@ -115,21 +131,27 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_step) 
 //                [M, 2 n_out] (pitch ld_aux) -- the training forward, whose backward reads it back.
 // kEpiDhDgv    : plain tile (256 columns); acc = dh tile; aux = stored projection [G | V] (pitch ld_aux);
 //                C = [d_gate | d_val] of shape [M, 2 n_out]. dh itself is never written.
-template <int EPI, bool A_MN, bool B_MN, typename T>
+template <int EPI, bool A_MN, bool B_MN, int CG, typename T>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, T* __restrict__ C,
             T* __restrict__ C2, const T* __restrict__ aux, int M, int n_out, int K, int64_t ldc, int64_t ld_aux,
             int* __restrict__ status) {
     static_assert(n_step_of(EPI) == kBN || !B_MN, "the gate/value split reads w12 K-major");
     constexpr int kNStep = n_step_of(EPI);  // output columns per tile
+    constexpr int kStages = num_stages(CG);
+    constexpr uint32_t kStageBytes = stage_bytes(CG);
     extern __shared__ unsigned char smem_raw[];
-    __shared__ __align__(8) uint64_t bar_full[kStages], bar_empty[kStages], bar_tfull[2], bar_tempty[2];
+    __shared__ __align__(8) uint64_t bar_full[kMaxStages], bar_empty[kMaxStages], bar_tfull[2], bar_tempty[2];
     __shared__ uint32_t tmem_base_slot;
     __shared__ int abort_flag;
 
     const uint32_t ring = (ptx::smem_addr(smem_raw) + 1023u) & ~1023u;
     const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
-    const int m_tiles = (M + kBM - 1) / kBM;
+    // In a pair, rank 0 is the leader: it owns the "full" and "accumulator free" barriers and issues the MMAs.
+    const uint32_t cta_rank = CG == 2 ? ptx::cluster_ctarank() : 0u;
+    const int first_tile = static_cast<int>(blockIdx.x) / CG;   // pairs walk the tile list together
+    const int tile_stride = static_cast<int>(gridDim.x) / CG;
+    const int m_tiles = (M + kBM * CG - 1) / (kBM * CG);
     const int n_tiles = (n_out + kNStep - 1) / kNStep;
     const int num_tiles = m_tiles * n_tiles;
     const int num_kb = (K + kBK - 1) / kBK;
@@ -142,18 +164,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(ptx::smem_addr(&bar_tfull[a]), 1);
-            ptx::mbar_init(ptx::smem_addr(&bar_tempty[a]), 4);
+            ptx::mbar_init(ptx::smem_addr(&bar_tempty[a]), 4 * CG);   // 4 epilogue warps per CTA
         }
         ptx::fence_mbar_init();
         ptx::prefetch_tmap(&tmA);
         ptx::prefetch_tmap(&tmB);
     }
     if (warp == 1) {
-        ptx::tmem_alloc(ptx::smem_addr(&tmem_base_slot), kTmemCols);
-        ptx::tmem_relinquish();
+        if constexpr (CG == 2) {
+            ptx::tmem_alloc_pair(ptx::smem_addr(&tmem_base_slot), kTmemCols);
+            ptx::tmem_relinquish_pair();
+        } else {
+            ptx::tmem_alloc(ptx::smem_addr(&tmem_base_slot), kTmemCols);
+            ptx::tmem_relinquish();
+        }
     }
     ptx::tc_fence_before_sync();
     __syncthreads();
+    if constexpr (CG == 2) ptx::cluster_sync();   // the partner's barriers exist before anything signals them
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
 
@@ -163,31 +191,53 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
-                const TileCoord tc = tile_coord(t, m_tiles, kNStep);
-                const int b_row1 = kNStep == kBN ? tc.n0 + kBN / 2 : n_out + tc.n0;
+            for (int t = first_tile; ok && t < num_tiles; t += tile_stride) {
+                const TileCoord tc = tile_coord(t, m_tiles, n_tiles, kNStep, kBM * CG);
+                const int m0 = tc.m0 + static_cast<int>(cta_rank) * kBM;     // this CTA's rows of the tile
+                const int b_row1 = kNStep == kBN ? tc.n0 + kBN / 2 : n_out + tc.n0;   // second half of the B rows
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(ptx::smem_addr(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
                         ok = false;
                         break;
                     }
-                    const uint32_t full = ptx::smem_addr(&bar_full[stage]);
                     const uint32_t sa = ring + stage * kStageBytes;
                     const uint32_t sb = sa + kABytes;
                     const int k0 = kb * kBK;
-                    ptx::mbar_arrive_expect_tx(full, kStageBytes);
-                    if constexpr (!A_MN) {
-                        ptx::tma_load_2d(sa, &tmA, k0, tc.m0, full);
-                    } else {
+                    if constexpr (CG == 1) {
+                        const uint32_t full = ptx::smem_addr(&bar_full[stage]);
+                        ptx::mbar_arrive_expect_tx(full, kStageBytes);
+                        if constexpr (!A_MN) {
+                            ptx::tma_load_2d(sa, &tmA, k0, m0, full);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < kBM / 64; ++c) ptx::tma_load_2d(sa + c * 8192u, &tmA, tc.m0 + 64 * c, k0, full);
-                    }
-                    if constexpr (!B_MN) {
-                        ptx::tma_load_2d(sb, &tmB, k0, tc.n0, full);
-                        ptx::tma_load_2d(sb + kBBytes / 2, &tmB, k0, b_row1, full);
-                    } else {
+                            for (int c = 0; c < kBM / 64; ++c) ptx::tma_load_2d(sa + c * 8192u, &tmA, m0 + 64 * c, k0, full);
+                        }
+                        if constexpr (!B_MN) {
+                            ptx::tma_load_2d(sb, &tmB, k0, tc.n0, full);
+                            ptx::tma_load_2d(sb + kBBytes / 2, &tmB, k0, b_row1, full);
+                        } else {
 #pragma unroll
-                        for (int c = 0; c < kBN / 64; ++c) ptx::tma_load_2d(sb + c * 8192u, &tmB, tc.n0 + 64 * c, k0, full);
+                            for (int c = 0; c < kBN / 64; ++c) ptx::tma_load_2d(sb + c * 8192u, &tmB, tc.n0 + 64 * c, k0, full);
+                        }
+                    } else {
+                        // Both CTAs' bytes are counted on the LEADER's barrier: the leader announces the total,
+                        // the partner only loads. (Bytes that land before the announcement leave the count
+                        // negative for a moment; the phase cannot complete before the leader's arrival.)
+                        const uint32_t full = ptx::map_to_cta(ptx::smem_addr(&bar_full[stage]), 0);
+                        if (cta_rank == 0) ptx::mbar_arrive_expect_tx(ptx::smem_addr(&bar_full[stage]), 2 * kStageBytes);
+                        if constexpr (!A_MN) {
+                            ptx::tma_load_2d_pair(sa, &tmA, k0, m0, full);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < kBM / 64; ++c) ptx::tma_load_2d_pair(sa + c * 8192u, &tmA, m0 + 64 * c, k0, full);
+                        }
+                        if constexpr (!B_MN) {   // this CTA's half of the B rows
+                            ptx::tma_load_2d_pair(sb, &tmB, k0, cta_rank == 0 ? tc.n0 : b_row1, full);
+                        } else {
+#pragma unroll
+                            for (int c = 0; c < kBN / 128; ++c)
+                                ptx::tma_load_2d_pair(sb + c * 8192u, &tmB, tc.n0 + static_cast<int>(cta_rank) * (kBN / 2) + 64 * c, k0, full);
+                        }
                     }
                     if (++stage == kStages) {
                         stage = 0;
@@ -198,14 +248,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
-        if (ptx::elect_one()) {
-            constexpr uint32_t idesc = instr_desc(std::is_same<T, __nv_bfloat16>::value ? 1u : 0u, A_MN, B_MN);
+        if (cta_rank == 0 && ptx::elect_one()) {
+            constexpr uint32_t idesc = instr_desc(std::is_same<T, __nv_bfloat16>::value ? 1u : 0u, A_MN, B_MN, CG);
             constexpr uint32_t a_step = A_MN ? (2048u >> 4) : (32u >> 4);  // start-address step per K=16 slice
             constexpr uint32_t b_step = B_MN ? (2048u >> 4) : (32u >> 4);
             int stage = 0, acc = 0;
             uint32_t phase = 0, acc_phase = 0;
             bool ok = true;
-            for (int t = blockIdx.x; ok && t < num_tiles; t += gridDim.x) {
+            for (int t = first_tile; ok && t < num_tiles; t += tile_stride) {
                 if (!ptx::mbar_wait(ptx::smem_addr(&bar_tempty[acc]), acc_phase ^ 1u, &abort_flag)) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * kBN;
@@ -219,15 +269,22 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     const uint64_t da = smem_desc_sw128(sa, A_MN);
                     const uint64_t db = smem_desc_sw128(sa + kABytes, B_MN);
 #pragma unroll
-                    for (int k = 0; k < kBK / kUmmaK; ++k)
-                        ptx::umma_f16(d_tmem, da + a_step * k, db + b_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                    ptx::umma_commit(ptx::smem_addr(&bar_empty[stage]));  // stage free once these MMAs retire
+                    for (int k = 0; k < kBK / kUmmaK; ++k) {
+                        if constexpr (CG == 2) ptx::umma_f16_pair(d_tmem, da + a_step * k, db + b_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        else ptx::umma_f16(d_tmem, da + a_step * k, db + b_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                    }
+                    // stage free (in both CTAs of a pair) once these MMAs retire
+                    if constexpr (CG == 2) ptx::umma_commit_pair(ptx::smem_addr(&bar_empty[stage]), 3);
+                    else ptx::umma_commit(ptx::smem_addr(&bar_empty[stage]));
                     if (++stage == kStages) {
                         stage = 0;
                         phase ^= 1u;
                     }
                 }
-                if (ok) ptx::umma_commit(ptx::smem_addr(&bar_tfull[acc]));  // accumulator complete
+                if (ok) {   // accumulator complete (each CTA of a pair holds its own 128 rows of it)
+                    if constexpr (CG == 2) ptx::umma_commit_pair(ptx::smem_addr(&bar_tfull[acc]), 3);
+                    else ptx::umma_commit(ptx::smem_addr(&bar_tfull[acc]));
+                }
                 acc ^= 1;
                 if (acc == 0) acc_phase ^= 1u;
             }
@@ -237,11 +294,11 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         const int q = warp & 3;  // TMEM lane quarter this warp may read: lanes [32q, 32q+32)
         int acc = 0;
         uint32_t acc_phase = 0;
-        for (int t = blockIdx.x; t < num_tiles; t += gridDim.x) {
-            const TileCoord tc = tile_coord(t, m_tiles, kNStep);
+        for (int t = first_tile; t < num_tiles; t += tile_stride) {
+            const TileCoord tc = tile_coord(t, m_tiles, n_tiles, kNStep, kBM * CG);
             if (!ptx::mbar_wait(ptx::smem_addr(&bar_tfull[acc]), acc_phase, &abort_flag)) break;
             ptx::tc_fence_after_sync();
-            const int row = tc.m0 + q * 32 + lane;
+            const int row = tc.m0 + static_cast<int>(cta_rank) * kBM + q * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * kBN;
             T* crow = C + static_cast<int64_t>(row) * ldc + tc.n0;
 #pragma unroll 1
@@ -367,7 +424,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) ptx::mbar_arrive(ptx::smem_addr(&bar_tempty[acc]));
+            if (lane == 0) {   // the accumulator is free when all 4 (pair: 8) epilogue warps have drained it
+                if (CG == 2 && cta_rank != 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&bar_tempty[acc]), 0));
+                else ptx::mbar_arrive(ptx::smem_addr(&bar_tempty[acc]));
+            }
             acc ^= 1;
             if (acc == 0) acc_phase ^= 1u;
         }
@@ -375,9 +435,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 
     ptx::tc_fence_before_sync();
     __syncthreads();
+    // A pair leaves together: the leader's MMAs read the partner's shared memory and the partner signals
+    // barriers in the leader's, so neither may exit (or free tensor memory) before both are done.
+    if constexpr (CG == 2) ptx::cluster_sync();
     if (warp == 1) {
         ptx::tc_fence_after_sync();
-        ptx::tmem_dealloc(tmem_base, kTmemCols);
+        if constexpr (CG == 2) ptx::tmem_dealloc_pair(tmem_base, kTmemCols);
+        else ptx::tmem_dealloc(tmem_base, kTmemCols);
     }
     if (threadIdx.x == 0 && abort_flag != 0) atomicExch(status, MGR_ERR_DEVICE_TIMEOUT);
 }
@@ -448,11 +512,19 @@ struct GemmArgs {
     int dtype;
 };
 
-template <int EPI, bool A_MN, bool B_MN, typename T>
+// MGR_GEMM_CTA_GROUP=1|2 pins the single-CTA or the CTA-pair kernels; unset = automatic.
+int forced_cta_group() {
+    const char* e = std::getenv("MGR_GEMM_CTA_GROUP");
+    if (e == nullptr) return 0;
+    return e[0] == '2' ? 2 : (e[0] == '1' ? 1 : 0);
+}
+
+template <int EPI, bool A_MN, bool B_MN, int CG, typename T>
 int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     static bool attr[kMaxDevices] = {false};
+    constexpr uint32_t kGemmSmem = gemm_smem(CG);
     if (!attr[di.device]) {
-        if (cudaFuncSetAttribute(gemm_kernel<EPI, A_MN, B_MN, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemm_kernel<EPI, A_MN, B_MN, CG, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kGemmSmem)) != cudaSuccess) {
             (void)cudaGetLastError();
             return MGR_ERR_CUDA;
@@ -466,18 +538,62 @@ int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     int* status = gemm_status_ptr(di);
     if (status == nullptr) return MGR_ERR_CUDA;
     constexpr int n_step = n_step_of(EPI);
-    const int64_t tiles = ((g.m + kBM - 1) / kBM) * ((g.n_out + n_step - 1) / n_step);
-    const unsigned grid = static_cast<unsigned>(tiles < di.sm_count ? tiles : di.sm_count);
-    gemm_kernel<EPI, A_MN, B_MN, T><<<grid, kGemmThreads, kGemmSmem, s>>>(
-        tmA, tmB, static_cast<T*>(g.c), static_cast<T*>(g.c2), static_cast<const T*>(g.aux), static_cast<int>(g.m), static_cast<int>(g.n_out),
-        static_cast<int>(g.k), g.ldc, g.ld_aux, status);
+    const int64_t tiles = ((g.m + kBM * CG - 1) / (kBM * CG)) * ((g.n_out + n_step - 1) / n_step);
+    const int64_t slots = di.sm_count / CG;   // CTAs (pairs) that can be resident at once
+    const unsigned grid = static_cast<unsigned>((tiles < slots ? tiles : slots) * CG);
+    T* c = static_cast<T*>(g.c);
+    T* c2 = static_cast<T*>(g.c2);
+    const T* aux = static_cast<const T*>(g.aux);
+    const int m = static_cast<int>(g.m), n_out = static_cast<int>(g.n_out), k = static_cast<int>(g.k);
+    if constexpr (CG == 1) {
+        gemm_kernel<EPI, A_MN, B_MN, 1, T><<<grid, kGemmThreads, kGemmSmem, s>>>(tmA, tmB, c, c2, aux, m, n_out, k, g.ldc, g.ld_aux, status);
+    } else {
+        cudaLaunchConfig_t cfg = {};
+        cfg.gridDim = dim3(grid);
+        cfg.blockDim = dim3(kGemmThreads);
+        cfg.dynamicSmemBytes = kGemmSmem;
+        cfg.stream = s;
+        cudaLaunchAttribute at[1];
+        at[0].id = cudaLaunchAttributeClusterDimension;
+        at[0].val.clusterDim.x = 2;
+        at[0].val.clusterDim.y = 1;
+        at[0].val.clusterDim.z = 1;
+        cfg.attrs = at;
+        cfg.numAttrs = 1;
+        if (cudaLaunchKernelEx(&cfg, gemm_kernel<EPI, A_MN, B_MN, 2, T>, tmA, tmB, c, c2, aux, m, n_out, k, g.ldc, g.ld_aux, status) != cudaSuccess) {
+            (void)cudaGetLastError();
+            return MGR_ERR_LAUNCH_FAILED;
+        }
+    }
     return launch_status();
+}
+
+// Choice between the single-CTA and the CTA-pair kernels, from measurements on B200 (1 kW power cap):
+//   * in cycles the pair kernels are clearly better: tensor pipe active 90-94 % against 77-79 % at 4096^3,
+//     15 % fewer cycles (deeper ring, half the B traffic per CTA);
+//   * a short burst of GEMMs (config 4: 0.2-0.4 ms each) runs near the maximum clock and gains from that:
+//     1.21 against 1.15 PFLOP/s for the whole MLP step;
+//   * a long run of large GEMMs (config 5 on one GPU: 5-10 ms each) is held at the power cap, where the pair
+//     kernels settle at about 1.0 GHz against 1.25 GHz for the single-CTA ones and lose 4 %
+//     (1.19 against 1.24 PFLOP/s).
+// Hence: pairs for GEMMs below 2 TFLOP of work, single CTAs above. MGR_GEMM_CTA_GROUP overrides.
+constexpr double kPairFlopLimit = 2.0e12;
+
+template <int EPI, bool A_MN, bool B_MN, typename T>
+int launch_gemm_cg(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
+    int cg = forced_cta_group();
+    if (cg == 0) {
+        const double flops = 2.0 * static_cast<double>(g.m) * static_cast<double>(g.b_rows) * static_cast<double>(g.k);
+        cg = flops < kPairFlopLimit ? 2 : 1;
+    }
+    if (cg == 2 && di.sm_count % 2 == 0) return launch_gemm<EPI, A_MN, B_MN, 2, T>(g, di, s);
+    return launch_gemm<EPI, A_MN, B_MN, 1, T>(g, di, s);
 }
 
 template <int EPI, bool A_MN, bool B_MN>
 int launch_gemm_dtype(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
-    if (g.dtype == MGR_F16) return launch_gemm<EPI, A_MN, B_MN, __half>(g, di, s);
-    return launch_gemm<EPI, A_MN, B_MN, __nv_bfloat16>(g, di, s);
+    if (g.dtype == MGR_F16) return launch_gemm_cg<EPI, A_MN, B_MN, __half>(g, di, s);
+    return launch_gemm_cg<EPI, A_MN, B_MN, __nv_bfloat16>(g, di, s);
 }
 
 int gemm_check(int64_t m, int64_t n, int64_t k, int dtype) {

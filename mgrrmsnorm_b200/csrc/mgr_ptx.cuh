@@ -87,7 +87,7 @@ __device__ __forceinline__ void bulk_copy_g2s(uint32_t dst_smem, const void* src
         : "memory");
 }
 
-// ---- tensor-map TMA load, 2-D tile -> shared (no multicast) -------------------------------------------
+// ---- tensor-map TMA load, 2-D tile -> this CTA's shared memory -------------------------------------------
 
 __device__ __forceinline__ void tma_load_2d(uint32_t dst_smem, const void* tmap, int32_t x, int32_t y, uint32_t bar) {
     asm volatile(
@@ -129,6 +129,72 @@ __device__ __forceinline__ void umma_f16(uint32_t d_tmem, uint64_t a_desc, uint6
 // Arrives (count 1) on the mbarrier once every tcgen05.mma issued so far by this thread has finished.
 __device__ __forceinline__ void umma_commit(uint32_t bar) {
     asm volatile("tcgen05.commit.cta_group::1.mbarrier::arrive::one.shared::cluster.b64 [%0];" ::"r"(bar) : "memory");
+}
+
+// ---- CTA pairs (cta_group::2): two CTAs of one cluster share one MMA -------------------------------
+
+__device__ __forceinline__ uint32_t cluster_ctarank() {
+    uint32_t r;
+    asm volatile("mov.u32 %0, %%cluster_ctarank;" : "=r"(r));
+    return r;
+}
+
+// shared::cluster address of the same shared-memory location in CTA `rank` of this cluster.
+__device__ __forceinline__ uint32_t map_to_cta(uint32_t smem_addr, uint32_t rank) {
+    uint32_t r;
+    asm volatile("mapa.shared::cluster.u32 %0, %1, %2;" : "=r"(r) : "r"(smem_addr), "r"(rank));
+    return r;
+}
+
+// All threads of all CTAs of the cluster. Not a bounded wait: every thread must reach it (all other
+// waits are bounded, so every thread does).
+__device__ __forceinline__ void cluster_sync() {
+    asm volatile("barrier.cluster.arrive.release.aligned;\n\tbarrier.cluster.wait.acquire.aligned;" ::: "memory");
+}
+
+// Arrive (count 1) on an mbarrier of another CTA of the cluster, given its shared::cluster address.
+__device__ __forceinline__ void mbar_arrive_cluster(uint32_t cluster_addr) {
+    asm volatile("mbarrier.arrive.release.cluster.shared::cluster.b64 _, [%0];" ::"r"(cluster_addr) : "memory");
+}
+
+// TMA tile load issued by one CTA of a pair into its OWN shared memory; the completion bytes go to the
+// mbarrier at `bar_cluster_addr`, which may live in the partner CTA. Each CTA loads only for itself.
+__device__ __forceinline__ void tma_load_2d_pair(uint32_t dst_smem, const void* tmap, int32_t x, int32_t y, uint32_t bar_cluster_addr) {
+    asm volatile(
+        "cp.async.bulk.tensor.2d.cta_group::2.shared::cluster.global.mbarrier::complete_tx::bytes [%0], [%1, {%3, %4}], [%2];"
+        ::"r"(dst_smem), "l"(tmap), "r"(bar_cluster_addr), "r"(x), "r"(y)
+        : "memory");
+}
+
+__device__ __forceinline__ void tmem_alloc_pair(uint32_t dst_smem, uint32_t ncols) {
+    asm volatile("tcgen05.alloc.cta_group::2.sync.aligned.shared::cta.b32 [%0], %1;" ::"r"(dst_smem), "r"(ncols) : "memory");
+}
+__device__ __forceinline__ void tmem_relinquish_pair() {
+    asm volatile("tcgen05.relinquish_alloc_permit.cta_group::2.sync.aligned;" ::: "memory");
+}
+__device__ __forceinline__ void tmem_dealloc_pair(uint32_t taddr, uint32_t ncols) {
+    asm volatile("tcgen05.dealloc.cta_group::2.sync.aligned.b32 %0, %1;" ::"r"(taddr), "r"(ncols) : "memory");
+}
+
+// One MMA over the pair: M = 256 (128 rows from each CTA's A tile), B's N rows split between the two
+// CTAs' shared memory, each CTA's tensor memory receives its own 128 rows of D. Issued by one thread of
+// the leader CTA (rank 0); descriptors are offsets valid in both CTAs.
+__device__ __forceinline__ void umma_f16_pair(uint32_t d_tmem, uint64_t a_desc, uint64_t b_desc, uint32_t idesc, uint32_t accumulate) {
+    asm volatile(
+        "{\n\t.reg .pred p;\n\t"
+        "setp.ne.b32 p, %4, 0;\n\t"
+        "tcgen05.mma.cta_group::2.kind::f16 [%0], %1, %2, %3, p;\n\t}\n"
+        ::"r"(d_tmem), "l"(a_desc), "l"(b_desc), "r"(idesc), "r"(accumulate)
+        : "memory");
+}
+
+// Arrives (count 1) on the mbarrier at the same offset in every CTA named by `cta_mask` once all MMAs
+// issued so far by this thread have finished.
+__device__ __forceinline__ void umma_commit_pair(uint32_t bar, uint16_t cta_mask) {
+    asm volatile(
+        "tcgen05.commit.cta_group::2.mbarrier::arrive::one.shared::cluster.multicast::cluster.b64 [%0], %1;"
+        ::"r"(bar), "h"(cta_mask)
+        : "memory");
 }
 
 // 32 lanes x 32 consecutive fp32 columns: thread i of the warp receives columns [c, c+32) of TMEM lane

@@ -6,7 +6,7 @@
 // in flight per SM are set by the ring depth, not by registers -- which is what a 16-32 KB row needs
 // to keep HBM3e busy. x (and dy) cross HBM exactly once per direction.
 //
-// No cluster, no multicast. Every mbarrier wait is bounded (mgr_ptx.cuh); a timeout raises the CTA's
+// One CTA per SM, each issuing its own copies. Every mbarrier wait is bounded (mgr_ptx.cuh); a timeout raises the CTA's
 // abort flag, sets *status and lets all roles fall out of their loops.
 #pragma once
 

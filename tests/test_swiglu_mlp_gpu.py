@@ -283,3 +283,38 @@ def test_module_backward_modes_agree_with_oracle(monkeypatch, recompute):
         assert float(np.abs(to_np(got) - out[key]).max()) < 2e-2 * max(1.0, float(np.abs(out[key]).max())), key
     with torch.no_grad():
         assert torch.equal(mlp(x.cuda()), y.detach()), "inference forward must equal the training forward"
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+@pytest.mark.parametrize("m,d,f", [(256, 64, 128), (128, 128, 256), (520, 256, 384), (1024, 1024, 1536), (296, 512, 1000)])
+def test_cta_pair_kernels_equal_single_cta_kernels(ops, built_lib, monkeypatch, dtype, m, d, f):
+    """MGR_GEMM_CTA_GROUP=2 runs every GEMM on pairs of CTAs sharing one MMA (256-row tiles, each CTA
+    loading half of B). The K order of the accumulation is the same, so every output must be bit-identical
+    to the single-CTA kernels' -- for all operand layouts and all epilogues."""
+    g = torch.Generator().manual_seed(m + d + f + 3)
+    td = TORCH_DTYPES[dtype]
+    x = torch.randn(m, d, generator=g).to(td).cuda()
+    w12 = (torch.randn(2 * f, d, generator=g) / d ** 0.5).to(td).cuda()
+    w3 = (torch.randn(d, f, generator=g) / f ** 0.5).to(td).cuda()
+    dy = torch.randn(m, d, generator=g).to(td).cuda()
+
+    def everything():
+        h, gv = ops.swiglu_fused_forward_save(x, w12, f)
+        out = {"h": h, "gv": gv, "h2": ops.swiglu_fused_forward(x, w12, f), "y": ops.linear_tn(h, w3)}
+        out["dh"] = ops.gemm(dy, w3, False, True)
+        out["dw3"] = ops.gemm(dy, h, True, True)
+        out["dgv"] = ops.swiglu_dh_dgv(dy, w3, gv, f)
+        out["dgv2"] = ops.swiglu_fused_backward(out["dh"], x, w12, f)
+        out["dx"] = ops.gemm(out["dgv"], w12, False, True)
+        out["dw12"] = ops.gemm(out["dgv"], x, True, True)
+        out["mn_k"] = ops.gemm(x.t().contiguous(), w12, True, False)     # MN-major A with K-major B
+        torch.cuda.synchronize()
+        return out
+
+    monkeypatch.setenv("MGR_GEMM_CTA_GROUP", "1")
+    one = everything()
+    monkeypatch.setenv("MGR_GEMM_CTA_GROUP", "2")
+    two = everything()
+    assert built_lib.mgr_device_status(1) == 0
+    for k in one:
+        assert torch.equal(one[k], two[k]), f"{k}: pair kernel differs, max |diff| {float((one[k].float() - two[k].float()).abs().max())}"
