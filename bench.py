@@ -306,12 +306,15 @@ def time_device_resident(bufsets, steps, warmup, world, sampler=None):
     return {"total_ms": total_ms, "fwd_ms": fwd_ms, "bwd_ms": bwd_ms, "window": (t0, t1)}
 
 
-def time_e2e(rows, cols, device, steps, warmup, world, src):
-    """Through the public API (RMSNorm module + autograd) with pinned host buffers: every step copies
-    x and dy host->device, runs forward and backward, and copies y, dx and dW back."""
+def time_e2e(rows, cols, device, steps, warmup, world, src, pipelined=True):
+    """Through the public API with pinned host buffers: every step copies x and dy host->device, runs
+    forward and backward, and copies y, dx and dW back. pipelined=True uses the library's host-tensor
+    entry (HostRMSNormPipeline: row chunks over three streams, inbound and outbound copies overlapped);
+    pipelined=False is the plain module call between two whole-tensor copies."""
     import torch.distributed as dist
 
     from mgrrmsnorm_b200 import RMSNorm
+    from mgrrmsnorm_b200.hostpipe import HostRMSNormPipeline
 
     dt = torch.bfloat16
     hx = torch.empty((rows, cols), dtype=dt).pin_memory()
@@ -325,8 +328,17 @@ def time_e2e(rows, cols, device, steps, warmup, world, src):
     with torch.no_grad():
         norm.weight.copy_(src.w)
     stream = torch.cuda.current_stream()
+    pipe = HostRMSNormPipeline(rows, cols, dt, device) if pipelined else None
+
+    def step_pipelined():
+        dw = pipe.run(hx, hdy, norm.weight.detach(), EPS, hy, hdx)
+        if world > 1:
+            dist.all_reduce(dw)
+        hdw.copy_(dw, non_blocking=True)
 
     def step():
+        if pipelined:
+            return step_pipelined()
         x = hx.to(device, non_blocking=True).requires_grad_(True)
         dy = hdy.to(device, non_blocking=True)
         norm.weight.grad = None
@@ -710,8 +722,10 @@ def main(argv=None) -> int:
 
     e2e = None
     if not args.no_e2e:
-        e2e = time_e2e(args.rows, HIDDEN, device, args.e2e_steps, 1, world, main_buf)
+        e2e = time_e2e(args.rows, HIDDEN, device, args.e2e_steps, 1, world, main_buf, pipelined=True)
         e2e_value = world * nb["total"] / (e2e["ms_per_step"] * 1e-3) / 1e9
+        e2e_plain = time_e2e(args.rows, HIDDEN, device, args.e2e_steps, 1, world, main_buf, pipelined=False)
+        e2e["unpipelined_value"] = world * nb["total"] / (e2e_plain["ms_per_step"] * 1e-3) / 1e9
 
     side = {}
     if world == 1 and not args.no_side:
@@ -740,7 +754,9 @@ def main(argv=None) -> int:
             "e2e": None if e2e is None else {
                 "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                 "ms_per_step": e2e["ms_per_step"], "steps": e2e["steps"],
-                "path": "pinned host -> RMSNorm module fwd+bwd -> pinned host (y, dx, dW)"},
+                "path": "pinned host x, dy -> HostRMSNormPipeline (8192-row chunks, copy-in / compute / copy-out streams) -> pinned host y, dx, dW",
+                "unpipelined_value": e2e["unpipelined_value"],
+                "unpipelined_path": "pinned host -> whole-tensor copies around the RMSNorm module fwd+bwd -> pinned host"},
             "gpu_launches": 3 * args.steps,
             "clocks": sampler.summary(*r["window"]) if sampler else None,
             "sm_count": sms.value,

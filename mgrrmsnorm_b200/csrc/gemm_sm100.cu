@@ -14,11 +14,12 @@
 //   * mgr_swiglu_fused_bwd  : recomputes the projection tile by tile and turns it, with the matching
 //     dh tile, into [d_gate | d_val] in the epilogue -- the projection is not stored in forward.
 //
-// Kernel shape (one CTA per SM, persistent over output tiles, 192 threads):
+// Kernel shape (one CTA per SM, persistent over output tiles, 320 threads):
 //   warp 0    : TMA producer  -- cp.async.bulk.tensor.2d into a 4-stage ring (A 128x64, B 256x64, 128B swizzle)
 //   warp 1    : MMA issuer    -- one elected thread issues tcgen05.mma (M128 N256 K16, fp32 accumulate);
 //               also owns the TMEM allocation (512 columns = two 128x256 accumulators)
-//   warps 2-5 : epilogue      -- tcgen05.ld the finished accumulator, apply the epilogue, store; the second
+//   warps 2-9 : epilogue      -- tcgen05.ld the finished accumulator, apply the epilogue, store (two warps per
+//               32-lane quarter of tensor memory, each taking half of the column chunks); the second
 //               accumulator lets the next tile's main loop run meanwhile.
 // Every CTA issues its own loads. Every mbarrier wait is bounded (mgr_ptx.cuh).
 
@@ -48,7 +49,8 @@ __host__ __device__ constexpr uint32_t stage_bytes(int cg) { return kABytes + kB
 __host__ __device__ constexpr int num_stages(int cg) { return cg == 1 ? 4 : 7; }
 __host__ __device__ constexpr uint32_t gemm_smem(int cg) { return num_stages(cg) * stage_bytes(cg) + 1024; }  // + slack to align to 1024 B
 constexpr int kMaxStages = 7;
-constexpr int kGemmThreads = 192;
+constexpr int kEpiWarps = 8;      // epilogue warps: two per 32-lane quarter of tensor memory
+constexpr int kGemmThreads = (2 + kEpiWarps) * 32;
 constexpr uint32_t kTmemCols = 512;
 
 enum Epilogue { kEpiPlain = 0, kEpiSwiglu = 1, kEpiSwigluBwd = 2, kEpiSwigluSave = 3, kEpiDhDgv = 4 };
@@ -164,7 +166,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         }
         for (int a = 0; a < 2; ++a) {
             ptx::mbar_init(ptx::smem_addr(&bar_tfull[a]), 1);
-            ptx::mbar_init(ptx::smem_addr(&bar_tempty[a]), 4 * CG);   // 4 epilogue warps per CTA
+            ptx::mbar_init(ptx::smem_addr(&bar_tempty[a]), kEpiWarps * CG);   // every epilogue warp of every CTA of the group
         }
         ptx::fence_mbar_init();
         ptx::prefetch_tmap(&tmA);
@@ -290,8 +292,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
         }
     } else {
-        // ---------------- epilogue (warps 2..5) ----------------
-        const int q = warp & 3;  // TMEM lane quarter this warp may read: lanes [32q, 32q+32)
+        // ---------------- epilogue (warps 2..9) ----------------
+        const int q = warp & 3;               // TMEM lane quarter this warp may read: lanes [32q, 32q+32)
+        const int chunk0 = (warp - 2) >> 2;   // the two warps of a quarter take the even / the odd 32-column chunks
         int acc = 0;
         uint32_t acc_phase = 0;
         for (int t = first_tile; t < num_tiles; t += tile_stride) {
@@ -301,8 +304,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const int row = tc.m0 + static_cast<int>(cta_rank) * kBM + q * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * kBN;
             T* crow = C + static_cast<int64_t>(row) * ldc + tc.n0;
+            [[maybe_unused]] uint4 gp_next[4], vp_next[4];   // kEpiDhDgv: packets requested one chunk ahead
 #pragma unroll 1
-            for (int c = 0; c < kNStep / 32; ++c) {
+            for (int c = chunk0; c < kNStep / 32; c += kEpiWarps / 4) {
                 if constexpr (EPI == kEpiSwigluBwd) {
                     uint32_t g[32], v[32];
                     ptx::tmem_ld_32x32(t_row + c * 32, g);
@@ -347,15 +351,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         }
                     }
                 } else if constexpr (EPI == kEpiDhDgv) {
+                    // The stored gate / value packets of the NEXT chunk are requested before this chunk is
+                    // worked on, so their latency (L2 or HBM) overlaps the arithmetic instead of heading it.
+                    constexpr int kStride = kEpiWarps / 4;
                     uint32_t a[32];
                     ptx::tmem_ld_32x32(t_row + c * 32, a);
+                    if (c == chunk0) {
+                        const T* grow = aux + static_cast<int64_t>(row) * ld_aux + tc.n0 + c * 32;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const bool on = row < M && tc.n0 + c * 32 + j * 8 < n_out;
+                            gp_next[j] = on ? ld_stream16(reinterpret_cast<const uint4*>(grow + j * 8)) : make_uint4(0, 0, 0, 0);
+                            vp_next[j] = on ? ld_stream16(reinterpret_cast<const uint4*>(grow + n_out + j * 8)) : make_uint4(0, 0, 0, 0);
+                        }
+                    }
                     uint4 gp[4], vp[4];
-                    const T* grow = aux + static_cast<int64_t>(row) * ld_aux + tc.n0 + c * 32;
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
-                        const bool on = row < M && tc.n0 + c * 32 + j * 8 < n_out;
-                        gp[j] = on ? *reinterpret_cast<const uint4*>(grow + j * 8) : make_uint4(0, 0, 0, 0);
-                        vp[j] = on ? *reinterpret_cast<const uint4*>(grow + n_out + j * 8) : make_uint4(0, 0, 0, 0);
+                        gp[j] = gp_next[j];
+                        vp[j] = vp_next[j];
+                    }
+                    if (c + kStride < kNStep / 32) {
+                        const int cn = c + kStride;
+                        const T* grow = aux + static_cast<int64_t>(row) * ld_aux + tc.n0 + cn * 32;
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) {
+                            const bool on = row < M && tc.n0 + cn * 32 + j * 8 < n_out;
+                            gp_next[j] = on ? ld_stream16(reinterpret_cast<const uint4*>(grow + j * 8)) : make_uint4(0, 0, 0, 0);
+                            vp_next[j] = on ? ld_stream16(reinterpret_cast<const uint4*>(grow + n_out + j * 8)) : make_uint4(0, 0, 0, 0);
+                        }
                     }
                     ptx::tmem_ld_wait();
 #pragma unroll
@@ -371,8 +395,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             dg[e] = dh * vv[e] * (sig * (1.0f + gg[e] * (1.0f - sig)));
                         }
                         if (row < M && tc.n0 + c * 32 + j * 8 < n_out) {
-                            *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) = pack16<T>(dg);
-                            *reinterpret_cast<uint4*>(crow + n_out + c * 32 + j * 8) = pack16<T>(dv);
+                            // read once / written once: streaming accesses keep the GEMM operands in L2
+                            st_stream16(reinterpret_cast<uint4*>(crow + c * 32 + j * 8), pack16<T>(dg));
+                            st_stream16(reinterpret_cast<uint4*>(crow + n_out + c * 32 + j * 8), pack16<T>(dv));
                         }
                     }
                 } else {
@@ -398,8 +423,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                             pg[e] = pack2<T>(__uint_as_float(g[j * 8 + 2 * e]), __uint_as_float(g[j * 8 + 2 * e + 1]));
                                             pv[e] = pack2<T>(__uint_as_float(v[j * 8 + 2 * e]), __uint_as_float(v[j * 8 + 2 * e + 1]));
                                         }
-                                        *reinterpret_cast<uint4*>(prow + j * 8) = make_uint4(pg[0], pg[1], pg[2], pg[3]);
-                                        *reinterpret_cast<uint4*>(prow + n_out + j * 8) = make_uint4(pv[0], pv[1], pv[2], pv[3]);
+                                        st_stream16(reinterpret_cast<uint4*>(prow + j * 8), make_uint4(pg[0], pg[1], pg[2], pg[3]));
+                                        st_stream16(reinterpret_cast<uint4*>(prow + n_out + j * 8), make_uint4(pv[0], pv[1], pv[2], pv[3]));
                                     }
                                 }
                             }
@@ -424,7 +449,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             }
             ptx::tc_fence_before_sync();
             __syncwarp();
-            if (lane == 0) {   // the accumulator is free when all 4 (pair: 8) epilogue warps have drained it
+            if (lane == 0) {   // the accumulator is free when every epilogue warp (of both CTAs of a pair) has drained it
                 if (CG == 2 && cta_rank != 0) ptx::mbar_arrive_cluster(ptx::map_to_cta(ptx::smem_addr(&bar_tempty[acc]), 0));
                 else ptx::mbar_arrive(ptx::smem_addr(&bar_tempty[acc]));
             }

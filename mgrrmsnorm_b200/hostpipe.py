@@ -1,0 +1,89 @@
+"""RMSNorm forward+backward over tensors that live in HOST memory.
+
+When x and dy sit in (pinned) host memory and y, dx have to end up there too, the step is bound by the
+PCIe link, not by the kernels: at 65536 x 8192 bf16 the copies move 4 GiB while the kernels need under a
+millisecond. Rows are independent, so the step is cut into row chunks and pipelined over three streams:
+
+    copy-in stream : x[c], dy[c]  host -> device      (chunk c+1 while chunk c computes)
+    compute stream : mgr_rmsnorm_fwd / mgr_rmsnorm_bwd on chunk c
+    copy-out stream: y[c], dx[c]  device -> host      (chunk c-1 meanwhile)
+
+PCIe is full duplex, so inbound and outbound copies overlap and the step takes about as long as the
+larger of the two directions instead of their sum. dW is the fp32 sum of the chunks' fp32 partial
+sums, added in chunk order (so it is bit-reproducible for a given chunking) and rounded once.
+
+The arithmetic is the library's (C ABI); torch supplies streams, events and memory only.
+"""
+from __future__ import annotations
+
+import torch
+
+from . import _capi
+from .rmsnorm_cuda_ops import _DTYPES
+
+
+class HostRMSNormPipeline:
+    """Reusable pipeline for one (rows, cols, dtype, device): device staging buffers are allocated once.
+
+    run(x_host, dy_host, weight_dev, eps, y_host, dx_host) -> dW (device tensor, weight dtype)
+    Host tensors should be pinned (torch.Tensor.pin_memory) for the copies to be asynchronous.
+    """
+
+    def __init__(self, rows: int, cols: int, dtype: torch.dtype, device: torch.device, chunk_rows: int = 8192, depth: int = 3):
+        if dtype not in _DTYPES:
+            raise RuntimeError("Unsupported dtype. Use float32, float16, or bfloat16.")
+        self.rows, self.cols, self.dtype, self.device = rows, cols, dtype, torch.device(device)
+        self.chunk = max(1, min(chunk_rows, rows))
+        self.depth = depth
+        self.code = _DTYPES[dtype]
+        self.L = _capi.lib()
+        with torch.cuda.device(self.device):
+            mk = lambda: torch.empty((self.chunk, cols), dtype=dtype, device=self.device)
+            self.slots = [dict(x=mk(), dy=mk(), y=mk(), dx=mk(), inv=torch.empty(self.chunk, dtype=torch.float32, device=self.device),
+                               loaded=torch.cuda.Event(), computed=torch.cuda.Event(), drained=torch.cuda.Event())
+                          for _ in range(depth)]
+            ws_bytes = int(self.L.mgr_rmsnorm_bwd_workspace_bytes(self.chunk, cols, self.code))
+            self.ws = torch.empty(max(ws_bytes, 16), dtype=torch.uint8, device=self.device)
+            self.dw_part = torch.empty(cols, dtype=torch.float32, device=self.device)
+            self.dw_sum = torch.empty(cols, dtype=torch.float32, device=self.device)
+            self.s_in = torch.cuda.Stream(self.device)
+            self.s_out = torch.cuda.Stream(self.device)
+
+    def run(self, x_host, dy_host, weight, eps: float, y_host, dx_host) -> torch.Tensor:
+        L, cols, code = self.L, self.cols, self.code
+        for t in (x_host, dy_host, y_host, dx_host):
+            if t.dtype != self.dtype or tuple(t.shape) != (self.rows, cols) or not t.is_contiguous():
+                raise RuntimeError("host tensors must be contiguous [rows, cols] of the pipeline's dtype")
+        if weight.dtype != self.dtype or weight.device != self.device or tuple(weight.shape) != (cols,):
+            raise RuntimeError("weight must be a device tensor [cols] of the pipeline's dtype")
+        main = torch.cuda.current_stream(self.device)
+        self.s_in.wait_stream(main)
+        self.s_out.wait_stream(main)
+        self.dw_sum.zero_()
+        nchunks = (self.rows + self.chunk - 1) // self.chunk
+        for c in range(nchunks):
+            r0 = c * self.chunk
+            n = min(self.chunk, self.rows - r0)
+            slot = self.slots[c % self.depth]
+            with torch.cuda.stream(self.s_in):
+                if c >= self.depth:
+                    self.s_in.wait_event(slot["drained"])       # the slot's previous outputs have left the device
+                slot["x"][:n].copy_(x_host[r0:r0 + n], non_blocking=True)
+                slot["dy"][:n].copy_(dy_host[r0:r0 + n], non_blocking=True)
+                slot["loaded"].record(self.s_in)
+            main.wait_event(slot["loaded"])
+            sp = main.cuda_stream
+            _capi.check("mgr_rmsnorm_fwd", L.mgr_rmsnorm_fwd(slot["y"].data_ptr(), slot["inv"].data_ptr(), slot["x"].data_ptr(),
+                                                             weight.data_ptr(), n, cols, float(eps), code, sp))
+            _capi.check("mgr_rmsnorm_bwd", L.mgr_rmsnorm_bwd(slot["dx"].data_ptr(), None, self.dw_part.data_ptr(), slot["dy"].data_ptr(),
+                                                             slot["x"].data_ptr(), weight.data_ptr(), slot["inv"].data_ptr(), n, cols,
+                                                             code, self.ws.data_ptr(), self.ws.numel(), sp))
+            self.dw_sum.add_(self.dw_part)                        # chunk order: fixed summation order
+            slot["computed"].record(main)
+            with torch.cuda.stream(self.s_out):
+                self.s_out.wait_event(slot["computed"])
+                y_host[r0:r0 + n].copy_(slot["y"][:n], non_blocking=True)
+                dx_host[r0:r0 + n].copy_(slot["dx"][:n], non_blocking=True)
+                slot["drained"].record(self.s_out)
+        main.wait_stream(self.s_out)
+        return self.dw_sum.to(self.dtype)

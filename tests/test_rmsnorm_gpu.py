@@ -336,3 +336,34 @@ def test_families_are_each_bit_reproducible(ops, monkeypatch, path):
             first = cur
         else:
             assert all(torch.equal(a, b) for a, b in zip(first, cur))
+
+
+def test_host_tensor_pipeline_matches_module(ops, monkeypatch):
+    """HostRMSNormPipeline (row chunks streamed over PCIe) against one whole-tensor call. With the kernel
+    family pinned (the automatic choice depends on the row count, which differs between a chunk and the
+    whole tensor) y and dx come from the same kernels on the same rows and are bit-identical; dW sums the
+    chunks' fp32 partials in chunk order, so it agrees up to fp32 reassociation before the single rounding,
+    and is itself reproducible."""
+    from mgrrmsnorm_b200.hostpipe import HostRMSNormPipeline
+
+    monkeypatch.setenv("MGR_RMSNORM_PATH", "reg")
+
+    rows, cols = 5000, 2048
+    x, w, dy = seeded_rmsnorm_inputs(rows, cols, "bf16", 99)
+    xd, wd, dyd = x.cuda(), w.cuda(), dy.cuda()
+    y, inv = ops.rmsnorm_forward(xd, wd, 1e-6)
+    dx, dw, dw32 = ops.rmsnorm_backward_full(dyd, xd, wd, inv, want_dw_f32=True)
+    hx, hdy = x.pin_memory(), dy.pin_memory()
+    hy, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
+    pipe = HostRMSNormPipeline(rows, cols, torch.bfloat16, torch.device("cuda", 0), chunk_rows=768)
+    outs = []
+    for _ in range(2):
+        hy.zero_()
+        hdx.zero_()
+        dwp = pipe.run(hx, hdy, wd, 1e-6, hy, hdx)
+        torch.cuda.synchronize()
+        assert torch.equal(hy, y.cpu()) and torch.equal(hdx, dx.cpu())
+        outs.append(dwp.clone())
+    assert torch.equal(outs[0], outs[1])
+    ulp = torch.maximum(dw.float().abs(), outs[0].float().abs()) * 2.0 ** -7
+    assert bool(((dw.float() - outs[0].float()).abs() <= ulp).all())
