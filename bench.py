@@ -565,6 +565,7 @@ def run_block(args, device, warmup, peaks, peak_kind, world, rank) -> int:
         local = mlp
     else:
         mlp = sharding.TensorParallelSwiGLU(d, f, world, rank).to(device).to(dt)
+        mlp.overlap = os.environ.get("MGR_TP_OVERLAP", "1") != "0"   # all-reduces overlapped with GEMMs (default)
         local = mlp.local
     # nn.Linear's default init, U(-1/sqrt(fan_in), 1/sqrt(fan_in)), drawn on the device; fan_in of w3 is the FULL d_ff
     g = torch.Generator(device=device).manual_seed(SEED + 17 * rank)

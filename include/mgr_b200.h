@@ -204,6 +204,13 @@ int mgr_swiglu_fused_bwd(void* dgv, const void* dh, const void* x, const void* w
  *   dh = dy w3 (Linear(w3).backward) with _mg_swiglu_bwd_kernel (megagemm/swiglu.py:46-79) as its
  *   epilogue; dh stays in fp32 in tensor memory and is never written.
  */
+/* Limits the GEMM kernels of this process to `sms` SMs (0 = all of them); returns the previous limit.
+ * The GEMM kernels are persistent (one CTA per SM), so a collective launched beside one finds no free SM
+ * unless some are left out: a tensor-parallel caller lowers the limit around the GEMMs it overlaps with an
+ * all-reduce and restores it afterwards. Host-side setting, read at each launch. No reference counterpart
+ * (the reference has no distributed code). */
+int mgr_gemm_set_sm_limit(int sms);
+
 int mgr_swiglu_fused_fwd_save(void* h, void* gv, const void* x, const void* w12, int64_t m, int64_t d, int64_t f,
                               int dtype, void* stream);
 int mgr_swiglu_dh_dgv(void* dgv, const void* dy, const void* w3, const void* gv, int64_t m, int64_t d, int64_t f,

@@ -50,6 +50,7 @@ SIGNATURES = {
     "mgr_swiglu_fused_bwd": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "mgr_swiglu_fused_fwd_save": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "mgr_swiglu_dh_dgv": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "mgr_gemm_set_sm_limit": (_int, [_int]),
 }
 
 

@@ -25,6 +25,7 @@
 
 #include <cuda.h>
 
+#include <atomic>
 #include <cstdlib>
 #include <type_traits>
 
@@ -537,6 +538,10 @@ struct GemmArgs {
     int dtype;
 };
 
+// SMs the GEMM kernels may occupy (0 = all). A caller that overlaps a collective with a GEMM lowers it so
+// that the communication kernel finds free SMs next to the persistent GEMM CTAs.
+std::atomic<int> g_sm_limit{0};
+
 // MGR_GEMM_CTA_GROUP=1|2 pins the single-CTA or the CTA-pair kernels; unset = automatic.
 int forced_cta_group() {
     const char* e = std::getenv("MGR_GEMM_CTA_GROUP");
@@ -564,7 +569,9 @@ int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     if (status == nullptr) return MGR_ERR_CUDA;
     constexpr int n_step = n_step_of(EPI);
     const int64_t tiles = ((g.m + kBM * CG - 1) / (kBM * CG)) * ((g.n_out + n_step - 1) / n_step);
-    const int64_t slots = di.sm_count / CG;   // CTAs (pairs) that can be resident at once
+    const int limit = g_sm_limit.load(std::memory_order_relaxed);
+    const int sms = (limit > 0 && limit < di.sm_count) ? limit : di.sm_count;
+    const int64_t slots = sms / CG > 0 ? sms / CG : 1;   // CTAs (pairs) that can be resident at once
     const unsigned grid = static_cast<unsigned>((tiles < slots ? tiles : slots) * CG);
     T* c = static_cast<T*>(g.c);
     T* c2 = static_cast<T*>(g.c2);
@@ -729,4 +736,9 @@ extern "C" int mgr_swiglu_dh_dgv(void* dgv, const void* dy, const void* w3, cons
     // dh[m, f] = dy[m, d] w3[d, f]: A K-major (pitch d), B MN-major (stored [k = d, n = f], pitch f)
     const GemmArgs g{nullptr, dgv, dy, w3, gv, m, f, d, f, d, f, 2 * f, 2 * f, dtype};
     return launch_gemm_dtype<kEpiDhDgv, false, true>(g, di, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mgr_gemm_set_sm_limit(int sms) {
+    if (sms < 0) sms = 0;
+    return g_sm_limit.exchange(sms, std::memory_order_relaxed);
 }

@@ -181,8 +181,9 @@ def swiglu_fused_forward(x: torch.Tensor, w12: torch.Tensor, hidden_dim: int) ->
     return h
 
 
-def linear_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
-    """a [M, K] x b [N, K]^T -> [M, N] on the tensor-core kernel (an nn.Linear without bias)."""
+def linear_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    """a [M, K] x b [N, K]^T -> [M, N] on the tensor-core kernel (an nn.Linear without bias). `out`, if
+    given, is a contiguous [M, N] tensor to write into (e.g. a row slab of a larger result)."""
     _check_input(a, "a")
     _check_input(b, "b")
     if a.dim() != 2 or b.dim() != 2 or a.shape[1] != b.shape[1]:
@@ -194,7 +195,12 @@ def linear_tn(a: torch.Tensor, b: torch.Tensor) -> torch.Tensor:
     n = b.shape[0]
     L = _capi.lib()
     with torch.cuda.device(a.device):
-        c = torch.empty((m, n), device=a.device, dtype=a.dtype)
+        if out is None:
+            c = torch.empty((m, n), device=a.device, dtype=a.dtype)
+        else:
+            if tuple(out.shape) != (m, n) or out.dtype != a.dtype or out.device != a.device or not out.is_contiguous():
+                raise RuntimeError("out must be a contiguous [M, N] tensor of the operands' dtype and device")
+            c = out
         st = L.mgr_gemm_tn(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, k, k, n, code, _stream_ptr(a.device))
     _capi.check("tensor-core GEMM kernel", st)
     return c
@@ -283,3 +289,21 @@ def swiglu_dh_dgv(dy: torch.Tensor, w3: torch.Tensor, gv: torch.Tensor, hidden_d
                                  _stream_ptr(dy.device))
     _capi.check("fused dh/dGV kernel", st)
     return dgv
+
+
+class gemm_sm_limit:
+    """Context manager: leaves `reserve` SMs free of GEMM CTAs while it is active (for a collective that
+    runs beside the GEMMs launched inside it)."""
+
+    def __init__(self, reserve: int, device=None):
+        self.reserve = reserve
+        self.device = device
+
+    def __enter__(self):
+        sms = torch.cuda.get_device_properties(self.device if self.device is not None else torch.cuda.current_device()).multi_processor_count
+        self.prev = _capi.lib().mgr_gemm_set_sm_limit(max(2, sms - self.reserve) if self.reserve > 0 else 0)
+        return self
+
+    def __exit__(self, *exc):
+        _capi.lib().mgr_gemm_set_sm_limit(self.prev)
+        return False

@@ -161,6 +161,68 @@ class RowShardedRMSNorm(nn.Module):
 # tensor-parallel SwiGLU MLP
 # ---------------------------------------------------------------------------------------------------
 
+# SMs kept free of GEMM CTAs while an all-reduce runs beside them (the GEMM kernels are persistent, one
+# CTA per SM, and would otherwise leave the collective nowhere to run until they finish).
+COMM_SMS = 16
+
+
+class _OverlappedTPMLP(torch.autograd.Function):
+    """One rank's share of the tensor-parallel MLP with its two all-reduces overlapped with GEMMs.
+
+    Forward: the fused projection for all rows, then the w3 GEMM in `slabs` row slabs; the all-reduce of
+    slab i (async, on NCCL's stream) runs while slab i+1 is multiplied. Backward: dx = dGV w12 first, its
+    all-reduce in flight while dW12 = dGV^T x and dW3 = dy^T h are computed. The GEMMs launched while a
+    collective is in flight leave COMM_SMS SMs free for it.
+    """
+
+    @staticmethod
+    def forward(ctx, x, w12, w3, group, slabs):
+        ops = rmsnorm_cuda_ops
+        hidden = w3.shape[1]
+        x2d = x.reshape(-1, x.shape[-1])
+        if not x2d.is_contiguous():
+            x2d = x2d.contiguous()
+        m = x2d.shape[0]
+        needs_grad = any(ctx.needs_input_grad[:3])
+        if needs_grad:
+            h, gv = ops.swiglu_fused_forward_save(x2d, w12, hidden)
+        else:
+            h, gv = ops.swiglu_fused_forward(x2d, w12, hidden), None
+        y = torch.empty((m, w3.shape[0]), device=x.device, dtype=x.dtype)
+        step = -(-m // slabs)
+        step = -(-step // 256) * 256          # whole 256-row tiles per slab
+        works = []
+        with ops.gemm_sm_limit(COMM_SMS, x.device):
+            for r0 in range(0, m, step):
+                r1 = min(m, r0 + step)
+                ops.linear_tn(h[r0:r1], w3, out=y[r0:r1])
+                works.append(dist.all_reduce(y[r0:r1], op=dist.ReduceOp.SUM, group=group, async_op=True))
+        for wk in works:
+            wk.wait()
+        if needs_grad:
+            ctx.save_for_backward(x2d, w12, w3, h, gv)
+        ctx.group = group
+        ctx.x_shape = x.shape
+        return y.view(x.shape[:-1] + (w3.shape[0],))
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        ops = rmsnorm_cuda_ops
+        x2d, w12, w3, h, gv = ctx.saved_tensors
+        hidden = w3.shape[1]
+        dy = grad_output.reshape(-1, grad_output.shape[-1])
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+        dgv = ops.swiglu_dh_dgv(dy, w3, gv, hidden)
+        dx = ops.gemm(dgv, w12, False, True)
+        work = dist.all_reduce(dx, op=dist.ReduceOp.SUM, group=ctx.group, async_op=True)   # x is replicated
+        with ops.gemm_sm_limit(COMM_SMS, dy.device):
+            dw12 = ops.gemm(dgv, x2d, True, True) if ctx.needs_input_grad[1] else None
+            dw3 = ops.gemm(dy, h, True, True) if ctx.needs_input_grad[2] else None
+        work.wait()
+        return dx.view(ctx.x_shape), dw12, dw3, None, None
+
+
 class TensorParallelSwiGLU(nn.Module):
     """MegaGemmTriton split over `group`: local `w12` [2F/P, D] and `w3` [D, F/P] (see module docstring).
 
@@ -173,6 +235,8 @@ class TensorParallelSwiGLU(nn.Module):
         f0, f1 = tp_hidden_slice(hidden, world, rank)
         self.hidden_full = hidden
         self.world, self.rank, self.group = world, rank, group
+        self.overlap = True     # overlap the all-reduces with GEMMs (False: plain reduce after / before the local MLP)
+        self.slabs = 4          # row slabs of the w3 GEMM whose all-reduces are pipelined
         self.local = MegaGemmTriton.__new__(MegaGemmTriton)
         nn.Module.__init__(self.local)
         self.local.hidden = f1 - f0
@@ -190,5 +254,10 @@ class TensorParallelSwiGLU(nn.Module):
         return tp
 
     def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w12, w3 = self.local.w12.weight, self.local.w3.weight
+        m = x.numel() // x.shape[-1] if x.numel() else 0
+        if (self.overlap and x.is_cuda and x.dtype == w12.dtype and m > 0 and m % 8 == 0 and x.shape[-1] % 8 == 0
+                and rmsnorm_cuda_ops._gemm_ok(w12, w3)):
+            return _OverlappedTPMLP.apply(x, w12, w3, self.group, self.slabs)
         x = _ReduceBackward.apply(x, self.group)
         return _ReduceForward.apply(self.local(x), self.group)

@@ -63,16 +63,27 @@ def _worker(rank: int, world: int, port: int, q):
         a = xm.to(dev).requires_grad_(True)
         ya = mlp(a)
         ya.backward(dym.to(dev))
-        b = xm.to(dev).requires_grad_(True)
-        yb = tp(b)
-        yb.backward(dym.to(dev))
         f0, f1 = sharding.tp_hidden_slice(mlp.hidden, world, rank)
         tol = 2e-2
-        ok_y = float((ya.float() - yb.float()).abs().max()) < tol
-        ok_dx = float((a.grad.float() - b.grad.float()).abs().max()) < tol
         gw12 = torch.cat([mlp.w12.weight.grad[f0:f1], mlp.w12.weight.grad[mlp.hidden + f0:mlp.hidden + f1]])
-        ok_w12 = float((gw12.float() - tp.local.w12.weight.grad.float()).abs().max()) < 5e-2
-        ok_w3 = float((mlp.w3.weight.grad[:, f0:f1].float() - tp.local.w3.weight.grad.float()).abs().max()) < 5e-2
+        ok_y = ok_dx = ok_w12 = ok_w3 = True
+        outs = []
+        for overlap in (False, True):       # plain reduce around the local MLP, and all-reduces overlapped with GEMMs
+            tp.overlap = overlap
+            tp.slabs = 2
+            tp.local.w12.weight.grad = None
+            tp.local.w3.weight.grad = None
+            b = xm.to(dev).requires_grad_(True)
+            yb = tp(b)
+            yb.backward(dym.to(dev))
+            ok_y &= float((ya.float() - yb.float()).abs().max()) < tol
+            ok_dx &= float((a.grad.float() - b.grad.float()).abs().max()) < tol
+            ok_w12 &= float((gw12.float() - tp.local.w12.weight.grad.float()).abs().max()) < 5e-2
+            ok_w3 &= float((mlp.w3.weight.grad[:, f0:f1].float() - tp.local.w3.weight.grad.float()).abs().max()) < 5e-2
+            outs.append((yb.detach().clone(), b.grad.clone()))
+        # the two schedules run the same kernels on the same data: identical results
+        ok_y &= torch.equal(outs[0][0], outs[1][0])
+        ok_dx &= torch.equal(outs[0][1], outs[1][1])
         torch.cuda.synchronize()
         q.put((rank, ok_rows, ok_dw, ok_y, ok_dx, ok_w12, ok_w3))
     finally:
