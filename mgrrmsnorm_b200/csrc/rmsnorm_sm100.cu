@@ -243,6 +243,10 @@ template <typename T>
 __global__ void __launch_bounds__(1024)
 rms_dw_reduce(T* __restrict__ dw, float* __restrict__ dw_f32, const float* __restrict__ ws, int P, int cols) {
     __shared__ float part[32][33];
+    // Launched as a programmatic dependent of the backward kernel: its CTAs may be scheduled while that
+    // kernel drains; this wait returns once the backward kernel has completed and its partial rows are
+    // visible. (A no-op when the launch carries no such dependency.)
+    asm volatile("griddepcontrol.wait;" ::: "memory");
     const int col = blockIdx.x * 32 + threadIdx.x;
     float a = 0.f;
     if (col < cols) {
@@ -626,8 +630,25 @@ int bwd_typed(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, 
         int st = launch_status();
         if (st != MGR_OK) return st;
     }
-    rms_dw_reduce<T><<<static_cast<unsigned>((cols + 31) / 32), dim3(32, 32), 0, s>>>(
-        static_cast<T*>(dw), dw_f32, ws, static_cast<int>(P), static_cast<int>(cols));
+    // Programmatic dependent launch: the reduce is queued behind the backward kernel without waiting for the
+    // stream to go idle in between, which hides its launch latency (a few microseconds; it matters for the
+    // 10-30 us problems).
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(static_cast<unsigned>((cols + 31) / 32));
+    cfg.blockDim = dim3(32, 32);
+    cfg.dynamicSmemBytes = 0;
+    cfg.stream = s;
+    cudaLaunchAttribute at[1];
+    at[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+    at[0].val.programmaticStreamSerializationAllowed = 1;
+    cfg.attrs = at;
+    cfg.numAttrs = 1;
+    if (cudaLaunchKernelEx(&cfg, rms_dw_reduce<T>, static_cast<T*>(dw), dw_f32, static_cast<const float*>(ws), static_cast<int>(P),
+                           static_cast<int>(cols)) != cudaSuccess) {
+        (void)cudaGetLastError();
+        rms_dw_reduce<T><<<static_cast<unsigned>((cols + 31) / 32), dim3(32, 32), 0, s>>>(
+            static_cast<T*>(dw), dw_f32, ws, static_cast<int>(P), static_cast<int>(cols));
+    }
     return launch_status();
 }
 
