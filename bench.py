@@ -373,21 +373,9 @@ def time_e2e(rows, cols, device, steps, warmup, world, src, pipelined=True):
     return {"ms_per_step": ms / steps, "steps": steps, "h2d": 2 * rows * cols * es, "d2h": 2 * rows * cols * es + cols * es}
 
 
-def side_results(L, device, peak_gbs) -> dict:
-    """Other configurations, N=1 only: the fp16 [4096,4096] shape the reference publishes (L2-cold by
-    rotating 8 buffer sets = 1.25 GiB) and the bf16 hidden sweep at 2^29 elements."""
-    out = {}
-    sets = [RmsBuffers(L, 4096, 4096, torch.float16, device, SEED + i) for i in range(8)]
-    r = time_device_resident(sets, 400, 40, 1)
-    nb = rms_bytes(4096, 4096, 2)
-    out["rmsnorm_fp16_4096x4096"] = {
-        "l2": "cold: 8 rotating buffer sets (1.25 GiB)", "us_per_step": r["total_ms"] * 1e3 / 400,
-        "GBps": nb["total"] / (r["total_ms"] / 400 * 1e-3) / 1e9,
-        "fwd_us": r["fwd_ms"] * 1e3, "bwd_us": r["bwd_ms"] * 1e3,
-        "fwd_frac_of_peak": nb["fwd"] / (r["fwd_ms"] * 1e-3) / 1e9 / peak_gbs,
-        "bwd_frac_of_peak": nb["bwd"] / (r["bwd_ms"] * 1e-3) / 1e9 / peak_gbs,
-        "launch": "one C-ABI call per kernel from Python; 10-30 us kernels leave the host behind, so these times include launch gaps"}
-    # The same rotation replayed from CUDA graphs: no host launch gaps, device time only.
+def graph_timed(sets, nb, peak_gbs, l2_note) -> dict:
+    """Forward, backward and forward+backward over the rotating buffer `sets`, replayed from CUDA graphs:
+    no host launch gaps, device time only (microseconds per call)."""
     stream = torch.cuda.current_stream()
 
     def graph_of(fn):
@@ -411,18 +399,38 @@ def side_results(L, device, peak_gbs) -> dict:
         return e0.elapsed_time(e1) * 1e3 / (n * len(sets))
 
     try:
+        sp0 = stream.cuda_stream
+        for b in sets:     # every first-call set-up (attributes, occupancy queries) happens before capture
+            b.fwd(sp0)
+            b.bwd(sp0)
+        torch.cuda.synchronize()
         gf = graph_of(lambda b, sp: b.fwd(sp))
         gb = graph_of(lambda b, sp: b.bwd(sp))
         gfb = graph_of(lambda b, sp: (b.fwd(sp), b.bwd(sp)))
         f_us, b_us, fb_us = replay_us(gf), replay_us(gb), replay_us(gfb)
-        out["rmsnorm_fp16_4096x4096_cuda_graph"] = {
-            "l2": "cold: 8 rotating buffer sets (1.25 GiB)", "fwd_us": f_us, "bwd_us": b_us, "us_per_step": fb_us,
-            "GBps": nb["total"] / (fb_us * 1e-6) / 1e9,
-            "fwd_frac_of_peak": nb["fwd"] / (f_us * 1e-6) / 1e9 / peak_gbs,
-            "bwd_frac_of_peak": nb["bwd"] / (b_us * 1e-6) / 1e9 / peak_gbs}
-        del gf, gb, gfb
+        return {"l2": l2_note, "fwd_us": f_us, "bwd_us": b_us, "us_per_step": fb_us,
+                "GBps": nb["total"] / (fb_us * 1e-6) / 1e9,
+                "fwd_frac_of_peak": nb["fwd"] / (f_us * 1e-6) / 1e9 / peak_gbs,
+                "bwd_frac_of_peak": nb["bwd"] / (b_us * 1e-6) / 1e9 / peak_gbs}
     except Exception as e:   # a capture problem must not take the headline line down with it
-        out["rmsnorm_fp16_4096x4096_cuda_graph"] = {"error": str(e)[:200]}
+        return {"error": str(e)[:200]}
+
+
+def side_results(L, device, peak_gbs) -> dict:
+    """Other configurations, N=1 only: the fp16 [4096,4096] shape the reference publishes (L2-cold by
+    rotating 8 buffer sets = 1.25 GiB) and the bf16 hidden sweep at 2^29 elements."""
+    out = {}
+    sets = [RmsBuffers(L, 4096, 4096, torch.float16, device, SEED + i) for i in range(8)]
+    r = time_device_resident(sets, 400, 40, 1)
+    nb = rms_bytes(4096, 4096, 2)
+    out["rmsnorm_fp16_4096x4096"] = {
+        "l2": "cold: 8 rotating buffer sets (1.25 GiB)", "us_per_step": r["total_ms"] * 1e3 / 400,
+        "GBps": nb["total"] / (r["total_ms"] / 400 * 1e-3) / 1e9,
+        "fwd_us": r["fwd_ms"] * 1e3, "bwd_us": r["bwd_ms"] * 1e3,
+        "fwd_frac_of_peak": nb["fwd"] / (r["fwd_ms"] * 1e-3) / 1e9 / peak_gbs,
+        "bwd_frac_of_peak": nb["bwd"] / (r["bwd_ms"] * 1e-3) / 1e9 / peak_gbs,
+        "launch": "one C-ABI call per kernel from Python; 10-30 us kernels leave the host behind, so these times include launch gaps"}
+    out["rmsnorm_fp16_4096x4096_cuda_graph"] = graph_timed(sets, nb, peak_gbs, "cold: 8 rotating buffer sets (1.25 GiB)")
     del sets
     torch.cuda.empty_cache()
     sweep = {}
@@ -438,6 +446,22 @@ def side_results(L, device, peak_gbs) -> dict:
         del b
         torch.cuda.empty_cache()
     out["rmsnorm_bf16_hidden_sweep_2^29_elements"] = sweep
+    # config 1's shape (fp32 [4096, 4096], the CPU-runnable case) on the GPU, L2-cold, graph-timed
+    sets = [RmsBuffers(L, 4096, 4096, torch.float32, device, SEED + i) for i in range(4)]
+    out["rmsnorm_fp32_4096x4096_cuda_graph"] = graph_timed(sets, rms_bytes(4096, 4096, 4), peak_gbs, "cold: 4 rotating buffer sets (1.25 GiB)")
+    del sets
+    torch.cuda.empty_cache()
+    # the sweep's latency regime: ONE row block of 2^20 elements per call (rows = 2^20 / hidden), L2-cold
+    lat = {}
+    for h in (1024, 4096, 8192, 16384):
+        rows = (1 << 20) // h
+        sets = [RmsBuffers(L, rows, h, torch.bfloat16, device, SEED + i, x_scale=2.0 ** 0.5) for i in range(24)]
+        r = graph_timed(sets, rms_bytes(rows, h, 2), peak_gbs, "cold: 24 rotating buffer sets (200 MB)")
+        r["rows"] = rows
+        lat[str(h)] = r
+        del sets
+        torch.cuda.empty_cache()
+    out["rmsnorm_bf16_hidden_sweep_2^20_elements_latency"] = lat
     out["swiglu_mlp_fp16_M4096_D4096_F6912"] = mlp_side_result(device)
     return out
 

@@ -619,7 +619,11 @@ int launch_gemm_cg(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
         const double flops = 2.0 * static_cast<double>(g.m) * static_cast<double>(g.b_rows) * static_cast<double>(g.k);
         cg = flops < kPairFlopLimit ? 2 : 1;
     }
-    if (cg == 2 && di.sm_count % 2 == 0) return launch_gemm<EPI, A_MN, B_MN, 2, T>(g, di, s);
+    if (cg == 2 && di.sm_count % 2 == 0) {
+        const int st = launch_gemm<EPI, A_MN, B_MN, 2, T>(g, di, s);
+        if (st != MGR_ERR_LAUNCH_FAILED) return st;
+        // a cluster of two could not be placed (e.g. a partitioned device): the single-CTA kernels need none
+    }
     return launch_gemm<EPI, A_MN, B_MN, 1, T>(g, di, s);
 }
 
