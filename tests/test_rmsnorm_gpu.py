@@ -367,3 +367,56 @@ def test_host_tensor_pipeline_matches_module(ops, monkeypatch):
     assert torch.equal(outs[0], outs[1])
     ulp = torch.maximum(dw.float().abs(), outs[0].float().abs()) * 2.0 ** -7
     assert bool(((dw.float() - outs[0].float()).abs() <= ulp).all())
+
+
+def test_speed_against_reference_cuda_kernels(ops, built_lib, capsys):
+    """The reference's own kernels (compiled unmodified for sm_100a into oracle/_ref) and this library on
+    the reference's benchmark shape, fp16 [4096, 4096] (README: batch 32, seq 128, hidden 4096), timed the
+    same way: 8 rotating buffer sets (L2-cold), CUDA events around 200 launches on the stream each side
+    uses. The test only requires this library not to be slower; the measured ratio is printed."""
+    ref = oracle.ref_lib()
+    if ref is None:
+        pytest.skip("oracle/_ref/libmgr_ref.so not present")
+    from mgrrmsnorm_b200 import _capi
+
+    rows, cols, nsets, iters = 4096, 4096, 8, 200
+    sets = []
+    for i in range(nsets):
+        x, w, dy = (t.cuda() for t in seeded_rmsnorm_inputs(rows, cols, "f16", 100 + i))
+        sets.append(dict(x=x, w=w, dy=dy, y=torch.empty_like(x), dx=torch.empty_like(x), dw=torch.empty_like(w),
+                         inv=torch.empty(rows, device="cuda")))
+    wsb = int(built_lib.mgr_rmsnorm_bwd_workspace_bytes(rows, cols, _capi.MGR_F16))
+    ws = torch.empty(wsb, dtype=torch.uint8, device="cuda")
+    legacy = torch.cuda.default_stream()      # the reference launches on the legacy default stream
+
+    def ours(b):
+        s = legacy.cuda_stream
+        assert built_lib.mgr_rmsnorm_fwd(b["y"].data_ptr(), b["inv"].data_ptr(), b["x"].data_ptr(), b["w"].data_ptr(), rows, cols, 1e-6,
+                                         _capi.MGR_F16, s) == 0
+        assert built_lib.mgr_rmsnorm_bwd(b["dx"].data_ptr(), b["dw"].data_ptr(), None, b["dy"].data_ptr(), b["x"].data_ptr(),
+                                         b["w"].data_ptr(), b["inv"].data_ptr(), rows, cols, _capi.MGR_F16, ws.data_ptr(), wsb, s) == 0
+
+    def theirs(b):
+        assert ref.fwd["f16"](b["y"].data_ptr(), b["inv"].data_ptr(), b["x"].data_ptr(), b["w"].data_ptr(), rows, cols, np.float32(1e-6))
+        assert ref.bwd["f16"](b["dx"].data_ptr(), b["dw"].data_ptr(), b["dy"].data_ptr(), b["x"].data_ptr(), b["w"].data_ptr(),
+                              b["inv"].data_ptr(), rows, cols)
+
+    def timed(fn):
+        with torch.cuda.stream(legacy):
+            for i in range(20):
+                fn(sets[i % nsets])
+            e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+            torch.cuda.synchronize()
+            e0.record(legacy)
+            for i in range(iters):
+                fn(sets[i % nsets])
+            e1.record(legacy)
+            torch.cuda.synchronize()
+        return e0.elapsed_time(e1) * 1e3 / iters
+
+    t_ref, t_ours = timed(theirs), timed(ours)
+    t_ref2, t_ours2 = timed(theirs), timed(ours)
+    t_ref, t_ours = min(t_ref, t_ref2), min(t_ours, t_ours2)
+    with capsys.disabled():
+        print(f"\n[fp16 4096x4096 fwd+bwd, L2-cold] reference kernels {t_ref:.1f} us, this library {t_ours:.1f} us, ratio {t_ref / t_ours:.2f}x")
+    assert t_ours <= t_ref * 1.05
