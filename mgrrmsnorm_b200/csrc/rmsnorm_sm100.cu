@@ -126,7 +126,7 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* __restrict_
 // partial sums stay in registers until the CTA is done; the G row groups of a CTA are then folded in
 // shared memory (fixed order) and the CTA writes ONE fp32 partial row ws[blockIdx.x, :].
 template <typename T, int TPR, int VPT>
-__global__ void __launch_bounds__(RegGeom<TPR>::kBlock, RegGeom<TPR>::kBwdMinBlocks)
+__global__ void __launch_bounds__(RegGeom<TPR>::kBlock, (VPT <= 2 && TPR >= 256) ? (VPT == 1 ? 1536 : 1024) / RegGeom<TPR>::kBlock : RegGeom<TPR>::kBwdMinBlocks)
 rms_bwd_reg(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
             const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int cols) {
     using Geo = RegGeom<TPR>;
@@ -351,11 +351,33 @@ rms_bwd_dw_scalar(float* __restrict__ ws, const T* __restrict__ dy, const T* __r
 struct RegShape {
     int tpr, vpt;
 };
-constexpr RegShape kRegShapes[] = {{32, 1}, {32, 2}, {32, 4}, {128, 2}, {128, 4}, {256, 4}, {512, 4}, {1024, 4}};
+// The last three are alternatives to {128,4}, {256,4} and {128,2} with one row per CTA pass; only the backward
+// picks them (bwd_shape_for), the size-ordered search of reg_shape_for never reaches them.
+constexpr RegShape kRegShapes[] = {{32, 1}, {32, 2}, {32, 4}, {128, 2}, {128, 4}, {256, 4}, {512, 4}, {1024, 4}, {256, 2}, {512, 2}, {256, 1}};
 constexpr int kNumRegShapes = sizeof(kRegShapes) / sizeof(kRegShapes[0]);
 constexpr int kScalarDwSlices = 64;
 
 // Index of the smallest packet shape that holds a row of `nvec` packets, or -1.
+// MGR_RMSNORM_BWD_SHAPE=<index into kRegShapes> pins the backward's packet shape when it can hold the row
+// (measurement aid); otherwise the default search.
+int reg_shape_for(int64_t nvec);
+int bwd_shape_for(int64_t nvec) {
+    const char* e = std::getenv("MGR_RMSNORM_BWD_SHAPE");
+    if (e != nullptr) {
+        const int i = std::atoi(e);
+        if (i >= 0 && i < static_cast<int>(sizeof(kRegShapes) / sizeof(kRegShapes[0])) &&
+            nvec <= static_cast<int64_t>(kRegShapes[i].tpr) * kRegShapes[i].vpt)
+            return i;
+    }
+    // Measured on B200 (bf16, 2^29 elements, fraction of the copy bandwidth): rows of 257-512 packets run at
+    // 0.92 with {256,2} (one row per pass, 4 CTAs per SM) against 0.86 with {128,4}; rows of 513-1024 packets
+    // are better left with {256,4} (0.92 against 0.89 for {512,2}).
+    // Rows of 129-256 packets: 0.93 with {256,1} against 0.76 with {128,2} (and 0.84 for the ring kernel).
+    if (nvec > 256 && nvec <= 512) return 8;
+    if (nvec > 128 && nvec <= 256) return 10;
+    return reg_shape_for(nvec);
+}
+
 int reg_shape_for(int64_t nvec) {
     for (int i = 0; i < kNumRegShapes; ++i)
         if (nvec <= static_cast<int64_t>(kRegShapes[i].tpr) * kRegShapes[i].vpt) return i;
@@ -544,7 +566,8 @@ struct RingDispatch {
 // Automatic choice between the register and the ring family, from back-to-back timings on B200
 // (fraction of the measured 6.55 TB/s copy bandwidth, register / ring):
 //   forward : 2-4 KB rows 0.83 / 1.00; 8 KB 0.97 / 0.95; 16 KB 0.99 / 0.92; 32 KB 0.97 / 0.89
-//   backward: 2 KB rows 0.90 / 0.80; 4 KB 0.76 / 0.84; 8 KB 0.85 / 0.83; 16 KB 0.92 / 0.82; 32 KB 0.84-0.87 / 0.90-0.94
+//   backward: 2 KB rows 0.90 / 0.80; 4 KB 0.93 / 0.84; 8 KB 0.92 / 0.83; 16 KB 0.92 / 0.82; 32 KB 0.84-0.87 / 0.90-0.94
+//   (register figures with the per-size packet shapes of bwd_shape_for)
 // The ring needs enough rows to fill its pipeline, hence the row-count floor.
 bool prefer_ring_fwd(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& di) {
     const int64_t row_bytes = cols * static_cast<int64_t>(elem);
@@ -552,7 +575,7 @@ bool prefer_ring_fwd(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& 
 }
 bool prefer_ring_bwd(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& di) {
     const int64_t row_bytes = cols * static_cast<int64_t>(elem);
-    return rows >= 8ll * di.sm_count && ((row_bytes > 2048 && row_bytes <= 4096) || row_bytes > 16384);
+    return rows >= 8ll * di.sm_count && row_bytes > 16384;
 }
 
 template <typename T>
@@ -583,7 +606,7 @@ int64_t bwd_partials(int64_t rows, int64_t cols, const DeviceInfo& di) {
     constexpr int VEC = Elem<T>::kVec;
     int64_t p = rows < kScalarDwSlices ? rows : kScalarDwSlices;
     if (cols % VEC == 0) {
-        const int shape = reg_shape_for(cols / VEC);
+        const int shape = bwd_shape_for(cols / VEC);
         if (shape >= 0) {
             const int64_t g = RegDispatch<T>::bwd_grid(shape, rows, di);
             if (g > p) p = g;
@@ -613,7 +636,7 @@ int bwd_typed(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, 
         }
     }
     if (P < 0) {
-        const int shape = packets ? reg_shape_for(cols / VEC) : -1;
+        const int shape = packets ? bwd_shape_for(cols / VEC) : -1;
         if (shape >= 0) {
             P = RegDispatch<T>::bwd_grid(shape, rows, di);
             RegDispatch<T>::bwd(shape, static_cast<T*>(dx), ws, static_cast<const T*>(dy), static_cast<const T*>(x),
