@@ -132,6 +132,7 @@ rms_bwd_reg(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy
     using Geo = RegGeom<TPR>;
     constexpr int VEC = Elem<T>::kVec;
     constexpr int G = Geo::kGroups;
+    constexpr bool kTwoPass = TPR >= 1024;   // 64 registers per thread: the row cannot stay resident
     __shared__ float red[2][Geo::kWarps];
     __shared__ __align__(16) float fold[G > 1 ? (G - 1) * TPR * VPT * VEC : 4];
     int buf = 0;
@@ -145,7 +146,7 @@ rms_bwd_reg(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy
 #pragma unroll
     for (int k = 0; k < VPT; ++k) {
         const int v = t + k * TPR;
-        wv[k] = v < nvec ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
+        wv[k] = (!kTwoPass && v < nvec) ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
 #pragma unroll
         for (int i = 0; i < VEC; ++i) acc[k][i] = 0.f;
     }
@@ -158,45 +159,88 @@ rms_bwd_reg(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy
         const int64_t off = (live ? r : 0) * static_cast<int64_t>(cols);
         const uint4* xr = reinterpret_cast<const uint4*>(x + off);
         const uint4* gr = reinterpret_cast<const uint4*>(dy + off);
-        uint4 xv[VPT], gv[VPT];
-#pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-            const int v = t + k * TPR;
-            const bool on = live && v < nvec;
-            xv[k] = on ? ld_stream16(xr + v) : make_uint4(0, 0, 0, 0);
-            gv[k] = on ? ld_stream16(gr + v) : make_uint4(0, 0, 0, 0);
-            keep_packed(wv[k]);
-        }
         const float rinv = live ? __ldg(inv_rms + r) : 0.f;
-
-        float c = 0.f;
+        if constexpr (!kTwoPass) {
+            uint4 xv[VPT], gv[VPT];
 #pragma unroll
-        for (int k = 0; k < VPT; ++k) {
-            float fx[VEC], fg[VEC], fw[VEC];
-            unpack16<T>(xv[k], fx);
-            unpack16<T>(gv[k], fg);
-            unpack16<T>(wv[k], fw);
-#pragma unroll
-            for (int i = 0; i < VEC; ++i) {
-                c += (fg[i] * fw[i]) * fx[i];
-                acc[k][i] += (fg[i] * fx[i]) * rinv;
+            for (int k = 0; k < VPT; ++k) {
+                const int v = t + k * TPR;
+                const bool on = live && v < nvec;
+                xv[k] = on ? ld_stream16(xr + v) : make_uint4(0, 0, 0, 0);
+                gv[k] = on ? ld_stream16(gr + v) : make_uint4(0, 0, 0, 0);
+                keep_packed(wv[k]);
             }
-        }
-        c = row_sum<TPR>(c, red, buf, group);
-        const float term2 = c * (rinv * rinv) * inv_cols;
 
-        if (live) {
+            float c = 0.f;
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                float fx[VEC], fg[VEC], fw[VEC];
+                unpack16<T>(xv[k], fx);
+                unpack16<T>(gv[k], fg);
+                unpack16<T>(wv[k], fw);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    c += (fg[i] * fw[i]) * fx[i];
+                    acc[k][i] += (fg[i] * fx[i]) * rinv;
+                }
+            }
+            c = row_sum<TPR>(c, red, buf, group);
+            const float term2 = c * (rinv * rinv) * inv_cols;
+
+            if (live) {
+                uint4* dr = reinterpret_cast<uint4*>(dx + off);
+#pragma unroll
+                for (int k = 0; k < VPT; ++k) {
+                    const int v = t + k * TPR;
+                    if (v < nvec) {
+                        float fx[VEC], fg[VEC], fw[VEC], o[VEC];
+                        unpack16<T>(xv[k], fx);
+                        unpack16<T>(gv[k], fg);
+                        unpack16<T>(wv[k], fw);
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) o[i] = rinv * (fg[i] * fw[i] - fx[i] * term2);
+                        st_stream16(dr + v, pack16<T>(o));
+                    }
+                }
+            }
+        } else {
+            // Rows too long to hold in the registers of 1024 threads next to the dW partials: the row is
+            // read twice, packet by packet. The first read comes from HBM and stays cached (plain loads); the
+            // second, right behind it, is served by L1/L2, so HBM traffic does not grow.
+            float c = 0.f;
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int v = t + k * TPR;
+                const bool on = live && v < nvec;
+                const uint4 px = on ? __ldg(xr + v) : make_uint4(0, 0, 0, 0);
+                const uint4 pg = on ? __ldg(gr + v) : make_uint4(0, 0, 0, 0);
+                const uint4 pw = v < nvec ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
+                float fx[VEC], fg[VEC], fw[VEC];
+                unpack16<T>(px, fx);
+                unpack16<T>(pg, fg);
+                unpack16<T>(pw, fw);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) c += (fg[i] * fw[i]) * fx[i];
+            }
+            c = row_sum<TPR>(c, red, buf, group);
+            const float term2 = c * (rinv * rinv) * inv_cols;
             uint4* dr = reinterpret_cast<uint4*>(dx + off);
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
                 const int v = t + k * TPR;
-                if (v < nvec) {
+                if (live && v < nvec) {
+                    const uint4 px = ld_stream16(xr + v);
+                    const uint4 pg = ld_stream16(gr + v);
+                    const uint4 pw = __ldg(reinterpret_cast<const uint4*>(w) + v);   // weights are not kept in registers here
                     float fx[VEC], fg[VEC], fw[VEC], o[VEC];
-                    unpack16<T>(xv[k], fx);
-                    unpack16<T>(gv[k], fg);
-                    unpack16<T>(wv[k], fw);
+                    unpack16<T>(px, fx);
+                    unpack16<T>(pg, fg);
+                    unpack16<T>(pw, fw);
 #pragma unroll
-                    for (int i = 0; i < VEC; ++i) o[i] = rinv * (fg[i] * fw[i] - fx[i] * term2);
+                    for (int i = 0; i < VEC; ++i) {
+                        acc[k][i] += (fg[i] * fx[i]) * rinv;
+                        o[i] = rinv * (fg[i] * fw[i] - fx[i] * term2);
+                    }
                     st_stream16(dr + v, pack16<T>(o));
                 }
             }
