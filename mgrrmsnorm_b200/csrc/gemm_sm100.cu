@@ -38,18 +38,19 @@ namespace {
 __device__ int g_gemm_status = 0;
 
 constexpr int kBM = 128;         // tile rows (UMMA M)
-constexpr int kBN = 256;         // accumulator columns per tile (UMMA N)
+constexpr int kBN = 256;         // accumulator columns per tile (UMMA N) of the throughput kernels
+constexpr int kBNSmall = 64;     // ... of the narrow-tile kernels used when a problem has few tiles (skinny M)
 constexpr int kBK = 64;          // K per stage: 64 x 2 B = one 128-byte swizzle row
 constexpr int kUmmaK = 16;       // K of one tcgen05.mma for 16-bit operands
 constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB: this CTA's 128 rows of A
-constexpr uint32_t kBBytes = kBN * kBK * 2;   // 32 KB: all 256 rows of B (a CTA pair holds half each)
+__host__ __device__ constexpr uint32_t b_bytes(int bn) { return bn * kBK * 2; }   // 32 KB at BN 256 (a CTA pair holds half each)
 // CG = CTAs that share one MMA (tcgen05 cta_group): 1, or 2 = a pair of CTAs in one cluster working on a
 // 256 x 256 tile, each loading its own A rows and HALF of the B rows, which halves the B traffic per CTA
 // and deepens the ring from 4 to 7 stages.
-__host__ __device__ constexpr uint32_t stage_bytes(int cg) { return kABytes + kBBytes / cg; }
-__host__ __device__ constexpr int num_stages(int cg) { return cg == 1 ? 4 : 7; }
-__host__ __device__ constexpr uint32_t gemm_smem(int cg) { return num_stages(cg) * stage_bytes(cg) + 1024; }  // + slack to align to 1024 B
-constexpr int kMaxStages = 7;
+__host__ __device__ constexpr uint32_t stage_bytes(int cg, int bn) { return kABytes + b_bytes(bn) / cg; }
+__host__ __device__ constexpr int num_stages(int cg, int bn) { return bn == kBNSmall ? 8 : (cg == 1 ? 4 : 7); }
+__host__ __device__ constexpr uint32_t gemm_smem(int cg, int bn) { return num_stages(cg, bn) * stage_bytes(cg, bn) + 1024; }  // + slack to align to 1024 B
+constexpr int kMaxStages = 8;
 constexpr int kEpiWarps = 8;      // epilogue warps: two per 32-lane quarter of tensor memory
 constexpr int kGemmThreads = (2 + kEpiWarps) * 32;
 constexpr uint32_t kTmemCols = 512;
@@ -58,7 +59,7 @@ enum Epilogue { kEpiPlain = 0, kEpiSwiglu = 1, kEpiSwigluBwd = 2, kEpiSwigluSave
 
 // Output columns one tile covers: the full 256-column accumulator, or 128 when the accumulator holds a
 // gate half and a value half.
-__host__ __device__ constexpr int n_step_of(int epi) { return (epi == kEpiPlain || epi == kEpiDhDgv) ? kBN : kBN / 2; }
+__host__ __device__ constexpr int n_step_of(int epi, int bn) { return (epi == kEpiPlain || epi == kEpiDhDgv) ? bn : bn / 2; }
 
 // Shared-memory matrix descriptors (64-bit, addresses in 16-byte units): start address [0,14),
 // leading byte offset [16,30), stride byte offset [32,46), descriptor version 1 at [46,48) (sm_100),
@@ -84,9 +85,9 @@ __device__ __forceinline__ uint64_t smem_desc_sw128(uint32_t smem_addr, bool mn_
 // Instruction descriptor, kind::f16: fp32 accumulator (bits [4,6) = 1), operand formats at [7,10) and
 // [10,13) (0 = fp16, 1 = bf16), A / B major-ness at bits 15 / 16 (1 = MN-major), N>>3 at [17,23),
 // M>>4 at [24,29). N=256; M=128, or 256 for a CTA pair.
-__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, bool a_mn, bool b_mn, int cg) {
+__host__ __device__ constexpr uint32_t instr_desc(uint32_t fmt, bool a_mn, bool b_mn, int cg, int bn) {
     return (1u << 4) | (fmt << 7) | (fmt << 10) | (a_mn ? (1u << 15) : 0u) | (b_mn ? (1u << 16) : 0u) |
-           (static_cast<uint32_t>(kBN >> 3) << 17) | (static_cast<uint32_t>((kBM * cg) >> 4) << 24);
+           (static_cast<uint32_t>(bn >> 3) << 17) | (static_cast<uint32_t>((kBM * cg) >> 4) << 24);
 }
 
 // MUFU exp + MUFU reciprocal: about 2 ulp, far below the 16-bit output rounding; keeps the epilogue short
@@ -135,15 +136,18 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_tiles,
 //                [M, 2 n_out] (pitch ld_aux) -- the training forward, whose backward reads it back.
 // kEpiDhDgv    : plain tile (256 columns); acc = dh tile; aux = stored projection [G | V] (pitch ld_aux);
 //                C = [d_gate | d_val] of shape [M, 2 n_out]. dh itself is never written.
-template <int EPI, bool A_MN, bool B_MN, int CG, typename T>
+template <int EPI, bool A_MN, bool B_MN, int CG, typename T, int BN = kBN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, T* __restrict__ C,
             T* __restrict__ C2, const T* __restrict__ aux, int M, int n_out, int K, int64_t ldc, int64_t ld_aux,
+            uint32_t a_box_bytes,
             int* __restrict__ status) {
-    static_assert(n_step_of(EPI) == kBN || !B_MN, "the gate/value split reads w12 K-major");
-    constexpr int kNStep = n_step_of(EPI);  // output columns per tile
-    constexpr int kStages = num_stages(CG);
-    constexpr uint32_t kStageBytes = stage_bytes(CG);
+    static_assert(n_step_of(EPI, BN) == BN || !B_MN, "the gate/value split reads w12 K-major");
+    static_assert(BN == kBN || (BN == kBNSmall && CG == 1 && !A_MN && !B_MN), "narrow tiles: single CTA, K-major operands");
+    constexpr int kNStep = n_step_of(EPI, BN);  // output columns per tile
+    constexpr int kStages = num_stages(CG, BN);
+    constexpr uint32_t kStageBytes = stage_bytes(CG, BN);
+    constexpr uint32_t kBBytes = b_bytes(BN);
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[kMaxStages], bar_empty[kMaxStages], bar_tfull[2], bar_tempty[2];
     __shared__ uint32_t tmem_base_slot;
@@ -198,7 +202,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int t = first_tile; ok && t < num_tiles; t += tile_stride) {
                 const TileCoord tc = tile_coord(t, m_tiles, n_tiles, kNStep, kBM * CG);
                 const int m0 = tc.m0 + static_cast<int>(cta_rank) * kBM;     // this CTA's rows of the tile
-                const int b_row1 = kNStep == kBN ? tc.n0 + kBN / 2 : n_out + tc.n0;   // second half of the B rows
+                const int b_row1 = kNStep == BN ? tc.n0 + BN / 2 : n_out + tc.n0;   // second half of the B rows
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(ptx::smem_addr(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
                         ok = false;
@@ -209,7 +213,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     const int k0 = kb * kBK;
                     if constexpr (CG == 1) {
                         const uint32_t full = ptx::smem_addr(&bar_full[stage]);
-                        ptx::mbar_arrive_expect_tx(full, kStageBytes);
+                        ptx::mbar_arrive_expect_tx(full, a_box_bytes + kBBytes);   // the A box may be shorter than 128 rows
                         if constexpr (!A_MN) {
                             ptx::tma_load_2d(sa, &tmA, k0, m0, full);
                         } else {
@@ -221,7 +225,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             ptx::tma_load_2d(sb + kBBytes / 2, &tmB, k0, b_row1, full);
                         } else {
 #pragma unroll
-                            for (int c = 0; c < kBN / 64; ++c) ptx::tma_load_2d(sb + c * 8192u, &tmB, tc.n0 + 64 * c, k0, full);
+                            for (int c = 0; c < BN / 64; ++c) ptx::tma_load_2d(sb + c * 8192u, &tmB, tc.n0 + 64 * c, k0, full);
                         }
                     } else {
                         // Both CTAs' bytes are counted on the LEADER's barrier: the leader announces the total,
@@ -239,8 +243,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             ptx::tma_load_2d_pair(sb, &tmB, k0, cta_rank == 0 ? tc.n0 : b_row1, full);
                         } else {
 #pragma unroll
-                            for (int c = 0; c < kBN / 128; ++c)
-                                ptx::tma_load_2d_pair(sb + c * 8192u, &tmB, tc.n0 + static_cast<int>(cta_rank) * (kBN / 2) + 64 * c, k0, full);
+                            for (int c = 0; c < BN / 128; ++c)
+                                ptx::tma_load_2d_pair(sb + c * 8192u, &tmB, tc.n0 + static_cast<int>(cta_rank) * (BN / 2) + 64 * c, k0, full);
                         }
                     }
                     if (++stage == kStages) {
@@ -253,7 +257,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     } else if (warp == 1) {
         // ---------------- MMA issuer ----------------
         if (cta_rank == 0 && ptx::elect_one()) {
-            constexpr uint32_t idesc = instr_desc(std::is_same<T, __nv_bfloat16>::value ? 1u : 0u, A_MN, B_MN, CG);
+            constexpr uint32_t idesc = instr_desc(std::is_same<T, __nv_bfloat16>::value ? 1u : 0u, A_MN, B_MN, CG, BN);
             constexpr uint32_t a_step = A_MN ? (2048u >> 4) : (32u >> 4);  // start-address step per K=16 slice
             constexpr uint32_t b_step = B_MN ? (2048u >> 4) : (32u >> 4);
             int stage = 0, acc = 0;
@@ -262,7 +266,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int t = first_tile; ok && t < num_tiles; t += tile_stride) {
                 if (!ptx::mbar_wait(ptx::smem_addr(&bar_tempty[acc]), acc_phase ^ 1u, &abort_flag)) break;
                 ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * kBN;
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * BN;
                 for (int kb = 0; kb < num_kb; ++kb) {
                     if (!ptx::mbar_wait(ptx::smem_addr(&bar_full[stage]), phase, &abort_flag)) {
                         ok = false;
@@ -304,7 +308,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (!ptx::mbar_wait(ptx::smem_addr(&bar_tfull[acc]), acc_phase, &abort_flag)) break;
             ptx::tc_fence_after_sync();
             const int row = tc.m0 + static_cast<int>(cta_rank) * kBM + q * 32 + lane;
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * kBN;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * BN;
             T* crow = C + static_cast<int64_t>(row) * ldc + tc.n0;
             [[maybe_unused]] uint4 gp_next[4], vp_next[4];   // kEpiDhDgv: packets requested one chunk ahead
 #pragma unroll 1
@@ -312,7 +316,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if constexpr (EPI == kEpiSwigluBwd) {
                     uint32_t g[32], v[32];
                     ptx::tmem_ld_32x32(t_row + c * 32, g);
-                    ptx::tmem_ld_32x32(t_row + kBN / 2 + c * 32, v);
+                    ptx::tmem_ld_32x32(t_row + BN / 2 + c * 32, v);
                     uint4 dhp[4];
                     const T* arow = aux + static_cast<int64_t>(row) * ld_aux + tc.n0 + c * 32;
 #pragma unroll
@@ -407,7 +411,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     if constexpr (EPI == kEpiSwiglu || EPI == kEpiSwigluSave) {
                         uint32_t g[32], v[32];
                         ptx::tmem_ld_32x32(t_row + c * 32, g);
-                        ptx::tmem_ld_32x32(t_row + kBN / 2 + c * 32, v);
+                        ptx::tmem_ld_32x32(t_row + BN / 2 + c * 32, v);
                         ptx::tmem_ld_wait();
 #pragma unroll
                         for (int j = 0; j < 16; ++j)
@@ -550,12 +554,12 @@ int forced_cta_group() {
     return e[0] == '2' ? 2 : (e[0] == '1' ? 1 : 0);
 }
 
-template <int EPI, bool A_MN, bool B_MN, int CG, typename T>
+template <int EPI, bool A_MN, bool B_MN, int CG, typename T, int BN = kBN>
 int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     static bool attr[kMaxDevices] = {false};
-    constexpr uint32_t kGemmSmem = gemm_smem(CG);
+    constexpr uint32_t kGemmSmem = gemm_smem(CG, BN);
     if (!attr[di.device]) {
-        if (cudaFuncSetAttribute(gemm_kernel<EPI, A_MN, B_MN, CG, T>, cudaFuncAttributeMaxDynamicSharedMemorySize,
+        if (cudaFuncSetAttribute(gemm_kernel<EPI, A_MN, B_MN, CG, T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kGemmSmem)) != cudaSuccess) {
             (void)cudaGetLastError();
             return MGR_ERR_CUDA;
@@ -563,12 +567,20 @@ int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
         attr[di.device] = true;
     }
     CUtensorMap tmA, tmB;
-    const bool okA = A_MN ? make_tmap(&tmA, g.a, g.k, g.m, g.lda, 64, g.dtype) : make_tmap(&tmA, g.a, g.m, g.k, g.lda, 128, g.dtype);
-    const bool okB = B_MN ? make_tmap(&tmB, g.b, g.k, g.b_rows, g.ldb, 64, g.dtype) : make_tmap(&tmB, g.b, g.b_rows, g.k, g.ldb, 128, g.dtype);
+    // A problem of fewer than 128 rows brings in only the rows it has (rounded up to 8): the rest of the
+    // 128-row operand tile stays whatever shared memory held, which only reaches output rows >= M, and those
+    // are never stored. At 16 rows this cuts the bytes per K step from 24 KB to 10 KB (narrow tiles).
+    const uint32_t a_rows = (CG == 1 && !A_MN && g.m < kBM) ? static_cast<uint32_t>((g.m + 7) / 8 * 8) : static_cast<uint32_t>(kBM);
+    const uint32_t a_box_bytes = A_MN ? kABytes : a_rows * kBK * 2;
+    const bool okA = A_MN ? make_tmap(&tmA, g.a, g.k, g.m, g.lda, 64, g.dtype) : make_tmap(&tmA, g.a, g.m, g.k, g.lda, a_rows, g.dtype);
+    // K-major B: a single CTA loads its B rows as two boxes of BN/2 rows (second one at the value rows for the
+    // gate|value split); a pair loads one box of 128 rows per CTA.
+    const bool okB = B_MN ? make_tmap(&tmB, g.b, g.k, g.b_rows, g.ldb, 64, g.dtype)
+                          : make_tmap(&tmB, g.b, g.b_rows, g.k, g.ldb, CG == 2 ? 128 : BN / 2, g.dtype);
     if (!okA || !okB) return MGR_ERR_CUDA;
     int* status = gemm_status_ptr(di);
     if (status == nullptr) return MGR_ERR_CUDA;
-    constexpr int n_step = n_step_of(EPI);
+    constexpr int n_step = n_step_of(EPI, BN);
     const int64_t tiles = ((g.m + kBM * CG - 1) / (kBM * CG)) * ((g.n_out + n_step - 1) / n_step);
     const int limit = g_sm_limit.load(std::memory_order_relaxed);
     const int sms = (limit > 0 && limit < di.sm_count) ? limit : di.sm_count;
@@ -579,7 +591,7 @@ int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     const T* aux = static_cast<const T*>(g.aux);
     const int m = static_cast<int>(g.m), n_out = static_cast<int>(g.n_out), k = static_cast<int>(g.k);
     if constexpr (CG == 1) {
-        gemm_kernel<EPI, A_MN, B_MN, 1, T><<<grid, kGemmThreads, kGemmSmem, s>>>(tmA, tmB, c, c2, aux, m, n_out, k, g.ldc, g.ld_aux, status);
+        gemm_kernel<EPI, A_MN, B_MN, 1, T, BN><<<grid, kGemmThreads, kGemmSmem, s>>>(tmA, tmB, c, c2, aux, m, n_out, k, g.ldc, g.ld_aux, a_box_bytes, status);
     } else {
         cudaLaunchConfig_t cfg = {};
         cfg.gridDim = dim3(grid);
@@ -593,7 +605,7 @@ int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
         at[0].val.clusterDim.z = 1;
         cfg.attrs = at;
         cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, gemm_kernel<EPI, A_MN, B_MN, 2, T>, tmA, tmB, c, c2, aux, m, n_out, k, g.ldc, g.ld_aux, status) != cudaSuccess) {
+        if (cudaLaunchKernelEx(&cfg, gemm_kernel<EPI, A_MN, B_MN, 2, T>, tmA, tmB, c, c2, aux, m, n_out, k, g.ldc, g.ld_aux, a_box_bytes, status) != cudaSuccess) {
             (void)cudaGetLastError();
             return MGR_ERR_LAUNCH_FAILED;
         }
@@ -614,6 +626,15 @@ constexpr double kPairFlopLimit = 2.0e12;
 
 template <int EPI, bool A_MN, bool B_MN, typename T>
 int launch_gemm_cg(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
+    // Few tiles (a skinny M, as in decoding): the 256-column tiles would leave most SMs without work while a
+    // handful stream the whole weight matrix; 64-column tiles spread it over 4x as many CTAs.
+    if constexpr ((EPI == kEpiPlain || EPI == kEpiSwiglu) && !A_MN && !B_MN) {
+        constexpr int wide_step = n_step_of(EPI, kBN);
+        const int64_t wide_tiles = ((g.m + kBM - 1) / kBM) * ((g.n_out + wide_step - 1) / wide_step);
+        const char* e = std::getenv("MGR_GEMM_NARROW");
+        const bool narrow = e != nullptr ? e[0] == '1' : wide_tiles * 2 <= di.sm_count;
+        if (narrow) return launch_gemm<EPI, A_MN, B_MN, 1, T, kBNSmall>(g, di, s);
+    }
     int cg = forced_cta_group();
     if (cg == 0) {
         const double flops = 2.0 * static_cast<double>(g.m) * static_cast<double>(g.b_rows) * static_cast<double>(g.k);
