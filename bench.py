@@ -462,8 +462,52 @@ def side_results(L, device, peak_gbs) -> dict:
         del sets
         torch.cuda.empty_cache()
     out["rmsnorm_bf16_hidden_sweep_2^20_elements_latency"] = lat
+    out["add_rmsnorm_bf16_65536x8192"] = add_rmsnorm_side_result(device, peak_gbs)
     out["swiglu_mlp_fp16_M4096_D4096_F6912"] = mlp_side_result(device)
     return out
+
+
+def add_rmsnorm_side_result(device, peak_gbs) -> dict:
+    """Residual add fused into the norm, bf16 [65536, 8192] (tensors of 1 GiB, far beyond L2): forward reads
+    x, residual and writes h, y (4*R*H*s bytes); backward reads dy, dres, h and writes dh (4*R*H*s).
+    Beside it the same work done the unfused way: torch add + norm forward (5 passes), norm backward +
+    torch add of the two gradients (6 passes)."""
+    import rmsnorm_cuda_ops as ops
+
+    rows, cols = 65536, 8192
+    g = torch.Generator(device=device).manual_seed(SEED)
+    x, res, dy, dres = (torch.randn(rows, cols, device=device, generator=g).to(torch.bfloat16) for _ in range(4))
+    w = (1 + 0.1 * torch.randn(cols, device=device, generator=g)).to(torch.bfloat16)
+    _, h, inv = ops.add_rmsnorm_forward(x, res, w, 1e-6)
+    pass_bytes = rows * cols * 2
+
+    def timed(fn, n=20):
+        for _ in range(3):
+            fn()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            fn()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / n
+
+    def unfused_fwd():
+        ops.rmsnorm_forward(x + res, w, 1e-6)
+
+    def unfused_bwd():
+        dx, _ = ops.rmsnorm_backward(dy, h, w, inv)
+        dx.add_(dres)
+
+    f_ms = timed(lambda: ops.add_rmsnorm_forward(x, res, w, 1e-6))
+    b_ms = timed(lambda: ops.add_rmsnorm_backward(dy, dres, h, w, inv))
+    uf_ms, ub_ms = timed(unfused_fwd), timed(unfused_bwd)
+    return {"fwd_ms": f_ms, "bwd_ms": b_ms,
+            "fwd_frac_of_peak": 4 * pass_bytes / (f_ms * 1e-3) / 1e9 / peak_gbs,
+            "bwd_frac_of_peak": 4 * pass_bytes / (b_ms * 1e-3) / 1e9 / peak_gbs,
+            "unfused_fwd_ms": uf_ms, "unfused_bwd_ms": ub_ms,
+            "speedup_fwd_bwd": (uf_ms + ub_ms) / (f_ms + b_ms)}
 
 
 def mlp_side_result(device) -> dict:
@@ -625,20 +669,30 @@ def run_block(args, device, warmup, peaks, peak_kind, world, rank) -> int:
         mlp = mlp.to(device).to(dt)
         local = mlp
     else:
-        mlp = sharding.TensorParallelSwiGLU(d, f, world, rank).to(device).to(dt)
-        mlp.overlap = os.environ.get("MGR_TP_OVERLAP", "1") != "0"   # all-reduces overlapped with GEMMs (default)
+        # MGR_TP_MODE=sp: rows sharded outside the MLP (norm on 1/P of the rows, all-gather / reduce-scatter per
+        # row slab); default: replicated rows, all-reduces overlapped with GEMMs (MGR_TP_OVERLAP=0: not overlapped)
+        seq_parallel = os.environ.get("MGR_TP_MODE", "ar") == "sp"
+        cls = sharding.SequenceParallelSwiGLU if seq_parallel else sharding.TensorParallelSwiGLU
+        mlp = cls(d, f, world, rank).to(device).to(dt)
+        mlp.overlap = os.environ.get("MGR_TP_OVERLAP", "1") != "0"
+        mlp.slabs = int(os.environ.get("MGR_TP_SLABS", mlp.slabs))
         local = mlp.local
     # nn.Linear's default init, U(-1/sqrt(fan_in), 1/sqrt(fan_in)), drawn on the device; fan_in of w3 is the FULL d_ff
     g = torch.Generator(device=device).manual_seed(SEED + 17 * rank)
     with torch.no_grad():
         local.w12.weight.copy_((torch.rand(local.w12.weight.shape, device=device, generator=g) * 2 - 1) / d ** 0.5)
         local.w3.weight.copy_((torch.rand(local.w3.weight.shape, device=device, generator=g) * 2 - 1) / f ** 0.5)
-    norm = RMSNorm(d, epsilon=EPS).to(device).to(dt)
+    seq_parallel = world > 1 and os.environ.get("MGR_TP_MODE", "ar") == "sp"
+    norm =(sharding.RowShardedRMSNorm(d, epsilon=EPS) if seq_parallel else RMSNorm(d, epsilon=EPS)).to(device).to(dt)
     gx = torch.Generator(device=device).manual_seed(SEED)            # replicated input: same seed on every rank
     with torch.no_grad():
         norm.weight.copy_((1 + 0.1 * torch.randn(d, device=device, generator=gx)).to(dt))
-    x = torch.randn(m, d, device=device, generator=gx).to(dt).requires_grad_(True)
+    x = torch.randn(m, d, device=device, generator=gx).to(dt)
     dy = torch.randn(m, d, device=device, generator=gx).to(dt)
+    if seq_parallel:                                                  # this rank's row block of the same tensors
+        r0, r1 = sharding.row_shard(m, world, rank)
+        x, dy = x[r0:r1].clone(), dy[r0:r1].clone()
+    x.requires_grad_(True)
     stream = torch.cuda.current_stream()
 
     def step():
@@ -681,7 +735,8 @@ def run_block(args, device, warmup, peaks, peak_kind, world, rank) -> int:
             "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": f"bf16 pre-norm block RMSNorm({d}) -> SwiGLU(d_ff {f}) over {m} tokens, forward+backward, "
-                                   f"tensor-parallel x{world}" + (" [REDUCED CASE]" if m != BLOCK_TOKENS else ""),
+                                   f"tensor-parallel x{world}" + (", rows sharded outside the MLP (sequence-parallel)" if seq_parallel else "")
+                                   + (" [REDUCED CASE]" if m != BLOCK_TOKENS else ""),
                        "tokens": m, "d_model": d, "d_ff": f, "d_ff_per_gpu": f1 - f0, "flops_per_step": flops,
                        "allreduce_bytes_per_step": 0 if world == 1 else 2 * m * d * 2, "seed": SEED},
             "tflops_per_gpu": flops / ms / 1e9 / world,

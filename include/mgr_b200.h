@@ -139,6 +139,31 @@ int mgr_rmsnorm_bwd(void* dx, void* dw, float* dw_f32, const void* dy, const voi
 int mgr_rmsnorm_bwd_noalloc(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, const void* w,
                             const float* inv_rms, int64_t rows, int64_t cols, int dtype, void* stream);
 
+/* Residual add fused into the norm, the pair of operations that opens a pre-norm transformer block:
+ *   h = x + residual;  y = RMSNorm(h) * w.
+ * The reference has no fused form; it replaces the sequence a caller of the reference writes as
+ * `h = x + residual` (a torch elementwise kernel) followed by RMSNormFunction.forward
+ * (megagemm/rmsnorm.py:22-36), and gives the same bits as that sequence run through mgr_rmsnorm_fwd:
+ * h is rounded to `dtype` first and the norm is taken of the rounded h.
+ *   y [rows, cols] out;  h [rows, cols] out (may be the buffer of x or of residual: in-place update of
+ *   the residual stream);  inv_rms [rows] fp32 out, may be NULL;  x, residual [rows, cols] in;  w [cols] in.
+ * Four passes over [rows, cols] (reads x, residual; writes h, y) instead of the five of the two-step
+ * sequence.
+ */
+int mgr_add_rmsnorm_fwd(void* y, void* h, float* inv_rms, const void* x, const void* residual, const void* w,
+                        int64_t rows, int64_t cols, float eps, int dtype, void* stream);
+
+/* Backward of the above: dh = dRMSNorm(h; dy) + dres, where dres is the gradient arriving along the
+ * residual stream (the gradient of whatever else consumed h). dh is at once the gradient of x and of
+ * residual. One rounding of the fp32 sum, where the two-step sequence (RMSNormFunction.backward,
+ * megagemm/rmsnorm.py:39-48, then autograd's accumulation of the two gradients of h) rounds twice.
+ *   dh [rows, cols] out (may be the buffer of dres);  dw, dw_f32, workspace as for mgr_rmsnorm_bwd (same
+ *   workspace size);  dy, dres, h [rows, cols] in;  w [cols] in;  inv_rms [rows] fp32 in.
+ */
+int mgr_add_rmsnorm_bwd(void* dh, void* dw, float* dw_f32, const void* dy, const void* dres, const void* h,
+                        const void* w, const float* inv_rms, int64_t rows, int64_t cols, int dtype,
+                        void* workspace, size_t workspace_bytes, void* stream);
+
 /* ------------------------------------------------------------------------------------------------
  * SwiGLU activation on an already-projected tensor: gv = [gate | val] of shape [m, 2f] (gate =
  * columns [0,f), val = columns [f,2f): the layout nn.Linear(d, 2*hidden) produces and

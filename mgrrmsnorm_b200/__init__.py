@@ -13,6 +13,8 @@ __version__ = "0.1.0"
 _EXPORTS = {
     "RMSNorm": "rmsnorm",
     "RMSNormFunction": "rmsnorm",
+    "AddRMSNorm": "rmsnorm",
+    "AddRMSNormFunction": "rmsnorm",
     "MegaGemmTriton": "swiglu",
     "MegaGemmFunction": "swiglu",
 }

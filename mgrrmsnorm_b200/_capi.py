@@ -42,6 +42,8 @@ SIGNATURES = {
     "mgr_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "mgr_rmsnorm_bwd": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _sz, _vp]),
     "mgr_rmsnorm_bwd_noalloc": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]),
+    "mgr_add_rmsnorm_fwd": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _f32, _int, _vp]),
+    "mgr_add_rmsnorm_bwd": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _sz, _vp]),
     "mgr_swiglu_act_fwd": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
     "mgr_swiglu_act_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp]),
     "mgr_swiglu_fused_fwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),

@@ -60,10 +60,12 @@ __device__ __forceinline__ float row_sum(float v, float (*red)[RegGeom<TPR>::kWa
     return v;
 }
 
-template <typename T, int TPR, int VPT>
+// ADD: the row that is normalised is h = round_T(x + res); h is also written out (the new residual
+// stream). h_out may be the buffer of x or of res: a thread reads its packets of a row before it writes them.
+template <typename T, int TPR, int VPT, bool ADD = false>
 __global__ void __launch_bounds__(RegGeom<TPR>::kBlock, RegGeom<TPR>::kFwdMinBlocks)
-rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* __restrict__ x,
-            const T* __restrict__ w, int64_t rows, int cols, float eps) {
+rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
+            const T* __restrict__ w, int64_t rows, int cols, float eps, const T* res = nullptr, T* h_out = nullptr) {
     using Geo = RegGeom<TPR>;
     constexpr int VEC = Elem<T>::kVec;
     __shared__ float red[2][Geo::kWarps];
@@ -92,6 +94,25 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* __restrict_
             const int v = t + k * TPR;
             xv[k] = (live && v < nvec) ? ld_stream16(xr + v) : make_uint4(0, 0, 0, 0);
             keep_packed(wv[k]);
+        }
+        if constexpr (ADD) {
+            const int64_t off = (live ? r : 0) * static_cast<int64_t>(cols);
+            const uint4* rr = reinterpret_cast<const uint4*>(res + off);
+            uint4* hr = reinterpret_cast<uint4*>(h_out + off);
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int v = t + k * TPR;
+                if (live && v < nvec) {
+                    const uint4 rv = ld_stream16(rr + v);
+                    float f[VEC], g[VEC];
+                    unpack16<T>(xv[k], f);
+                    unpack16<T>(rv, g);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) f[i] += g[i];
+                    xv[k] = pack16<T>(f);
+                    st_stream16(hr + v, xv[k]);
+                }
+            }
         }
         float ss = 0.f;
 #pragma unroll
@@ -125,14 +146,19 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* __restrict_
 // Backward. Each thread owns the same VPT*VEC columns for every row its CTA visits, so the dW
 // partial sums stay in registers until the CTA is done; the G row groups of a CTA are then folded in
 // shared memory (fixed order) and the CTA writes ONE fp32 partial row ws[blockIdx.x, :].
-template <typename T, int TPR, int VPT>
+// ADD: dx = round_T(dx_norm + dres), the gradient that arrives along the residual stream folded into the
+// same store (one rounding). dx may be the buffer of dres.
+template <typename T, int TPR, int VPT, bool ADD = false>
 __global__ void __launch_bounds__(RegGeom<TPR>::kBlock, (VPT <= 2 && TPR >= 256) ? (VPT == 1 ? 1536 : 1024) / RegGeom<TPR>::kBlock : RegGeom<TPR>::kBwdMinBlocks)
-rms_bwd_reg(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
-            const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int cols) {
+rms_bwd_reg(T* dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
+            const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int cols, const T* dres = nullptr) {
     using Geo = RegGeom<TPR>;
     constexpr int VEC = Elem<T>::kVec;
     constexpr int G = Geo::kGroups;
     constexpr bool kTwoPass = TPR >= 1024;   // 64 registers per thread: the row cannot stay resident
+    // Residual gradient fetched together with x and dy (all of a row's loads in flight at once) where the
+    // register budget is 128 per thread; elsewhere it is fetched just before the store.
+    constexpr bool kEarlyRes = ADD && !kTwoPass && !(VPT <= 2 && TPR >= 256);
     __shared__ float red[2][Geo::kWarps];
     __shared__ __align__(16) float fold[G > 1 ? (G - 1) * TPR * VPT * VEC : 4];
     int buf = 0;
@@ -162,12 +188,14 @@ rms_bwd_reg(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy
         const float rinv = live ? __ldg(inv_rms + r) : 0.f;
         if constexpr (!kTwoPass) {
             uint4 xv[VPT], gv[VPT];
+            uint4 dv[kEarlyRes ? VPT : 1];
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
                 const int v = t + k * TPR;
                 const bool on = live && v < nvec;
                 xv[k] = on ? ld_stream16(xr + v) : make_uint4(0, 0, 0, 0);
                 gv[k] = on ? ld_stream16(gr + v) : make_uint4(0, 0, 0, 0);
+                if constexpr (kEarlyRes) dv[k] = on ? ld_stream16(reinterpret_cast<const uint4*>(dres + off) + v) : make_uint4(0, 0, 0, 0);
                 keep_packed(wv[k]);
             }
 
@@ -199,6 +227,13 @@ rms_bwd_reg(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy
                         unpack16<T>(wv[k], fw);
 #pragma unroll
                         for (int i = 0; i < VEC; ++i) o[i] = rinv * (fg[i] * fw[i] - fx[i] * term2);
+                        if constexpr (ADD) {
+                            float fr[VEC];
+                            if constexpr (kEarlyRes) unpack16<T>(dv[k], fr);
+                            else unpack16<T>(ld_stream16(reinterpret_cast<const uint4*>(dres + off) + v), fr);
+#pragma unroll
+                            for (int i = 0; i < VEC; ++i) o[i] += fr[i];
+                        }
                         st_stream16(dr + v, pack16<T>(o));
                     }
                 }
@@ -240,6 +275,12 @@ rms_bwd_reg(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy
                     for (int i = 0; i < VEC; ++i) {
                         acc[k][i] += (fg[i] * fx[i]) * rinv;
                         o[i] = rinv * (fg[i] * fw[i] - fx[i] * term2);
+                    }
+                    if constexpr (ADD) {
+                        float fr[VEC];
+                        unpack16<T>(ld_stream16(reinterpret_cast<const uint4*>(dres + off) + v), fr);
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) o[i] += fr[i];
                     }
                     st_stream16(dr + v, pack16<T>(o));
                 }
@@ -333,18 +374,19 @@ __device__ __forceinline__ float block_sum_256(float v, float* red /* [8] */) {
     return s;
 }
 
-template <typename T>
+template <typename T, bool ADD = false>
 __global__ void __launch_bounds__(256)
-rms_fwd_scalar(T* __restrict__ y, float* __restrict__ inv_rms, const T* __restrict__ x,
-               const T* __restrict__ w, int64_t rows, int64_t cols, float eps) {
+rms_fwd_scalar(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
+               const T* __restrict__ w, int64_t rows, int64_t cols, float eps, const T* res = nullptr, T* h_out = nullptr) {
     __shared__ float red[8];
     const float inv_cols = 1.0f / static_cast<float>(cols);
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
-        const T* xr = x + r * cols;
+        const T* xr = ADD ? h_out + r * cols : x + r * cols;
         T* yr = y + r * cols;
         float ss = 0.f;
         for (int64_t j = threadIdx.x; j < cols; j += 256) {
-            const float f = to_f32(xr[j]);
+            if constexpr (ADD) h_out[r * cols + j] = from_f32<T>(to_f32(x[r * cols + j]) + to_f32(res[r * cols + j]));
+            const float f = to_f32(xr[j]);   // with ADD: the element this thread has just written
             ss += f * f;
         }
         ss = block_sum_256(ss, red);
@@ -355,10 +397,10 @@ rms_fwd_scalar(T* __restrict__ y, float* __restrict__ inv_rms, const T* __restri
     }
 }
 
-template <typename T>
+template <typename T, bool ADD = false>
 __global__ void __launch_bounds__(256)
-rms_bwd_dx_scalar(T* __restrict__ dx, const T* __restrict__ dy, const T* __restrict__ x,
-                  const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int64_t cols) {
+rms_bwd_dx_scalar(T* dx, const T* __restrict__ dy, const T* __restrict__ x,
+                  const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int64_t cols, const T* dres = nullptr) {
     __shared__ float red[8];
     const float inv_cols = 1.0f / static_cast<float>(cols);
     for (int64_t r = blockIdx.x; r < rows; r += gridDim.x) {
@@ -370,8 +412,11 @@ rms_bwd_dx_scalar(T* __restrict__ dx, const T* __restrict__ dy, const T* __restr
         for (int64_t j = threadIdx.x; j < cols; j += 256) c += (to_f32(gr[j]) * to_f32(w[j])) * to_f32(xr[j]);
         c = block_sum_256(c, red);
         const float term2 = c * (rinv * rinv) * inv_cols;
-        for (int64_t j = threadIdx.x; j < cols; j += 256)
-            dr[j] = from_f32<T>(rinv * (to_f32(gr[j]) * to_f32(w[j]) - to_f32(xr[j]) * term2));
+        for (int64_t j = threadIdx.x; j < cols; j += 256) {
+            float o = rinv * (to_f32(gr[j]) * to_f32(w[j]) - to_f32(xr[j]) * term2);
+            if constexpr (ADD) o += to_f32(dres[r * cols + j]);
+            dr[j] = from_f32<T>(o);
+        }
     }
 }
 
@@ -441,7 +486,7 @@ int resident_ctas(K kernel, int block, int* cache /* [kMaxDevices] */, int devic
     return n;
 }
 
-template <typename T, int I>
+template <typename T, int I, bool ADD = false>
 struct RegKernels {
     static constexpr int TPR = kRegShapes[I].tpr;
     static constexpr int VPT = kRegShapes[I].vpt;
@@ -451,41 +496,50 @@ struct RegKernels {
     static int64_t fwd_grid(int64_t rows, const DeviceInfo& di) {
         static int occ[kMaxDevices] = {0};
         const int64_t ngroups = (rows + G - 1) / G;
-        const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_fwd_reg<T, TPR, VPT>, BLOCK, occ, di.device);
+        const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_fwd_reg<T, TPR, VPT, ADD>, BLOCK, occ, di.device);
         return ngroups < cap ? ngroups : cap;
     }
     static int64_t bwd_grid(int64_t rows, const DeviceInfo& di) {
         static int occ[kMaxDevices] = {0};
         const int64_t ngroups = (rows + G - 1) / G;
-        const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_bwd_reg<T, TPR, VPT>, BLOCK, occ, di.device);
+        const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_bwd_reg<T, TPR, VPT, ADD>, BLOCK, occ, di.device);
         return ngroups < cap ? ngroups : cap;
     }
     static void fwd(T* y, float* inv, const T* x, const T* w, int64_t rows, int cols, float eps,
-                    const DeviceInfo& di, cudaStream_t s) {
-        rms_fwd_reg<T, TPR, VPT><<<static_cast<unsigned>(fwd_grid(rows, di)), BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps);
+                    const DeviceInfo& di, cudaStream_t s, const T* res, T* h_out) {
+        rms_fwd_reg<T, TPR, VPT, ADD><<<static_cast<unsigned>(fwd_grid(rows, di)), BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps, res, h_out);
     }
     static void bwd(T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv, int64_t rows,
-                    int cols, int64_t grid, cudaStream_t s) {
-        rms_bwd_reg<T, TPR, VPT><<<static_cast<unsigned>(grid), BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols);
+                    int cols, int64_t grid, cudaStream_t s, const T* dres) {
+        rms_bwd_reg<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres);
     }
 };
 
+// `res`/`h_out` (forward) and `dres` (backward) select the residual-add kernels when non-null.
 template <typename T, int I = 0>
 struct RegDispatch {
     static void fwd(int shape, T* y, float* inv, const T* x, const T* w, int64_t rows, int cols, float eps,
-                    const DeviceInfo& di, cudaStream_t s) {
-        if (shape == I) RegKernels<T, I>::fwd(y, inv, x, w, rows, cols, eps, di, s);
-        else if constexpr (I + 1 < kNumRegShapes) RegDispatch<T, I + 1>::fwd(shape, y, inv, x, w, rows, cols, eps, di, s);
+                    const DeviceInfo& di, cudaStream_t s, const T* res = nullptr, T* h_out = nullptr) {
+        if (shape == I) {
+            if (res != nullptr) RegKernels<T, I, true>::fwd(y, inv, x, w, rows, cols, eps, di, s, res, h_out);
+            else RegKernels<T, I, false>::fwd(y, inv, x, w, rows, cols, eps, di, s, nullptr, nullptr);
+        } else if constexpr (I + 1 < kNumRegShapes) {
+            RegDispatch<T, I + 1>::fwd(shape, y, inv, x, w, rows, cols, eps, di, s, res, h_out);
+        }
     }
-    static int64_t bwd_grid(int shape, int64_t rows, const DeviceInfo& di) {
-        if (shape == I) return RegKernels<T, I>::bwd_grid(rows, di);
-        if constexpr (I + 1 < kNumRegShapes) return RegDispatch<T, I + 1>::bwd_grid(shape, rows, di);
+    static int64_t bwd_grid(int shape, int64_t rows, const DeviceInfo& di, bool add = false) {
+        if (shape == I) return add ? RegKernels<T, I, true>::bwd_grid(rows, di) : RegKernels<T, I, false>::bwd_grid(rows, di);
+        if constexpr (I + 1 < kNumRegShapes) return RegDispatch<T, I + 1>::bwd_grid(shape, rows, di, add);
         return 0;
     }
     static void bwd(int shape, T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv,
-                    int64_t rows, int cols, int64_t grid, cudaStream_t s) {
-        if (shape == I) RegKernels<T, I>::bwd(dx, ws, dy, x, w, inv, rows, cols, grid, s);
-        else if constexpr (I + 1 < kNumRegShapes) RegDispatch<T, I + 1>::bwd(shape, dx, ws, dy, x, w, inv, rows, cols, grid, s);
+                    int64_t rows, int cols, int64_t grid, cudaStream_t s, const T* dres = nullptr) {
+        if (shape == I) {
+            if (dres != nullptr) RegKernels<T, I, true>::bwd(dx, ws, dy, x, w, inv, rows, cols, grid, s, dres);
+            else RegKernels<T, I, false>::bwd(dx, ws, dy, x, w, inv, rows, cols, grid, s, nullptr);
+        } else if constexpr (I + 1 < kNumRegShapes) {
+            RegDispatch<T, I + 1>::bwd(shape, dx, ws, dy, x, w, inv, rows, cols, grid, s, dres);
+        }
     }
 };
 
@@ -624,18 +678,24 @@ bool prefer_ring_bwd(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& 
 
 template <typename T>
 int fwd_typed(void* y, float* inv, const void* x, const void* w, int64_t rows, int64_t cols, float eps,
-              const DeviceInfo& di, cudaStream_t s) {
+              const DeviceInfo& di, cudaStream_t s, const void* res = nullptr, void* h_out = nullptr) {
     constexpr int VEC = Elem<T>::kVec;
     const Path forced = forced_path();
-    const bool packets = forced != Path::kScalar && cols % VEC == 0 && aligned_to(y, 16) && aligned_to(x, 16) && aligned_to(w, 16);
-    if (packets && forced != Path::kReg && (forced == Path::kRing || prefer_ring_fwd(rows, cols, sizeof(T), di))) {
+    const bool add = res != nullptr;   // the residual-add variants exist in the register and scalar families
+    const bool packets = forced != Path::kScalar && cols % VEC == 0 && aligned_to(y, 16) && aligned_to(x, 16) && aligned_to(w, 16) &&
+                         aligned_to(res, 16) && aligned_to(h_out, 16);
+    if (!add && packets && forced != Path::kReg && (forced == Path::kRing || prefer_ring_fwd(rows, cols, sizeof(T), di))) {
         const int st = fwd_ring_try<T>(static_cast<T*>(y), inv, static_cast<const T*>(x), static_cast<const T*>(w), rows, cols, eps, di, s);
         if (st <= 0) return st;
     }
     const int shape = packets ? reg_shape_for(cols / VEC) : -1;
     if (shape >= 0) {
         RegDispatch<T>::fwd(shape, static_cast<T*>(y), inv, static_cast<const T*>(x), static_cast<const T*>(w), rows,
-                            static_cast<int>(cols), eps, di, s);
+                            static_cast<int>(cols), eps, di, s, static_cast<const T*>(res), static_cast<T*>(h_out));
+    } else if (add) {
+        rms_fwd_scalar<T, true><<<static_cast<unsigned>(scalar_grid(rows, di)), 256, 0, s>>>(
+            static_cast<T*>(y), inv, static_cast<const T*>(x), static_cast<const T*>(w), rows, cols, eps,
+            static_cast<const T*>(res), static_cast<T*>(h_out));
     } else {
         rms_fwd_scalar<T><<<static_cast<unsigned>(scalar_grid(rows, di)), 256, 0, s>>>(
             static_cast<T*>(y), inv, static_cast<const T*>(x), static_cast<const T*>(w), rows, cols, eps);
@@ -654,6 +714,8 @@ int64_t bwd_partials(int64_t rows, int64_t cols, const DeviceInfo& di) {
         if (shape >= 0) {
             const int64_t g = RegDispatch<T>::bwd_grid(shape, rows, di);
             if (g > p) p = g;
+            const int64_t ga = RegDispatch<T>::bwd_grid(shape, rows, di, true);
+            if (ga > p) p = ga;
         }
         const BwdRingPlan rp = bwd_ring_plan(rows, cols, sizeof(T), di);
         if (rp.ok && rp.grid > p) p = rp.grid;
@@ -663,13 +725,14 @@ int64_t bwd_partials(int64_t rows, int64_t cols, const DeviceInfo& di) {
 
 template <typename T>
 int bwd_typed(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, const void* w, const float* inv,
-              int64_t rows, int64_t cols, float* ws, const DeviceInfo& di, cudaStream_t s) {
+              int64_t rows, int64_t cols, float* ws, const DeviceInfo& di, cudaStream_t s, const void* dres = nullptr) {
     constexpr int VEC = Elem<T>::kVec;
     const Path forced = forced_path();
+    const bool add = dres != nullptr;
     const bool packets = forced != Path::kScalar && cols % VEC == 0 && aligned_to(dx, 16) && aligned_to(dy, 16) &&
-                         aligned_to(x, 16) && aligned_to(w, 16);
+                         aligned_to(x, 16) && aligned_to(w, 16) && aligned_to(dres, 16);
     int64_t P = -1;
-    if (packets && forced != Path::kReg && (forced == Path::kRing || prefer_ring_bwd(rows, cols, sizeof(T), di))) {
+    if (!add && packets && forced != Path::kReg && (forced == Path::kRing || prefer_ring_bwd(rows, cols, sizeof(T), di))) {
         const BwdRingPlan plan = bwd_ring_plan(rows, cols, sizeof(T), di);
         int* status = plan.ok ? rms_status_ptr(di) : nullptr;
         if (status != nullptr) {
@@ -682,13 +745,18 @@ int bwd_typed(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, 
     if (P < 0) {
         const int shape = packets ? bwd_shape_for(cols / VEC) : -1;
         if (shape >= 0) {
-            P = RegDispatch<T>::bwd_grid(shape, rows, di);
+            P = RegDispatch<T>::bwd_grid(shape, rows, di, add);
             RegDispatch<T>::bwd(shape, static_cast<T*>(dx), ws, static_cast<const T*>(dy), static_cast<const T*>(x),
-                                static_cast<const T*>(w), inv, rows, static_cast<int>(cols), P, s);
+                                static_cast<const T*>(w), inv, rows, static_cast<int>(cols), P, s, static_cast<const T*>(dres));
         } else {
             P = rows < kScalarDwSlices ? rows : kScalarDwSlices;
-            rms_bwd_dx_scalar<T><<<static_cast<unsigned>(scalar_grid(rows, di)), 256, 0, s>>>(
-                static_cast<T*>(dx), static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(w), inv, rows, cols);
+            if (add)
+                rms_bwd_dx_scalar<T, true><<<static_cast<unsigned>(scalar_grid(rows, di)), 256, 0, s>>>(
+                    static_cast<T*>(dx), static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(w), inv, rows, cols,
+                    static_cast<const T*>(dres));
+            else
+                rms_bwd_dx_scalar<T><<<static_cast<unsigned>(scalar_grid(rows, di)), 256, 0, s>>>(
+                    static_cast<T*>(dx), static_cast<const T*>(dy), static_cast<const T*>(x), static_cast<const T*>(w), inv, rows, cols);
             int st = launch_status();
             if (st != MGR_OK) return st;
             dim3 grid(static_cast<unsigned>((cols + 127) / 128), static_cast<unsigned>(P));
@@ -731,22 +799,40 @@ int check_common(int64_t rows, int64_t cols, int dtype) {
 
 using namespace mgr;
 
-extern "C" int mgr_rmsnorm_fwd(void* y, float* inv_rms, const void* x, const void* w, int64_t rows, int64_t cols,
-                               float eps, int dtype, void* stream) {
+namespace mgr {
+namespace {
+// Shared by the plain and the residual-add forward; `add` says which (then res and h_out are required).
+int fwd_entry(void* y, float* inv_rms, const void* x, const void* w, int64_t rows, int64_t cols, float eps, int dtype,
+              void* stream, bool add, const void* res, void* h_out) {
     int st = check_common(rows, cols, dtype);
     if (st != MGR_OK) return st;
     if (rows == 0) return MGR_OK;
     if (y == nullptr || x == nullptr || w == nullptr) return MGR_ERR_NULL_PTR;
+    if (add && (res == nullptr || h_out == nullptr)) return MGR_ERR_NULL_PTR;
     const size_t es = dtype_size(dtype);
     if (!aligned_to(y, es) || !aligned_to(x, es) || !aligned_to(w, es) || !aligned_to(inv_rms, 4)) return MGR_ERR_MISALIGNED;
+    if (add && (!aligned_to(res, es) || !aligned_to(h_out, es))) return MGR_ERR_MISALIGNED;
     const DeviceInfo di = current_device_info();
     if (di.status != MGR_OK) return di.status;
     cudaStream_t s = static_cast<cudaStream_t>(stream);
+    if (!add) res = nullptr, h_out = nullptr;
     switch (dtype) {
-        case MGR_F32: return fwd_typed<float>(y, inv_rms, x, w, rows, cols, eps, di, s);
-        case MGR_F16: return fwd_typed<__half>(y, inv_rms, x, w, rows, cols, eps, di, s);
-        default: return fwd_typed<__nv_bfloat16>(y, inv_rms, x, w, rows, cols, eps, di, s);
+        case MGR_F32: return fwd_typed<float>(y, inv_rms, x, w, rows, cols, eps, di, s, res, h_out);
+        case MGR_F16: return fwd_typed<__half>(y, inv_rms, x, w, rows, cols, eps, di, s, res, h_out);
+        default: return fwd_typed<__nv_bfloat16>(y, inv_rms, x, w, rows, cols, eps, di, s, res, h_out);
     }
+}
+}  // namespace
+}  // namespace mgr
+
+extern "C" int mgr_rmsnorm_fwd(void* y, float* inv_rms, const void* x, const void* w, int64_t rows, int64_t cols,
+                               float eps, int dtype, void* stream) {
+    return fwd_entry(y, inv_rms, x, w, rows, cols, eps, dtype, stream, false, nullptr, nullptr);
+}
+
+extern "C" int mgr_add_rmsnorm_fwd(void* y, void* h, float* inv_rms, const void* x, const void* residual, const void* w,
+                                   int64_t rows, int64_t cols, float eps, int dtype, void* stream) {
+    return fwd_entry(y, inv_rms, x, w, rows, cols, eps, dtype, stream, true, residual, h);
 }
 
 extern "C" size_t mgr_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t cols, int dtype) {
@@ -762,9 +848,11 @@ extern "C" size_t mgr_rmsnorm_bwd_workspace_bytes(int64_t rows, int64_t cols, in
     return static_cast<size_t>(p) * static_cast<size_t>(cols) * sizeof(float);
 }
 
-extern "C" int mgr_rmsnorm_bwd(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, const void* w,
-                               const float* inv_rms, int64_t rows, int64_t cols, int dtype, void* workspace,
-                               size_t workspace_bytes, void* stream) {
+namespace mgr {
+namespace {
+int bwd_entry(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, const void* w, const float* inv_rms,
+              int64_t rows, int64_t cols, int dtype, void* workspace, size_t workspace_bytes, void* stream, bool add,
+              const void* dres) {
     int st = check_common(rows, cols, dtype);
     if (st != MGR_OK) return st;
     if (dw == nullptr && dw_f32 == nullptr) return MGR_ERR_NULL_PTR;
@@ -778,18 +866,34 @@ extern "C" int mgr_rmsnorm_bwd(void* dx, void* dw, float* dw_f32, const void* dy
     }
     if (dx == nullptr || dy == nullptr || x == nullptr || w == nullptr || inv_rms == nullptr || workspace == nullptr)
         return MGR_ERR_NULL_PTR;
+    if (add && dres == nullptr) return MGR_ERR_NULL_PTR;
     if (!aligned_to(dx, es) || !aligned_to(dy, es) || !aligned_to(x, es) || !aligned_to(w, es) ||
-        !aligned_to(inv_rms, 4) || !aligned_to(workspace, 16))
+        !aligned_to(inv_rms, 4) || !aligned_to(workspace, 16) || (add && !aligned_to(dres, es)))
         return MGR_ERR_MISALIGNED;
     const DeviceInfo di = current_device_info();
     if (di.status != MGR_OK) return di.status;
     if (workspace_bytes < mgr_rmsnorm_bwd_workspace_bytes(rows, cols, dtype)) return MGR_ERR_WORKSPACE_TOO_SMALL;
     float* ws = static_cast<float*>(workspace);
+    if (!add) dres = nullptr;
     switch (dtype) {
-        case MGR_F32: return bwd_typed<float>(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, ws, di, s);
-        case MGR_F16: return bwd_typed<__half>(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, ws, di, s);
-        default: return bwd_typed<__nv_bfloat16>(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, ws, di, s);
+        case MGR_F32: return bwd_typed<float>(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, ws, di, s, dres);
+        case MGR_F16: return bwd_typed<__half>(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, ws, di, s, dres);
+        default: return bwd_typed<__nv_bfloat16>(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, ws, di, s, dres);
     }
+}
+}  // namespace
+}  // namespace mgr
+
+extern "C" int mgr_rmsnorm_bwd(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, const void* w,
+                               const float* inv_rms, int64_t rows, int64_t cols, int dtype, void* workspace,
+                               size_t workspace_bytes, void* stream) {
+    return bwd_entry(dx, dw, dw_f32, dy, x, w, inv_rms, rows, cols, dtype, workspace, workspace_bytes, stream, false, nullptr);
+}
+
+extern "C" int mgr_add_rmsnorm_bwd(void* dh, void* dw, float* dw_f32, const void* dy, const void* dres, const void* h,
+                                   const void* w, const float* inv_rms, int64_t rows, int64_t cols, int dtype,
+                                   void* workspace, size_t workspace_bytes, void* stream) {
+    return bwd_entry(dh, dw, dw_f32, dy, h, w, inv_rms, rows, cols, dtype, workspace, workspace_bytes, stream, true, dres);
 }
 
 // Defined here, declared for capi_common.cu: reads (and optionally clears) this file's status word.

@@ -40,6 +40,16 @@ def _stream_ptr(device: torch.device) -> int:
     return torch.cuda.current_stream(device).cuda_stream
 
 
+def _out_or_new(out, shape, like: torch.Tensor, name: str) -> torch.Tensor:
+    """`out` checked as a contiguous tensor of `shape` with `like`'s dtype and device (e.g. a row slab of a
+    larger buffer), or a new tensor when it is None."""
+    if out is None:
+        return torch.empty(shape, device=like.device, dtype=like.dtype)
+    if tuple(out.shape) != tuple(shape) or out.dtype != like.dtype or out.device != like.device or not out.is_contiguous():
+        raise RuntimeError(f"{name} must be a contiguous {list(shape)} tensor of the operands' dtype and device")
+    return out
+
+
 def rmsnorm_forward(input: torch.Tensor, weight: torch.Tensor, epsilon: float):
     """[output, inv_rms] = RMSNorm forward of a 2-D tensor (binding.cpp:16-68)."""
     _check_input(input, "input")
@@ -105,6 +115,79 @@ def rmsnorm_backward(grad_output: torch.Tensor, input: torch.Tensor, weight: tor
     return rmsnorm_backward_full(grad_output, input, weight, inv_rms)[:2]
 
 
+def add_rmsnorm_forward(input: torch.Tensor, residual: torch.Tensor, weight: torch.Tensor, epsilon: float,
+                        inplace: bool = False):
+    """[output, hidden, inv_rms] with hidden = input + residual and output = RMSNorm(hidden) * weight.
+
+    One kernel for the `h = x + residual; y = norm(h)` pair that opens a pre-norm block; the same bits as
+    the torch add followed by rmsnorm_forward. `inplace=True` writes hidden over `residual` (the residual
+    stream is updated where it lies) and returns that tensor.
+    """
+    _check_input(input, "input")
+    _check_input(residual, "residual")
+    _check_input(weight, "weight")
+    if input.dim() != 2:
+        raise RuntimeError("Input must be 2D")
+    rows, cols = input.shape
+    if residual.shape != input.shape:
+        raise RuntimeError("residual shape must match input shape")
+    if weight.dim() != 1 or weight.shape[0] != cols:
+        raise RuntimeError("Weight size must match hidden size")
+    code = _dtype_code(input, "")
+    if weight.dtype != input.dtype or residual.dtype != input.dtype:
+        raise RuntimeError("input, residual and weight must share one dtype")
+    if not (input.device == residual.device == weight.device):
+        raise RuntimeError("all tensors must be on the same device")
+    L = _capi.lib()
+    with torch.cuda.device(input.device):
+        inv_rms = torch.empty((rows,), dtype=torch.float32, device=input.device)
+        output = torch.empty_like(input)
+        hidden = residual if inplace else torch.empty_like(input)
+        st = L.mgr_add_rmsnorm_fwd(output.data_ptr(), hidden.data_ptr(), inv_rms.data_ptr(), input.data_ptr(),
+                                   residual.data_ptr(), weight.data_ptr(), rows, cols, float(epsilon), code,
+                                   _stream_ptr(input.device))
+    _capi.check("Add+RMSNorm Forward CUDA kernel", st)
+    return [output, hidden, inv_rms]
+
+
+def add_rmsnorm_backward(grad_output: torch.Tensor, grad_hidden: torch.Tensor, hidden: torch.Tensor,
+                         weight: torch.Tensor, inv_rms: torch.Tensor, want_dw_f32: bool = False):
+    """[grad_hidden_total, grad_weight, grad_weight_fp32 | None]: the norm's input gradient plus the
+    gradient that arrives along the residual stream, rounded once. It is the gradient of both `input`
+    and `residual` of add_rmsnorm_forward."""
+    for t, n in ((grad_output, "grad_output"), (grad_hidden, "grad_hidden"), (hidden, "hidden"), (weight, "weight"),
+                 (inv_rms, "inv_rms")):
+        _check_input(t, n)
+    if hidden.dim() != 2:
+        raise RuntimeError("Input must be 2D")
+    rows, cols = hidden.shape
+    if grad_output.shape != hidden.shape or grad_hidden.shape != hidden.shape:
+        raise RuntimeError("gradient shapes must match the hidden shape")
+    if weight.dim() != 1 or weight.shape[0] != cols:
+        raise RuntimeError("Weight size must match hidden size")
+    if inv_rms.dtype != torch.float32 or inv_rms.numel() != rows:
+        raise RuntimeError("inv_rms must be a float32 tensor with one value per row")
+    code = _dtype_code(hidden, " for backward")
+    if not (grad_output.dtype == grad_hidden.dtype == weight.dtype == hidden.dtype):
+        raise RuntimeError("grad_output, grad_hidden, hidden and weight must share one dtype")
+    if not (grad_output.device == grad_hidden.device == hidden.device == weight.device == inv_rms.device):
+        raise RuntimeError("all tensors must be on the same device")
+    L = _capi.lib()
+    with torch.cuda.device(hidden.device):
+        grad_total = torch.empty_like(hidden)
+        grad_weight = torch.empty_like(weight)
+        dw_f32 = torch.empty((cols,), dtype=torch.float32, device=hidden.device) if want_dw_f32 else None
+        ws_bytes = int(L.mgr_rmsnorm_bwd_workspace_bytes(rows, cols, code))
+        ws = torch.empty((max(ws_bytes, 16),), dtype=torch.uint8, device=hidden.device)
+        st = L.mgr_add_rmsnorm_bwd(grad_total.data_ptr(), grad_weight.data_ptr(),
+                                   dw_f32.data_ptr() if dw_f32 is not None else None,
+                                   grad_output.data_ptr(), grad_hidden.data_ptr(), hidden.data_ptr(), weight.data_ptr(),
+                                   inv_rms.data_ptr(), rows, cols, code, ws.data_ptr(), ws.numel(),
+                                   _stream_ptr(hidden.device))
+    _capi.check("Add+RMSNorm Backward CUDA kernel", st)
+    return [grad_total, grad_weight, dw_f32]
+
+
 # ---------------------------------------------------------------------------------------------------
 # SwiGLU entry points. The reference has no native code here (its activation is a Triton kernel inside
 # megagemm/swiglu.py); these are what that file calls instead.
@@ -161,7 +244,7 @@ def _gemm_ok(*tensors: torch.Tensor) -> bool:
     return True
 
 
-def swiglu_fused_forward(x: torch.Tensor, w12: torch.Tensor, hidden_dim: int) -> torch.Tensor:
+def swiglu_fused_forward(x: torch.Tensor, w12: torch.Tensor, hidden_dim: int, out: torch.Tensor | None = None) -> torch.Tensor:
     """h[M, hidden] = silu(x w12[:hidden]^T) * (x w12[hidden:]^T) in one tensor-core kernel: what
     `self.w12(x)` followed by MegaGemmFunction computes (megagemm/swiglu.py:167-168), without the
     [M, 2*hidden] intermediate."""
@@ -175,7 +258,7 @@ def swiglu_fused_forward(x: torch.Tensor, w12: torch.Tensor, hidden_dim: int) ->
     m, d = x.shape
     L = _capi.lib()
     with torch.cuda.device(x.device):
-        h = torch.empty((m, hidden_dim), device=x.device, dtype=x.dtype)
+        h = _out_or_new(out, (m, hidden_dim), x, "out")
         st = L.mgr_swiglu_fused_fwd(h.data_ptr(), x.data_ptr(), w12.data_ptr(), m, d, hidden_dim, code, _stream_ptr(x.device))
     _capi.check("fused SwiGLU projection kernel", st)
     return h
@@ -206,7 +289,8 @@ def linear_tn(a: torch.Tensor, b: torch.Tensor, out: torch.Tensor | None = None)
     return c
 
 
-def gemm(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool = False, b_mn_major: bool = False) -> torch.Tensor:
+def gemm(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool = False, b_mn_major: bool = False,
+         out: torch.Tensor | None = None) -> torch.Tensor:
     """c[m, n] = op(a) op(b)^T on the tensor-core kernel. K-major operands are stored [m, k] / [n, k];
     MN-major ones are stored [k, m] / [k, n] (the transposed matrix as it already lies in memory), so
     the backward GEMMs of an nn.Linear need no transposed copy."""
@@ -223,7 +307,7 @@ def gemm(a: torch.Tensor, b: torch.Tensor, a_mn_major: bool = False, b_mn_major:
     code = _dtype_code(a, "")
     L = _capi.lib()
     with torch.cuda.device(a.device):
-        c = torch.empty((m, n), device=a.device, dtype=a.dtype)
+        c = _out_or_new(out, (m, n), a, "out")
         st = L.mgr_gemm(c.data_ptr(), a.data_ptr(), b.data_ptr(), m, n, k, a.shape[1], b.shape[1], n,
                         int(a_mn_major), int(b_mn_major), code, _stream_ptr(a.device))
     _capi.check("tensor-core GEMM kernel", st)
@@ -250,7 +334,8 @@ def swiglu_fused_backward(dh: torch.Tensor, x: torch.Tensor, w12: torch.Tensor, 
     return dgv
 
 
-def swiglu_fused_forward_save(x: torch.Tensor, w12: torch.Tensor, hidden_dim: int):
+def swiglu_fused_forward_save(x: torch.Tensor, w12: torch.Tensor, hidden_dim: int, out_h: torch.Tensor | None = None,
+                              out_gv: torch.Tensor | None = None):
     """(h[M, hidden], gv[M, 2*hidden]): the fused projection that also keeps the projection for backward,
     as the reference keeps w12_out (megagemm/swiglu.py:98)."""
     _check_input(x, "x")
@@ -263,15 +348,16 @@ def swiglu_fused_forward_save(x: torch.Tensor, w12: torch.Tensor, hidden_dim: in
     m, d = x.shape
     L = _capi.lib()
     with torch.cuda.device(x.device):
-        h = torch.empty((m, hidden_dim), device=x.device, dtype=x.dtype)
-        gv = torch.empty((m, 2 * hidden_dim), device=x.device, dtype=x.dtype)
+        h = _out_or_new(out_h, (m, hidden_dim), x, "out_h")
+        gv = _out_or_new(out_gv, (m, 2 * hidden_dim), x, "out_gv")
         st = L.mgr_swiglu_fused_fwd_save(h.data_ptr(), gv.data_ptr(), x.data_ptr(), w12.data_ptr(), m, d, hidden_dim, code,
                                          _stream_ptr(x.device))
     _capi.check("fused SwiGLU projection kernel", st)
     return h, gv
 
 
-def swiglu_dh_dgv(dy: torch.Tensor, w3: torch.Tensor, gv: torch.Tensor, hidden_dim: int) -> torch.Tensor:
+def swiglu_dh_dgv(dy: torch.Tensor, w3: torch.Tensor, gv: torch.Tensor, hidden_dim: int,
+                  out: torch.Tensor | None = None) -> torch.Tensor:
     """[d_gate | d_val] of shape [M, 2*hidden] from dy [M, d_model], w3 [d_model, hidden] and the stored
     projection gv: the dh = dy w3 GEMM with the activation backward as its epilogue."""
     for t, nme in ((dy, "dy"), (w3, "w3"), (gv, "gv")):
@@ -284,7 +370,7 @@ def swiglu_dh_dgv(dy: torch.Tensor, w3: torch.Tensor, gv: torch.Tensor, hidden_d
     code = _dtype_code(dy, " for backward")
     L = _capi.lib()
     with torch.cuda.device(dy.device):
-        dgv = torch.empty_like(gv)
+        dgv = _out_or_new(out, gv.shape, gv, "out")
         st = L.mgr_swiglu_dh_dgv(dgv.data_ptr(), dy.data_ptr(), w3.data_ptr(), gv.data_ptr(), m, d, hidden_dim, code,
                                  _stream_ptr(dy.device))
     _capi.check("fused dh/dGV kernel", st)

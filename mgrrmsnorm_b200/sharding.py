@@ -261,3 +261,137 @@ class TensorParallelSwiGLU(nn.Module):
             return _OverlappedTPMLP.apply(x, w12, w3, self.group, self.slabs)
         x = _ReduceBackward.apply(x, self.group)
         return _ReduceForward.apply(self.local(x), self.group)
+
+
+# ---------------------------------------------------------------------------------------------------
+# sequence-parallel form of the pre-norm block: rows sharded outside the MLP, hidden units inside it
+# ---------------------------------------------------------------------------------------------------
+
+def slab_bounds(local_rows: int, slabs: int) -> list[tuple[int, int]]:
+    """[a, b) row ranges that cut a rank's `local_rows` rows into at most `slabs` pieces, each a multiple of
+    8 rows long except possibly the last. The same cut on every rank, since all ranks hold equally many rows."""
+    if local_rows <= 0:
+        return []
+    step = -(-local_rows // max(1, slabs))
+    step = -(-step // 8) * 8
+    return [(a, min(local_rows, a + step)) for a in range(0, local_rows, step)]
+
+
+# Which GEMMs of the sequence-parallel MLP leave COMM_SMS SMs to the collectives in flight beside them:
+# "all" = every GEMM; "big" = per slab only the larger one (fused projection / dx GEMM); "small" = only the
+# smaller one (w3 GEMM / dh-dGV kernel). A collective queued while an unrestricted persistent GEMM holds
+# every SM starts when that GEMM ends. MGR_SP_LIMIT overrides (measurement aid).
+SP_LIMIT = "all"
+
+
+def _sp_limit(kind: str, device):
+    import contextlib
+    import os
+
+    mode = os.environ.get("MGR_SP_LIMIT", SP_LIMIT)
+    on = mode == "all" or mode == kind
+    return rmsnorm_cuda_ops.gemm_sm_limit(COMM_SMS, device) if on else contextlib.nullcontext()
+
+
+class _SequenceParallelMLP(torch.autograd.Function):
+    """One rank's share of the SwiGLU MLP when the tokens are sharded by rows outside it.
+
+    The rank holds `m` rows of the (already normalised) input and F/P hidden units of the weights. The
+    rows are cut into slabs; for slab s: all-gather that slab of every rank (P*m_s rows), fused
+    projection + w3 GEMM on those rows with the local hidden units, reduce-scatter the partial result
+    back so that each rank receives the sum for its own m_s rows. The MLP is row-wise independent, so
+    the gathered rows are simply processed in the order they arrive (slab-major, then rank) and kept
+    in that order for backward; no row is ever moved back into "global" order. The collectives of one
+    slab run beside the GEMMs of its neighbours (async, on the communicator's stream; the GEMMs leave
+    COMM_SMS SMs free).
+
+    Backward mirrors it: all-gather the output gradient slab by slab, dh/dGV kernel and dx GEMM per slab,
+    reduce-scatter each partial dx; the two weight-gradient GEMMs run once over all gathered rows.
+    Against the all-reduce form this moves the same bytes but leaves the norm (and every other row-wise
+    operation outside the MLP) with 1/P of the rows instead of a replicated copy.
+    """
+
+    @staticmethod
+    def forward(ctx, x_local, w12, w3, group, slabs):
+        ops = rmsnorm_cuda_ops
+        world = dist.get_world_size(group)
+        hidden = w3.shape[1]
+        d_out = w3.shape[0]
+        x2d = x_local.reshape(-1, x_local.shape[-1])
+        if not x2d.is_contiguous():
+            x2d = x2d.contiguous()
+        m, d = x2d.shape
+        cuts = slab_bounds(m, slabs)
+        needs_grad = any(ctx.needs_input_grad[:3])
+        xg = x2d.new_empty((world * m, d))                      # gathered rows, slab-major then rank
+        h = x2d.new_empty((world * m, hidden))
+        gv = x2d.new_empty((world * m, 2 * hidden)) if needs_grad else None
+        out = x2d.new_empty((m, d_out))
+        gathers = [dist.all_gather_into_tensor(xg[world * a:world * b], x2d[a:b], group=group, async_op=True)
+                   for a, b in cuts]
+        pending = []
+        for (a, b), wk in zip(cuts, gathers):
+            wk.wait()
+            ga, gb = world * a, world * b
+            with _sp_limit("big", x2d.device):
+                if needs_grad:
+                    ops.swiglu_fused_forward_save(xg[ga:gb], w12, hidden, out_h=h[ga:gb], out_gv=gv[ga:gb])
+                else:
+                    ops.swiglu_fused_forward(xg[ga:gb], w12, hidden, out=h[ga:gb])
+            with _sp_limit("small", x2d.device):
+                part = ops.linear_tn(h[ga:gb], w3)
+            pending.append((dist.reduce_scatter_tensor(out[a:b], part, op=dist.ReduceOp.SUM, group=group, async_op=True), part))
+        for wk, _ in pending:
+            wk.wait()
+        if needs_grad:
+            ctx.save_for_backward(xg, w12, w3, h, gv)
+        ctx.group, ctx.cuts, ctx.world = group, cuts, world
+        ctx.x_shape = x_local.shape
+        return out.view(x_local.shape[:-1] + (d_out,))
+
+    @staticmethod
+    def backward(ctx, grad_output):
+        ops = rmsnorm_cuda_ops
+        xg, w12, w3, h, gv = ctx.saved_tensors
+        world, cuts, group = ctx.world, ctx.cuts, ctx.group
+        hidden = w3.shape[1]
+        dy = grad_output.reshape(-1, grad_output.shape[-1])
+        if not dy.is_contiguous():
+            dy = dy.contiguous()
+        m = dy.shape[0]
+        dyg = dy.new_empty((world * m, dy.shape[1]))
+        dgv = torch.empty_like(gv)
+        dx = dy.new_empty((m, xg.shape[1]))
+        gathers = [dist.all_gather_into_tensor(dyg[world * a:world * b], dy[a:b], group=group, async_op=True)
+                   for a, b in cuts]
+        pending = []
+        for (a, b), wk in zip(cuts, gathers):
+            wk.wait()
+            ga, gb = world * a, world * b
+            with _sp_limit("small", dy.device):
+                ops.swiglu_dh_dgv(dyg[ga:gb], w3, gv[ga:gb], hidden, out=dgv[ga:gb])
+            with _sp_limit("big", dy.device):
+                part = ops.gemm(dgv[ga:gb], w12, False, True)
+            pending.append((dist.reduce_scatter_tensor(dx[a:b], part, op=dist.ReduceOp.SUM, group=group, async_op=True), part))
+        with ops.gemm_sm_limit(COMM_SMS, dy.device):      # the last reduce-scatter is in flight beside this one
+            dw12 = ops.gemm(dgv, xg, True, True) if ctx.needs_input_grad[1] else None
+        dw3 = ops.gemm(dyg, h, True, True) if ctx.needs_input_grad[2] else None
+        for wk, _ in pending:
+            wk.wait()
+        return dx.view(ctx.x_shape), dw12, dw3, None, None
+
+
+class SequenceParallelSwiGLU(TensorParallelSwiGLU):
+    """TensorParallelSwiGLU whose input and output are this rank's ROW block [.., m, D] of the batch
+    (every rank the same number of rows) instead of replicated tensors. Same weight shards, same
+    `from_full`. Put a RowShardedRMSNorm in front of it for the pre-norm block: the norm then touches
+    1/P of the rows, and its dW is the all-reduced fp32 sum."""
+
+    def forward(self, x_local: torch.Tensor) -> torch.Tensor:
+        w12, w3 = self.local.w12.weight, self.local.w3.weight
+        m = x_local.numel() // x_local.shape[-1] if x_local.numel() else 0
+        if m == 0 or m % 8 != 0 or x_local.shape[-1] % 8 != 0:
+            raise RuntimeError("sequence-parallel MLP needs a non-empty row block whose row count and width are multiples of 8")
+        if x_local.dtype != w12.dtype:
+            raise RuntimeError("input and weights must share one dtype")
+        return _SequenceParallelMLP.apply(x_local, w12, w3, self.group, self.slabs)

@@ -1,0 +1,179 @@
+"""Residual add fused into RMSNorm (mgr_add_rmsnorm_fwd / _bwd) on the GPU, through the operator API.
+
+The reference has no fused form; its users write `h = x + residual` and call RMSNormFunction
+(megagemm/rmsnorm.py:18-48). So the forward is held to two things: the same bits as that two-step
+sequence run through the unfused kernels, and the CPU oracle applied to the rounded sum. The backward
+(norm gradient + gradient arriving through h, one rounding) is held to the oracle's fp64 truth.
+"""
+import numpy as np
+import pytest
+import torch
+
+from oracle import oracle
+from tests.util import TORCH_DTYPES, assert_matches_truth, seeded_rmsnorm_inputs, to_np
+
+pytestmark = pytest.mark.gpu
+
+SHAPES = [(1, 2), (3, 8), (129, 128), (7, 1000), (33, 1024), (128, 2048), (127, 4096), (64, 5120), (300, 8192),
+          (40, 16384), (9, 32768), (3, 40000)]
+
+
+@pytest.fixture(scope="module")
+def ops(built_lib):
+    import rmsnorm_cuda_ops
+
+    return rmsnorm_cuda_ops
+
+
+def seeded(rows, cols, dtype, seed=77):
+    x, w, dy = seeded_rmsnorm_inputs(rows, cols, dtype, seed)
+    g = torch.Generator().manual_seed(seed + 1)
+    res = torch.randn(rows, cols, generator=g).to(TORCH_DTYPES[dtype])
+    dres = torch.randn(rows, cols, generator=g).to(TORCH_DTYPES[dtype])
+    return x, res, w, dy, dres
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("rows,cols", SHAPES)
+def test_matches_two_step_sequence_and_oracle(ops, rows, cols, dtype):
+    eps = 1e-6
+    x, res, w, dy, dres = seeded(rows, cols, dtype)
+    xd, rd, wd, dyd, drd = (t.cuda() for t in (x, res, w, dy, dres))
+
+    y, h, inv = ops.add_rmsnorm_forward(xd, rd, wd, eps)
+    h2 = xd + rd                                   # the reference user's first step (torch)
+    y2, inv2 = ops.rmsnorm_forward(h2, wd, eps)    # and the second
+    assert torch.equal(h, h2), "h must be the rounded sum torch produces"
+    assert torch.equal(y, y2) and torch.equal(inv, inv2), "fused forward must give the two-step bits"
+
+    hf = oracle.round_to(to_np(x) + to_np(res), dtype)   # fp32 add, one rounding: what torch's add does
+    assert np.array_equal(to_np(h), hf)
+    ty, tinv = oracle.rmsnorm_fwd(hf, to_np(w), eps)
+    assert_matches_truth(y, ty, dtype, "y")
+    assert_matches_truth(inv, tinv, "f32", "inv_rms")
+
+    dh, dw, dw32 = ops.add_rmsnorm_backward(dyd, drd, h, wd, inv, want_dw_f32=True)
+    tdx, tdw = oracle.rmsnorm_bwd(to_np(dy), hf, to_np(w), eps)
+    assert_matches_truth(dh, tdx + to_np(dres).astype(np.float64), dtype, "dh")
+    assert_matches_truth(dw32, tdw, "f32", "dw_f32", slack=4.0)
+    assert torch.equal(dw, dw32.to(dw.dtype))
+    # dW does not depend on the residual gradient: same bits as the unfused backward
+    _, dw_plain, dw32_plain = ops.rmsnorm_backward_full(dyd, h, wd, inv, want_dw_f32=True)
+    if cols * x.element_size() <= 16384 or rows < 8 * 148:   # same kernel family on both sides
+        assert torch.equal(dw32, dw32_plain) and torch.equal(dw, dw_plain)
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_in_place_residual_stream(ops, dtype):
+    x, res, w, dy, dres = seeded(700, 4096, dtype, seed=5)
+    xd, rd, wd, dyd, drd = (t.cuda() for t in (x, res, w, dy, dres))
+    y0, h0, inv0 = ops.add_rmsnorm_forward(xd, rd.clone(), wd, 1e-6)
+    r_inplace = rd.clone()
+    y1, h1, inv1 = ops.add_rmsnorm_forward(xd, r_inplace, wd, 1e-6, inplace=True)
+    assert h1.data_ptr() == r_inplace.data_ptr()
+    assert torch.equal(h1, h0) and torch.equal(y1, y0) and torch.equal(inv1, inv0)
+    # backward writing over the residual gradient, through the C ABI directly
+    from mgrrmsnorm_b200 import _capi
+
+    L = _capi.lib()
+    dh0, dw0, _ = ops.add_rmsnorm_backward(dyd, drd, h0, wd, inv0)
+    buf = drd.clone()
+    dw1 = torch.empty_like(wd)
+    nbytes = int(L.mgr_rmsnorm_bwd_workspace_bytes(700, 4096, _capi.MGR_F16 if dtype == "f16" else _capi.MGR_BF16))
+    ws = torch.empty(max(nbytes, 16), dtype=torch.uint8, device="cuda")
+    st = L.mgr_add_rmsnorm_bwd(buf.data_ptr(), dw1.data_ptr(), None, dyd.data_ptr(), buf.data_ptr(), h0.data_ptr(),
+                               wd.data_ptr(), inv0.data_ptr(), 700, 4096,
+                               _capi.MGR_F16 if dtype == "f16" else _capi.MGR_BF16, ws.data_ptr(), ws.numel(),
+                               torch.cuda.current_stream().cuda_stream)
+    assert st == 0
+    torch.cuda.synchronize()
+    assert torch.equal(buf, dh0) and torch.equal(dw1, dw0)
+
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+def test_unaligned_views_take_the_scalar_kernels(ops, dtype):
+    rows, cols = 37, 1001
+    x, res, w, dy, dres = seeded(rows, cols, dtype, seed=9)
+    td = TORCH_DTYPES[dtype]
+
+    def shifted(t):
+        flat = torch.empty(t.numel() + 1, dtype=td, device="cuda")
+        v = flat[1:].view(t.shape)
+        v.copy_(t)
+        return v
+
+    xd, rd, wd, dyd, drd = (shifted(t) for t in (x, res, w, dy, dres))
+    y, h, inv = ops.add_rmsnorm_forward(xd, rd, wd, 1e-6)
+    assert torch.equal(h, xd + rd)
+    y2, inv2 = ops.rmsnorm_forward(h, wd, 1e-6)
+    assert torch.equal(y, y2)
+    dh, dw, _ = ops.add_rmsnorm_backward(dyd, drd, h, wd, inv)
+    tdx, tdw = oracle.rmsnorm_bwd(to_np(dy), to_np(h), to_np(w), 1e-6)
+    assert_matches_truth(dh, tdx + to_np(dres).astype(np.float64), dtype, "dh")
+    assert_matches_truth(dw, tdw, dtype, "dw", slack=4.0)
+
+
+def test_errors(ops, built_lib):
+    from mgrrmsnorm_b200 import _capi
+
+    x = torch.zeros(4, 64, device="cuda", dtype=torch.float16)
+    w = torch.ones(64, device="cuda", dtype=torch.float16)
+    with pytest.raises(RuntimeError, match="residual shape"):
+        ops.add_rmsnorm_forward(x, x[:2].contiguous(), w, 1e-6)
+    with pytest.raises(RuntimeError, match="share one dtype"):
+        ops.add_rmsnorm_forward(x, x.float(), w, 1e-6)
+    L = _capi.lib()
+    y = torch.empty_like(x)
+    st = L.mgr_add_rmsnorm_fwd(y.data_ptr(), y.data_ptr(), None, x.data_ptr(), None, w.data_ptr(), 4, 64, 1e-6,
+                               _capi.MGR_F16, None)
+    assert st == _capi.MGR_ERR_NULL_PTR
+    st = L.mgr_add_rmsnorm_bwd(y.data_ptr(), w.data_ptr(), None, x.data_ptr(), None, x.data_ptr(), w.data_ptr(),
+                               torch.zeros(4, device="cuda").data_ptr(), 4, 64, _capi.MGR_F16, x.data_ptr(), 1 << 20, None)
+    assert st == _capi.MGR_ERR_NULL_PTR
+
+
+@pytest.mark.parametrize("dtype", ["f32", "bf16"])
+def test_module_matches_unfused_modules_in_a_two_layer_stack(dtype):
+    """Two pre-norm 'layers' (branch = a fixed linear map) written with AddRMSNorm against the same
+    stack written the reference user's way (torch add + RMSNorm): forward bits equal; gradients within
+    the rounding of the unfused path."""
+    from mgrrmsnorm_b200 import AddRMSNorm, RMSNorm
+
+    td = TORCH_DTYPES[dtype]
+    torch.manual_seed(3)
+    B, S, H = 3, 50, 1024
+    x0 = torch.randn(B, S, H, device="cuda").to(td)
+    r0 = torch.randn(B, S, H, device="cuda").to(td)
+    m = (torch.randn(H, H, device="cuda") / H ** 0.5).to(td)
+    wa = (1 + 0.1 * torch.randn(H, device="cuda")).to(td)
+    wb = (1 + 0.1 * torch.randn(H, device="cuda")).to(td)
+
+    def run(fused: bool):
+        x = x0.clone().requires_grad_(True)
+        r = r0.clone().requires_grad_(True)
+        if fused:
+            n1, n2 = AddRMSNorm(H, 1e-6).cuda().to(td), AddRMSNorm(H, 1e-6).cuda().to(td)
+        else:
+            n1, n2 = RMSNorm(H, 1e-6).cuda().to(td), RMSNorm(H, 1e-6).cuda().to(td)
+        with torch.no_grad():
+            n1.weight.copy_(wa)
+            n2.weight.copy_(wb)
+        if fused:
+            y1, h1 = n1(x, r)
+            y2, h2 = n2(y1 @ m, h1)
+        else:
+            h1 = x + r
+            y1 = n1(h1)
+            h2 = y1 @ m + h1
+            y2 = n2(h2)
+        out = (y2.float() * 0.01).sum() + (h2.float() * 0.02).sum()
+        out.backward()
+        return y2, h2, x.grad, r.grad, n1.weight.grad, n2.weight.grad
+
+    f, u = run(True), run(False)
+    assert torch.equal(f[0], u[0]) and torch.equal(f[1], u[1])
+    assert torch.equal(f[2], f[3]), "x and residual receive the same gradient"
+    tol = 1e-5 if dtype == "f32" else 2e-2
+    for a, b, name in zip(f[2:], u[2:], ("dx", "dres", "dw1", "dw2")):
+        scale = float(b.float().abs().max())
+        assert float((a.float() - b.float()).abs().max()) <= tol * max(scale, 1.0), name

@@ -8,8 +8,10 @@ import torch
 def test_package_exports_are_lazy_and_complete():
     import mgrrmsnorm_b200 as pkg
 
-    assert set(pkg.__all__) == {"RMSNorm", "RMSNormFunction", "MegaGemmTriton", "MegaGemmFunction", "__version__"}
-    for name in ("RMSNorm", "RMSNormFunction", "MegaGemmTriton", "MegaGemmFunction"):
+    reference_names = {"RMSNorm", "RMSNormFunction", "MegaGemmTriton", "MegaGemmFunction", "__version__"}
+    added = {"AddRMSNorm", "AddRMSNormFunction"}   # residual add fused into the norm; not in the reference
+    assert set(pkg.__all__) == reference_names | added
+    for name in sorted((reference_names | added) - {"__version__"}):
         assert getattr(pkg, name).__name__ == name
     with pytest.raises(AttributeError):
         pkg.NoSuchThing

@@ -125,3 +125,121 @@ def test_collectives_on_two_gloo_ranks():
         assert p.exitcode == 0
     assert sorted(r[0] for r in results) == [0, 1]
     assert all(r[1] and r[2] and r[3] for r in results), results
+
+
+# ---------------------------------------------------------------------------------------------------
+# sequence-parallel MLP: slab cuts, the gathered row order and the collectives, on two gloo ranks.
+# The kernels are replaced by a stand-in with the same signatures (fp64 torch on CPU), so what is
+# checked here is everything around them: which rows are gathered where, which partial sums are
+# scattered back to whom, and that the weight gradients cover every gathered row exactly once.
+# ---------------------------------------------------------------------------------------------------
+
+class _FakeKernels:
+    """Signatures of the rmsnorm_cuda_ops entry points _SequenceParallelMLP calls; test code only."""
+
+    class gemm_sm_limit:
+        def __init__(self, reserve, device=None):
+            pass
+
+        def __enter__(self):
+            return self
+
+        def __exit__(self, *exc):
+            return False
+
+    @staticmethod
+    def _act(gv, f):
+        g, v = gv[:, :f], gv[:, f:]
+        return torch.nn.functional.silu(g) * v
+
+    @classmethod
+    def swiglu_fused_forward_save(cls, x, w12, hidden, out_h=None, out_gv=None):
+        gv = x @ w12.T
+        out_gv.copy_(gv)
+        out_h.copy_(cls._act(gv, hidden))
+        return out_h, out_gv
+
+    @classmethod
+    def swiglu_fused_forward(cls, x, w12, hidden, out=None):
+        out.copy_(cls._act(x @ w12.T, hidden))
+        return out
+
+    @staticmethod
+    def linear_tn(a, b, out=None):
+        return a @ b.T
+
+    @staticmethod
+    def swiglu_dh_dgv(dy, w3, gv, hidden, out=None):
+        dh = dy @ w3
+        g, v = gv[:, :hidden], gv[:, hidden:]
+        s = torch.sigmoid(g)
+        out.copy_(torch.cat([dh * v * s * (1 + g * (1 - s)), dh * g * s], dim=1))
+        return out
+
+    @staticmethod
+    def gemm(a, b, a_mn_major=False, b_mn_major=False, out=None):
+        a2 = a.T if a_mn_major else a
+        b2 = b.T if b_mn_major else b
+        return a2 @ b2.T
+
+
+def test_slab_bounds():
+    for rows, slabs in ((2048, 4), (16, 4), (8, 4), (24, 2), (4096, 3)):
+        cuts = sharding.slab_bounds(rows, slabs)
+        assert cuts[0][0] == 0 and cuts[-1][1] == rows and len(cuts) <= slabs
+        assert all(a1 == b0 for (_, b0), (a1, _) in zip(cuts, cuts[1:]))
+        assert all((b - a) % 8 == 0 for a, b in cuts)
+    assert sharding.slab_bounds(0, 4) == []
+
+
+def _sp_worker(rank: int, world: int, port: int, q):
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world)
+    try:
+        sharding.rmsnorm_cuda_ops = _FakeKernels          # stand-in for the CUDA library (this process only)
+        rng = np.random.default_rng(11)
+        m_local, d, f = 24, 16, 8 * world
+        m = m_local * world
+        x = rng.standard_normal((m, d))
+        w12 = rng.standard_normal((2 * f, d)) / 4
+        w3 = rng.standard_normal((d, f)) / 4
+        dy = rng.standard_normal((m, d))
+        full = oracle.swiglu_mlp(x, w12, w3, dy=dy)
+        r0, r1 = sharding.row_shard(m, world, rank)
+        assert (r0, r1) == (rank * m_local, (rank + 1) * m_local)
+        ok = True
+        for slabs in (1, 2, 3):
+            xl = torch.from_numpy(x[r0:r1].copy()).requires_grad_(True)
+            w12l = sharding.tp_shard_w12(torch.from_numpy(w12), world, rank).requires_grad_(True)
+            w3l = sharding.tp_shard_w3(torch.from_numpy(w3), world, rank).requires_grad_(True)
+            out = sharding._SequenceParallelMLP.apply(xl, w12l, w3l, None, slabs)
+            out.backward(torch.from_numpy(dy[r0:r1].copy()))
+            ok &= np.allclose(out.detach().numpy(), full["y"][r0:r1], rtol=1e-10, atol=1e-10)
+            ok &= np.allclose(xl.grad.numpy(), full["dx"][r0:r1], rtol=1e-10, atol=1e-10)
+            f0, f1 = sharding.tp_hidden_slice(f, world, rank)
+            want12 = np.concatenate([full["dw12"][f0:f1], full["dw12"][f + f0:f + f1]])
+            ok &= np.allclose(w12l.grad.numpy(), want12, rtol=1e-10, atol=1e-10)
+            ok &= np.allclose(w3l.grad.numpy(), full["dw3"][:, f0:f1], rtol=1e-10, atol=1e-10)
+        # inference (no gradient wanted): the projection is not kept
+        with torch.no_grad():
+            out = sharding._SequenceParallelMLP.apply(torch.from_numpy(x[r0:r1].copy()), w12l.detach(), w3l.detach(), None, 2)
+        ok &= np.allclose(out.numpy(), full["y"][r0:r1], rtol=1e-10, atol=1e-10)
+        q.put((rank, bool(ok)))
+    finally:
+        dist.destroy_process_group()
+
+
+def test_sequence_parallel_mlp_on_two_gloo_ranks():
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_sp_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=120) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=60)
+        assert p.exitcode == 0
+    assert sorted(r[0] for r in results) == [0, 1]
+    assert all(r[1] for r in results), results

@@ -1,5 +1,5 @@
-"""Row-sharded RMSNorm and tensor-parallel SwiGLU on two real GPUs (NCCL), against the single-GPU
-result of the same library. Skipped with fewer than two devices. Ranks are child processes; they meet
+"""Row-sharded RMSNorm, tensor-parallel SwiGLU and the sequence-parallel pre-norm block on two real GPUs
+(NCCL), against the single-GPU result of the same library. Skipped with fewer than two devices. Ranks are child processes; they meet
 only in collectives between kernels, NVLS is switched off, and nothing waits on a peer inside a kernel."""
 import os
 import socket
@@ -84,8 +84,42 @@ def _worker(rank: int, world: int, port: int, q):
         # the two schedules run the same kernels on the same data: identical results
         ok_y &= torch.equal(outs[0][0], outs[1][0])
         ok_dx &= torch.equal(outs[0][1], outs[1][1])
+
+        # ---- sequence-parallel pre-norm block: rows sharded outside the MLP (norm on 1/P of the rows, all-gather,
+        # MLP on the local hidden units, reduce-scatter), against norm -> MLP on one GPU with the same weights
+        norm1 = RMSNorm(512, epsilon=1e-6).to(dev).half()
+        with torch.no_grad():
+            norm1.weight.copy_((1 + 0.1 * torch.randn(512, generator=g)).half().to(dev))
+        mlp.zero_grad()
+        a = xm.to(dev).requires_grad_(True)
+        ya = mlp(norm1(a))
+        ya.backward(dym.to(dev))
+        gw12 = torch.cat([mlp.w12.weight.grad[f0:f1], mlp.w12.weight.grad[mlp.hidden + f0:mlp.hidden + f1]])
+        sp = sharding.SequenceParallelSwiGLU.from_full(mlp, world, rank)
+        norm_s = sharding.RowShardedRMSNorm(512, epsilon=1e-6).to(dev).half()
+        with torch.no_grad():
+            norm_s.weight.copy_(norm1.weight)
+        r0, r1 = sharding.row_shard(xm.shape[0], world, rank)
+        ok_sp = True
+        sp_outs = []
+        for slabs in (1, 3):
+            sp.slabs = slabs
+            sp.zero_grad()
+            norm_s.zero_grad()
+            b = xm[r0:r1].to(dev).requires_grad_(True)
+            yb = sp(norm_s(b))
+            yb.backward(dym[r0:r1].to(dev))
+            ok_sp &= tuple(yb.shape) == (r1 - r0, 512)
+            ok_sp &= float((ya[r0:r1].float() - yb.float()).abs().max()) < tol
+            ok_sp &= float((a.grad[r0:r1].float() - b.grad.float()).abs().max()) < tol
+            ok_sp &= float((gw12.float() - sp.local.w12.weight.grad.float()).abs().max()) < 5e-2
+            ok_sp &= float((mlp.w3.weight.grad[:, f0:f1].float() - sp.local.w3.weight.grad.float()).abs().max()) < 5e-2
+            ok_sp &= float((norm1.weight.grad.float() - norm_s.weight.grad.float()).abs().max()) < 5e-2
+            sp_outs.append((yb.detach().clone(), b.grad.clone()))
+        # forward rows do not depend on how they are cut into slabs (each row is one independent GEMM row)
+        ok_sp &= torch.equal(sp_outs[0][0], sp_outs[1][0])
         torch.cuda.synchronize()
-        q.put((rank, ok_rows, ok_dw, ok_y, ok_dx, ok_w12, ok_w3))
+        q.put((rank, ok_rows, ok_dw, ok_y, ok_dx, ok_w12, ok_w3, bool(ok_sp)))
     finally:
         dist.barrier()
         dist.destroy_process_group()
@@ -106,4 +140,4 @@ def test_sharded_paths_on_two_gpus(built_lib):
         p.join(timeout=120)
         assert p.exitcode == 0
     for r in results:
-        assert all(r[1:]), f"rank {r[0]}: rows/dw/y/dx/dw12/dw3 = {r[1:]}"
+        assert all(r[1:]), f"rank {r[0]}: rows/dw/y/dx/dw12/dw3/sequence-parallel = {r[1:]}"
