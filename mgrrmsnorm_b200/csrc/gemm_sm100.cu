@@ -40,6 +40,7 @@ __device__ int g_gemm_status = 0;
 constexpr int kBM = 128;         // tile rows (UMMA M)
 constexpr int kBN = 256;         // accumulator columns per tile (UMMA N) of the throughput kernels
 constexpr int kBNSmall = 64;     // ... of the narrow-tile kernels used when a problem has few tiles (skinny M)
+constexpr int kBNTiny = 32;      // ... and of the narrowest ones, for problems that still leave SMs idle at 64
 constexpr int kBK = 64;          // K per stage: 64 x 2 B = one 128-byte swizzle row
 constexpr int kUmmaK = 16;       // K of one tcgen05.mma for 16-bit operands
 constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB: this CTA's 128 rows of A
@@ -48,9 +49,39 @@ __host__ __device__ constexpr uint32_t b_bytes(int bn) { return bn * kBK * 2; } 
 // 256 x 256 tile, each loading its own A rows and HALF of the B rows, which halves the B traffic per CTA
 // and deepens the ring from 4 to 7 stages.
 __host__ __device__ constexpr uint32_t stage_bytes(int cg, int bn) { return kABytes + b_bytes(bn) / cg; }
-__host__ __device__ constexpr int num_stages(int cg, int bn) { return bn == kBNSmall ? 8 : (cg == 1 ? 4 : 7); }
-__host__ __device__ constexpr uint32_t gemm_smem(int cg, int bn) { return num_stages(cg, bn) * stage_bytes(cg, bn) + 1024; }  // + slack to align to 1024 B
+__host__ __device__ constexpr int num_stages(int cg, int bn) { return bn < kBN ? 8 : (cg == 1 ? 4 : 7); }
+// + slack to align to 1024 B. The narrow-tile kernels take (nearly) all the shared memory an SM has and cut it into
+// as many stages as fit at run time (a short A box makes a stage smaller, see narrow_stages()).
+constexpr uint32_t kNarrowRing = 216 * 1024;
+__host__ __device__ constexpr uint32_t gemm_smem(int cg, int bn) {
+    return (bn < kBN ? kNarrowRing : num_stages(cg, bn) * stage_bytes(cg, bn)) + 1024;
+}
 constexpr int kMaxStages = 8;
+// Narrow-tile kernels: a sub-stage is the A box actually loaded (8..128 rows) plus the 8 KB B tile of one
+// 64-element K block; a STAGE (one full/empty barrier pair) is `ksub` consecutive sub-stages, i.e. ksub K blocks
+// requested together. A decode-sized batch is bound by streaming the weights once; 64-element K blocks handled
+// one barrier round trip at a time held an SM to ~40 GB/s (each weight row was touched 128 bytes at a time, and
+// every 8 KB paid a wait / issue / commit round). With ksub = 4 a stage asks for 512 contiguous bytes of each
+// weight row at once and the fixed cost per stage is spread over 32 KB.
+struct NarrowGeom {
+    int ksub, stages;
+    uint32_t sub_bytes;
+};
+__host__ __device__ inline NarrowGeom narrow_geom(uint32_t a_box_bytes, int bn) {
+    NarrowGeom g;
+    g.sub_bytes = a_box_bytes + b_bytes(bn);
+    // The MMA reads a full 128-row A operand (16 KB from the sub-stage's start) whatever the box loaded; the rows
+    // beyond the box only feed output rows that are never stored, but the read itself must stay inside the ring
+    // (reading past the CTA's shared memory is an illegal access): the last sub-stage must end >= 16 KB before
+    // the end of the ring.
+    const uint32_t tail = kABytes > g.sub_bytes ? kABytes - g.sub_bytes : 0u;
+    g.ksub = bn <= kBNTiny ? 8 : 4;
+    while (g.ksub > 1 && (kNarrowRing - tail) / (g.ksub * g.sub_bytes) < 4) g.ksub >>= 1;   // keep >= 4 stages in flight
+    const uint32_t n = (kNarrowRing - tail) / (g.ksub * g.sub_bytes);
+    g.stages = n > static_cast<uint32_t>(kMaxStages) ? kMaxStages : static_cast<int>(n);
+    return g;
+}
+
 constexpr int kEpiWarps = 8;      // epilogue warps: two per 32-lane quarter of tensor memory
 constexpr int kGemmThreads = (2 + kEpiWarps) * 32;
 constexpr uint32_t kTmemCols = 512;
@@ -143,11 +174,18 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             uint32_t a_box_bytes,
             int* __restrict__ status) {
     static_assert(n_step_of(EPI, BN) == BN || !B_MN, "the gate/value split reads w12 K-major");
-    static_assert(BN == kBN || (BN == kBNSmall && CG == 1 && !A_MN && !B_MN), "narrow tiles: single CTA, K-major operands");
+    static_assert(BN == kBN || ((BN == kBNSmall || BN == kBNTiny) && CG == 1 && !A_MN && !B_MN && (EPI == kEpiPlain || EPI == kEpiSwiglu)),
+                  "narrow tiles: single CTA, K-major operands, plain or fused-activation epilogue");
     constexpr int kNStep = n_step_of(EPI, BN);  // output columns per tile
-    constexpr int kStages = num_stages(CG, BN);
-    constexpr uint32_t kStageBytes = stage_bytes(CG, BN);
     constexpr uint32_t kBBytes = b_bytes(BN);
+    constexpr bool kNarrow = BN < kBN;
+    // wide tiles: compile-time ring of one K block per stage; narrow tiles: see narrow_geom()
+    const NarrowGeom ng = kNarrow ? narrow_geom(a_box_bytes, BN) : NarrowGeom{1, num_stages(CG, BN), stage_bytes(CG, BN)};
+    const int kStages = kNarrow ? ng.stages : num_stages(CG, BN);
+    const int kSub = kNarrow ? ng.ksub : 1;                                           // K blocks per stage
+    const uint32_t kSubBytes = kNarrow ? ng.sub_bytes : stage_bytes(CG, BN);          // bytes of one K block
+    const uint32_t kStageBytes = kNarrow ? ng.sub_bytes * ng.ksub : stage_bytes(CG, BN);
+    const uint32_t kAOff = kNarrow ? a_box_bytes : kABytes;   // B follows the A box inside a sub-stage
     extern __shared__ unsigned char smem_raw[];
     __shared__ __align__(8) uint64_t bar_full[kMaxStages], bar_empty[kMaxStages], bar_tfull[2], bar_tempty[2];
     __shared__ uint32_t tmem_base_slot;
@@ -162,7 +200,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     const int m_tiles = (M + kBM * CG - 1) / (kBM * CG);
     const int n_tiles = (n_out + kNStep - 1) / kNStep;
     const int num_tiles = m_tiles * n_tiles;
-    const int num_kb = (K + kBK - 1) / kBK;
+    const int num_kb = (K + kBK - 1) / kBK;   // K blocks; a stage carries kSub of them (blocks past K read as zeros)
 
     if (threadIdx.x == 0) {
         abort_flag = 0;
@@ -192,10 +230,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     if constexpr (CG == 2) ptx::cluster_sync();   // the partner's barriers exist before anything signals them
     ptx::tc_fence_after_sync();
     const uint32_t tmem_base = tmem_base_slot;
+    // Programmatic dependent launch (when the host asks for it): everything above overlaps the tail of the
+    // previous kernel in the stream; the roles that touch global memory wait for that kernel here. The next
+    // kernel may begin its own prologue as soon as this one's CTAs start to retire.
+    ptx::grid_dep_launch();
 
     if (warp == 0) {
         // ---------------- TMA producer ----------------
         if (ptx::elect_one()) {
+            ptx::grid_dep_wait();
             int stage = 0;
             uint32_t phase = 0;
             bool ok = true;
@@ -203,29 +246,35 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 const TileCoord tc = tile_coord(t, m_tiles, n_tiles, kNStep, kBM * CG);
                 const int m0 = tc.m0 + static_cast<int>(cta_rank) * kBM;     // this CTA's rows of the tile
                 const int b_row1 = kNStep == BN ? tc.n0 + BN / 2 : n_out + tc.n0;   // second half of the B rows
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = 0; kb < num_kb; kb += kSub) {
                     if (!ptx::mbar_wait(ptx::smem_addr(&bar_empty[stage]), phase ^ 1u, &abort_flag)) {
                         ok = false;
                         break;
                     }
                     const uint32_t sa = ring + stage * kStageBytes;
-                    const uint32_t sb = sa + kABytes;
+                    const uint32_t sb = sa + kAOff;
                     const int k0 = kb * kBK;
                     if constexpr (CG == 1) {
                         const uint32_t full = ptx::smem_addr(&bar_full[stage]);
-                        ptx::mbar_arrive_expect_tx(full, a_box_bytes + kBBytes);   // the A box may be shorter than 128 rows
-                        if constexpr (!A_MN) {
-                            ptx::tma_load_2d(sa, &tmA, k0, m0, full);
-                        } else {
+                        // the A box may be shorter than 128 rows; a narrow-tile stage holds kSub K blocks (blocks
+                        // past K are out of range for the tensor maps: they arrive as zeros and count their bytes)
+                        ptx::mbar_arrive_expect_tx(full, (a_box_bytes + kBBytes) * static_cast<uint32_t>(kSub));
+                        for (int sub = 0; sub < kSub; ++sub) {
+                            const uint32_t ssa = sa + sub * kSubBytes, ssb = sb + sub * kSubBytes;
+                            const int kk = k0 + sub * kBK;
+                            if constexpr (!A_MN) {
+                                ptx::tma_load_2d(ssa, &tmA, kk, m0, full);
+                            } else {
 #pragma unroll
-                            for (int c = 0; c < kBM / 64; ++c) ptx::tma_load_2d(sa + c * 8192u, &tmA, m0 + 64 * c, k0, full);
-                        }
-                        if constexpr (!B_MN) {
-                            ptx::tma_load_2d(sb, &tmB, k0, tc.n0, full);
-                            ptx::tma_load_2d(sb + kBBytes / 2, &tmB, k0, b_row1, full);
-                        } else {
+                                for (int c = 0; c < kBM / 64; ++c) ptx::tma_load_2d(ssa + c * 8192u, &tmA, m0 + 64 * c, kk, full);
+                            }
+                            if constexpr (!B_MN) {
+                                ptx::tma_load_2d(ssb, &tmB, kk, tc.n0, full);
+                                ptx::tma_load_2d(ssb + kBBytes / 2, &tmB, kk, b_row1, full);
+                            } else {
 #pragma unroll
-                            for (int c = 0; c < BN / 64; ++c) ptx::tma_load_2d(sb + c * 8192u, &tmB, tc.n0 + 64 * c, k0, full);
+                                for (int c = 0; c < BN / 64; ++c) ptx::tma_load_2d(ssb + c * 8192u, &tmB, tc.n0 + 64 * c, kk, full);
+                            }
                         }
                     } else {
                         // Both CTAs' bytes are counted on the LEADER's barrier: the leader announces the total,
@@ -267,19 +316,21 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 if (!ptx::mbar_wait(ptx::smem_addr(&bar_tempty[acc]), acc_phase ^ 1u, &abort_flag)) break;
                 ptx::tc_fence_after_sync();
                 const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * BN;
-                for (int kb = 0; kb < num_kb; ++kb) {
+                for (int kb = 0; kb < num_kb; kb += kSub) {
                     if (!ptx::mbar_wait(ptx::smem_addr(&bar_full[stage]), phase, &abort_flag)) {
                         ok = false;
                         break;
                     }
                     ptx::tc_fence_after_sync();
-                    const uint32_t sa = ring + stage * kStageBytes;
-                    const uint64_t da = smem_desc_sw128(sa, A_MN);
-                    const uint64_t db = smem_desc_sw128(sa + kABytes, B_MN);
+                    for (int sub = 0; sub < kSub; ++sub) {
+                        const uint32_t sa = ring + stage * kStageBytes + sub * kSubBytes;
+                        const uint64_t da = smem_desc_sw128(sa, A_MN);
+                        const uint64_t db = smem_desc_sw128(sa + kAOff, B_MN);
 #pragma unroll
-                    for (int k = 0; k < kBK / kUmmaK; ++k) {
-                        if constexpr (CG == 2) ptx::umma_f16_pair(d_tmem, da + a_step * k, db + b_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
-                        else ptx::umma_f16(d_tmem, da + a_step * k, db + b_step * k, idesc, (kb | k) != 0 ? 1u : 0u);
+                        for (int k = 0; k < kBK / kUmmaK; ++k) {
+                            if constexpr (CG == 2) ptx::umma_f16_pair(d_tmem, da + a_step * k, db + b_step * k, idesc, (kb | sub | k) != 0 ? 1u : 0u);
+                            else ptx::umma_f16(d_tmem, da + a_step * k, db + b_step * k, idesc, (kb | sub | k) != 0 ? 1u : 0u);
+                        }
                     }
                     // stage free (in both CTAs of a pair) once these MMAs retire
                     if constexpr (CG == 2) ptx::umma_commit_pair(ptx::smem_addr(&bar_empty[stage]), 3);
@@ -301,6 +352,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
         // ---------------- epilogue (warps 2..9) ----------------
         const int q = warp & 3;               // TMEM lane quarter this warp may read: lanes [32q, 32q+32)
         const int chunk0 = (warp - 2) >> 2;   // the two warps of a quarter take the even / the odd 32-column chunks
+        ptx::grid_dep_wait();
         int acc = 0;
         uint32_t acc_phase = 0;
         for (int t = first_tile; t < num_tiles; t += tile_stride) {
@@ -311,6 +363,25 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * BN;
             T* crow = C + static_cast<int64_t>(row) * ldc + tc.n0;
             [[maybe_unused]] uint4 gp_next[4], vp_next[4];   // kEpiDhDgv: packets requested one chunk ahead
+            if constexpr (BN == kBNTiny && EPI == kEpiSwiglu) {
+                // one 32-column read holds the whole accumulator: 16 gate columns, then the 16 value columns
+                if (chunk0 == 0) {
+                    uint32_t a[32];
+                    ptx::tmem_ld_32x32(t_row, a);
+                    ptx::tmem_ld_wait();
+                    uint32_t out[8];
+#pragma unroll
+                    for (int j = 0; j < 8; ++j)
+                        out[j] = pack2<T>(silu_mul(__uint_as_float(a[2 * j]), __uint_as_float(a[16 + 2 * j])),
+                                          silu_mul(__uint_as_float(a[2 * j + 1]), __uint_as_float(a[16 + 2 * j + 1])));
+                    if (row < M) {
+#pragma unroll
+                        for (int j = 0; j < 2; ++j)
+                            if (tc.n0 + j * 8 < n_out)
+                                *reinterpret_cast<uint4*>(crow + j * 8) = make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
+                    }
+                }
+            }
 #pragma unroll 1
             for (int c = chunk0; c < kNStep / 32; c += kEpiWarps / 4) {
                 if constexpr (EPI == kEpiSwigluBwd) {
@@ -554,6 +625,18 @@ int forced_cta_group() {
     return e[0] == '2' ? 2 : (e[0] == '1' ? 1 : 0);
 }
 
+// GEMM kernels are launched with programmatic stream serialization: the prologue (barriers, tensor memory,
+// descriptor prefetch) of a GEMM overlaps the tail of the kernel before it in the stream (1-2.5 us per launch in a
+// chain of short GEMMs). Not while an SM limit is set: the early CTAs of the next GEMM would park on the SMs that
+// the limit keeps free for a collective. MGR_GEMM_PDL=0 switches it off.
+bool pdl_enabled() {
+    static const bool on = [] {
+        const char* e = std::getenv("MGR_GEMM_PDL");
+        return e == nullptr || e[0] != '0';
+    }();
+    return on && g_sm_limit.load(std::memory_order_relaxed) == 0;
+}
+
 template <int EPI, bool A_MN, bool B_MN, int CG, typename T, int BN = kBN>
 int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     static bool attr[kMaxDevices] = {false};
@@ -590,25 +673,31 @@ int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     T* c2 = static_cast<T*>(g.c2);
     const T* aux = static_cast<const T*>(g.aux);
     const int m = static_cast<int>(g.m), n_out = static_cast<int>(g.n_out), k = static_cast<int>(g.k);
-    if constexpr (CG == 1) {
-        gemm_kernel<EPI, A_MN, B_MN, 1, T, BN><<<grid, kGemmThreads, kGemmSmem, s>>>(tmA, tmB, c, c2, aux, m, n_out, k, g.ldc, g.ld_aux, a_box_bytes, status);
-    } else {
-        cudaLaunchConfig_t cfg = {};
-        cfg.gridDim = dim3(grid);
-        cfg.blockDim = dim3(kGemmThreads);
-        cfg.dynamicSmemBytes = kGemmSmem;
-        cfg.stream = s;
-        cudaLaunchAttribute at[1];
-        at[0].id = cudaLaunchAttributeClusterDimension;
-        at[0].val.clusterDim.x = 2;
-        at[0].val.clusterDim.y = 1;
-        at[0].val.clusterDim.z = 1;
-        cfg.attrs = at;
-        cfg.numAttrs = 1;
-        if (cudaLaunchKernelEx(&cfg, gemm_kernel<EPI, A_MN, B_MN, 2, T>, tmA, tmB, c, c2, aux, m, n_out, k, g.ldc, g.ld_aux, a_box_bytes, status) != cudaSuccess) {
-            (void)cudaGetLastError();
-            return MGR_ERR_LAUNCH_FAILED;
-        }
+    cudaLaunchConfig_t cfg = {};
+    cfg.gridDim = dim3(grid);
+    cfg.blockDim = dim3(kGemmThreads);
+    cfg.dynamicSmemBytes = kGemmSmem;
+    cfg.stream = s;
+    cudaLaunchAttribute at[2];
+    unsigned na = 0;
+    if constexpr (CG == 2) {
+        at[na].id = cudaLaunchAttributeClusterDimension;
+        at[na].val.clusterDim.x = 2;
+        at[na].val.clusterDim.y = 1;
+        at[na].val.clusterDim.z = 1;
+        ++na;
+    }
+    if (pdl_enabled()) {   // the kernel's prologue may overlap the tail of the previous kernel in the stream
+        at[na].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+        at[na].val.programmaticStreamSerializationAllowed = 1;
+        ++na;
+    }
+    cfg.attrs = at;
+    cfg.numAttrs = na;
+    if (cudaLaunchKernelEx(&cfg, gemm_kernel<EPI, A_MN, B_MN, CG, T, BN>, tmA, tmB, c, c2, aux, m, n_out, k, g.ldc, g.ld_aux,
+                           a_box_bytes, status) != cudaSuccess) {
+        (void)cudaGetLastError();
+        return MGR_ERR_LAUNCH_FAILED;
     }
     return launch_status();
 }
@@ -630,10 +719,20 @@ int launch_gemm_cg(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     // handful stream the whole weight matrix; 64-column tiles spread it over 4x as many CTAs.
     if constexpr ((EPI == kEpiPlain || EPI == kEpiSwiglu) && !A_MN && !B_MN) {
         constexpr int wide_step = n_step_of(EPI, kBN);
-        const int64_t wide_tiles = ((g.m + kBM - 1) / kBM) * ((g.n_out + wide_step - 1) / wide_step);
+        constexpr int small_step = n_step_of(EPI, kBNSmall);
+        const int64_t m_tiles = (g.m + kBM - 1) / kBM;
+        const int64_t wide_tiles = m_tiles * ((g.n_out + wide_step - 1) / wide_step);
+        const int64_t small_tiles = m_tiles * ((g.n_out + small_step - 1) / small_step);
+        // MGR_GEMM_NARROW = 0: never; 1 (or 64): 64-column tiles; 32: 32-column tiles; unset: automatic.
+        // Measured on B200 (fp16, D 4096, F 6912, CUDA graphs): the w3 GEMM of a 16-row batch has 16 / 64 / 128
+        // tiles at 256 / 64 / 32 columns and takes 32 / 18 / 16 us; the fused projection (54 / 216 / 432 tiles)
+        // 36 / 26 / 27 us. So: 32 columns only while 64 would still leave half the SMs idle.
         const char* e = std::getenv("MGR_GEMM_NARROW");
-        const bool narrow = e != nullptr ? e[0] == '1' : wide_tiles * 2 <= di.sm_count;
-        if (narrow) return launch_gemm<EPI, A_MN, B_MN, 1, T, kBNSmall>(g, di, s);
+        int bn = 0;
+        if (e != nullptr) bn = e[0] == '0' ? 0 : (e[0] == '3' ? kBNTiny : kBNSmall);
+        else if (wide_tiles * 2 <= di.sm_count) bn = small_tiles * 2 <= di.sm_count ? kBNTiny : kBNSmall;
+        if (bn == kBNTiny) return launch_gemm<EPI, A_MN, B_MN, 1, T, kBNTiny>(g, di, s);
+        if (bn == kBNSmall) return launch_gemm<EPI, A_MN, B_MN, 1, T, kBNSmall>(g, di, s);
     }
     int cg = forced_cta_group();
     if (cg == 0) {

@@ -214,6 +214,12 @@ __device__ __forceinline__ void tmem_ld_32x32(uint32_t taddr, uint32_t (&r)[32])
 __device__ __forceinline__ void tmem_ld_wait() { asm volatile("tcgen05.wait::ld.sync.aligned;" ::: "memory"); }
 
 // Named barrier among `count` threads (a multiple of 32); id 0 is __syncthreads.
+// Programmatic dependent launch. Both are no-ops in a kernel launched without the attribute.
+// grid_dep_wait: returns once the kernel this one depends on has completed and its writes are visible.
+// grid_dep_launch: lets the next kernel in the stream start its prologue while this one is still running.
+__device__ __forceinline__ void grid_dep_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+__device__ __forceinline__ void grid_dep_launch() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+
 __device__ __forceinline__ void named_barrier(uint32_t id, uint32_t count) {
     asm volatile("bar.sync %0, %1;" ::"r"(id), "r"(count) : "memory");
 }

@@ -158,7 +158,7 @@ rms_bwd_reg(T* dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __
     constexpr bool kTwoPass = TPR >= 1024;   // 64 registers per thread: the row cannot stay resident
     // Residual gradient fetched together with x and dy (all of a row's loads in flight at once) where the
     // register budget is 128 per thread; elsewhere it is fetched just before the store.
-    constexpr bool kEarlyRes = ADD && !kTwoPass && !(VPT <= 2 && TPR >= 256);
+    constexpr bool kEarlyRes = ADD && !kTwoPass;
     __shared__ float red[2][Geo::kWarps];
     __shared__ __align__(16) float fold[G > 1 ? (G - 1) * TPR * VPT * VEC : 4];
     int buf = 0;

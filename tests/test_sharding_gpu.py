@@ -47,10 +47,15 @@ def _worker(rank: int, world: int, port: int, q):
         ys.backward(dy[r0:r1].to(dev))
         ok_rows = torch.equal(ys, yf[r0:r1]) and torch.equal(xs.grad, xf.grad[r0:r1])
         # fp32 partial sums are added across ranks before the single rounding: at most one bf16 ulp from
-        # the one-GPU result (a different fp32 summation order next to a rounding boundary)
+        # the one-GPU result (a different fp32 summation order next to a rounding boundary). Columns whose sum
+        # nearly cancels (|dW| << the terms' size) carry the fp32 summation error itself, hence the absolute floor.
         dws, dwf = shard.weight.grad.float(), full.weight.grad.float()
-        ulp = torch.maximum(dws.abs(), dwf.abs()) * 2.0 ** -7
+        ulp = torch.maximum(dws.abs(), dwf.abs()) * 2.0 ** -7 + 1e-4
+        worst = int(((dws - dwf).abs() - ulp).argmax())
         ok_dw = bool(((dws - dwf).abs() <= ulp).all()) and float((dws != dwf).float().mean()) < 0.05
+        if not ok_dw:
+            ok_dw = (f"dw differs: column {worst}: {float(dws[worst])!r} vs {float(dwf[worst])!r}; "
+                     f"{float((dws != dwf).float().mean()):.4f} of the columns differ")
 
         # ---- tensor-parallel MLP: d_model 512, hidden 1024 split over 2 ranks, fp16
         torch.manual_seed(7)
@@ -100,7 +105,15 @@ def _worker(rank: int, world: int, port: int, q):
         with torch.no_grad():
             norm_s.weight.copy_(norm1.weight)
         r0, r1 = sharding.row_shard(xm.shape[0], world, rank)
-        ok_sp = True
+        sp_bad = []          # names of the checks that failed, for the assertion message
+
+        def close(name, got, want, rel):
+            # |got - want| <= rel * max|want|: the two paths round their fp16 intermediates at different points
+            # (partial sums are rounded before the cross-rank sum), so the error scales with the values' size
+            err = float((got.float() - want.float()).abs().max())
+            if not err <= rel * max(float(want.float().abs().max()), 1.0):
+                sp_bad.append(f"{name}: err {err:.4g} vs max {float(want.float().abs().max()):.4g}")
+
         sp_outs = []
         for slabs in (1, 3):
             sp.slabs = slabs
@@ -109,17 +122,20 @@ def _worker(rank: int, world: int, port: int, q):
             b = xm[r0:r1].to(dev).requires_grad_(True)
             yb = sp(norm_s(b))
             yb.backward(dym[r0:r1].to(dev))
-            ok_sp &= tuple(yb.shape) == (r1 - r0, 512)
-            ok_sp &= float((ya[r0:r1].float() - yb.float()).abs().max()) < tol
-            ok_sp &= float((a.grad[r0:r1].float() - b.grad.float()).abs().max()) < tol
-            ok_sp &= float((gw12.float() - sp.local.w12.weight.grad.float()).abs().max()) < 5e-2
-            ok_sp &= float((mlp.w3.weight.grad[:, f0:f1].float() - sp.local.w3.weight.grad.float()).abs().max()) < 5e-2
-            ok_sp &= float((norm1.weight.grad.float() - norm_s.weight.grad.float()).abs().max()) < 5e-2
+            if tuple(yb.shape) != (r1 - r0, 512):
+                sp_bad.append("shape")
+            close(f"y/{slabs}", yb, ya[r0:r1], 2e-2)
+            close(f"dx/{slabs}", b.grad, a.grad[r0:r1], 2e-2)
+            close(f"dw12/{slabs}", sp.local.w12.weight.grad, gw12, 2e-2)
+            close(f"dw3/{slabs}", sp.local.w3.weight.grad, mlp.w3.weight.grad[:, f0:f1], 2e-2)
+            close(f"dw_norm/{slabs}", norm_s.weight.grad, norm1.weight.grad, 2e-2)
             sp_outs.append((yb.detach().clone(), b.grad.clone()))
         # forward rows do not depend on how they are cut into slabs (each row is one independent GEMM row)
-        ok_sp &= torch.equal(sp_outs[0][0], sp_outs[1][0])
+        if not torch.equal(sp_outs[0][0], sp_outs[1][0]):
+            sp_bad.append("forward differs between 1 and 3 slabs: max %.4g" % float((sp_outs[0][0].float() - sp_outs[1][0].float()).abs().max()))
+        ok_sp = "; ".join(sp_bad) if sp_bad else True
         torch.cuda.synchronize()
-        q.put((rank, ok_rows, ok_dw, ok_y, ok_dx, ok_w12, ok_w3, bool(ok_sp)))
+        q.put((rank, ok_rows, ok_dw, ok_y, ok_dx, ok_w12, ok_w3, ok_sp))
     finally:
         dist.barrier()
         dist.destroy_process_group()
@@ -140,4 +156,4 @@ def test_sharded_paths_on_two_gpus(built_lib):
         p.join(timeout=120)
         assert p.exitcode == 0
     for r in results:
-        assert all(r[1:]), f"rank {r[0]}: rows/dw/y/dx/dw12/dw3/sequence-parallel = {r[1:]}"
+        assert all(v is True or v == 1 for v in r[1:]), f"rank {r[0]}: rows/dw/y/dx/dw12/dw3/sequence-parallel = {r[1:]}"
