@@ -749,6 +749,81 @@ def run_block(args, device, warmup, peaks, peak_kind, world, rank) -> int:
     return 0
 
 
+def run_decode(args, device, warmup, peaks, peak_kind) -> int:
+    """Inference-sized MLP forward: fp16, d_model 4096, hidden 6912, --tokens rows (default 16), no autograd.
+    Two kernels (fused projection, w3 GEMM) whose cost is reading the 162 MB of weights once, so the bound is
+    HBM: achieved = weight bytes / time. Timed from a CUDA graph of the two launches (a decoding loop replays
+    graphs; host launch gaps would otherwise dominate a 40 us step); the weights exceed L2, and each replay
+    streams all of them again. Beside it: torch's library GEMMs + elementwise activation on the same tensors."""
+    import torch.nn.functional as F
+
+    from mgrrmsnorm_b200 import MegaGemmTriton
+    from mgrrmsnorm_b200 import rmsnorm_cuda_ops as ops
+
+    m = args.tokens if args.tokens != MLP_TOKENS else 16
+    torch.manual_seed(SEED)
+    mlp = MegaGemmTriton(MLP_D).to(device).half()
+    f = mlp.hidden
+    w12, w3 = mlp.w12.weight.detach(), mlp.w3.weight.detach()
+    g = torch.Generator(device=device).manual_seed(SEED)
+    x = torch.randn(m, MLP_D, device=device, generator=g).half()
+    h0 = ops.swiglu_fused_forward(x, w12, f)
+
+    def ours():
+        return ops.linear_tn(ops.swiglu_fused_forward(x, w12, f), w3)
+
+    def library():
+        gv = F.linear(x, w12)
+        return F.linear(F.silu(gv[:, :f]) * gv[:, f:], w3)
+
+    per_graph = 4
+
+    def graph_us(fn, replays):
+        fn()
+        torch.cuda.synchronize()
+        gr = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(gr):
+            for _ in range(per_graph):
+                fn()
+        for _ in range(warmup):
+            gr.replay()
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(replays):
+            gr.replay()
+        e1.record()
+        torch.cuda.synchronize()
+        return e0.elapsed_time(e1) / (replays * per_graph) * 1e3
+
+    replays = max(1, args.steps // per_graph)
+    sampler = ClockSampler(device.index or 0)
+    sampler.start()
+    t0 = time.perf_counter()
+    us = graph_us(ours, replays)
+    t1 = time.perf_counter()
+    sampler.stop()
+    us_proj = graph_us(lambda: ops.swiglu_fused_forward(x, w12, f), replays)
+    us_w3 = graph_us(lambda: ops.linear_tn(h0, w3), replays)
+    us_lib = graph_us(library, replays)
+    wbytes = (w12.numel() + w3.numel()) * 2
+    peak = float(peaks["hbm_gbs"])
+    line = {
+        "metric": "SwiGLU MLP forward (decode) weight GB/s", "value": wbytes / us / 1e3, "unit": "GB/s", "n_gpus": 1,
+        "steps": replays * per_graph, "warmup": warmup * per_graph, "ms_per_step": us / 1e3, "higher_is_better": True, "scaling": "weak",
+        "vs_baseline": None, "dtype": "f16", "data": "synthetic",
+        "config": {"workload": f"fp16 SwiGLU MLP forward, {m} tokens, d_model {MLP_D}, hidden {f}; CUDA graph of the two kernels; "
+                               "weights (162 MB) larger than L2, streamed again by every step", "tokens": m, "seed": SEED},
+        "roofline": {"bound": "hbm", "achieved": wbytes / us / 1e3, "peak": peak, "unit": "GB/s", "frac": wbytes / us / 1e3 / peak,
+                     "traffic": None, "peak_source": f"of {peak_kind} (copy bandwidth)"},
+        "us": {"step": us, "fused_projection_alone": us_proj, "w3_gemm_alone": us_w3, "weights_at_peak": wbytes / peak / 1e3,
+               "library_gemms_plus_activation": us_lib},
+        "gpu_launches": 2 * replays * per_graph, "clocks": sampler.summary(t0, t1),
+    }
+    print(json.dumps(line), flush=True)
+    return 0
+
+
 def time_cpu_mlp(mlp, f) -> dict:
     """The reference's CPU path for the MLP: the PyTorchSwiGLU formula (benchmark_swiglu.py:40-58) in fp32
     on the host cores, forward+backward, on a 128-token sample of the batch."""
@@ -784,9 +859,10 @@ def main(argv=None) -> int:
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
     ap.add_argument("--rows", type=int, default=ROWS_PER_GPU,
                     help="rows per GPU; anything but the default is a reduced case for profiler captures, not a bench value")
-    ap.add_argument("--workload", choices=["rmsnorm", "mlp", "block"], default="rmsnorm",
+    ap.add_argument("--workload", choices=["rmsnorm", "mlp", "block", "decode"], default="rmsnorm",
                     help="rmsnorm (default, the headline); mlp: SwiGLU MLP fp16 d_model 4096 hidden 6912 forward+backward, 1 GPU; "
-                         "block: bf16 pre-norm block RMSNorm(8192) -> SwiGLU(d_ff 28672) over 16384 tokens, tensor-parallel over --gpus")
+                         "block: bf16 pre-norm block RMSNorm(8192) -> SwiGLU(d_ff 28672) over 16384 tokens, tensor-parallel over --gpus; "
+                         "decode: the fp16 MLP forward alone at --tokens rows (default 16), bound by streaming the weights")
     ap.add_argument("--tokens", type=int, default=MLP_TOKENS,
                     help="tokens for --workload mlp; anything but the default is a reduced case for profiler captures")
     args = ap.parse_args(argv)
@@ -825,6 +901,11 @@ def main(argv=None) -> int:
         return run_mlp(args, L, device, warmup, peaks, peak_kind, sms.value)
     if args.workload == "block":
         return run_block(args, device, warmup, peaks, peak_kind, world, rank)
+    if args.workload == "decode":
+        if world != 1:
+            print("--workload decode runs on one GPU", file=sys.stderr)
+            return 2
+        return run_decode(args, device, warmup, peaks, peak_kind)
 
     main_buf = RmsBuffers(L, args.rows, HIDDEN, torch.bfloat16, device, SEED + rank, x_scale=2.0 ** 0.5)
     sampler = ClockSampler(local_rank) if rank == 0 else None
