@@ -20,6 +20,12 @@
  *     errors are detected on the host before anything is launched (the reference returns `false`
  *     after an fprintf, src/rmsnorm_kernel.cu:533-549).
  *   - tensors are row-major and dense: row r of an [rows, cols] tensor starts at element r*cols.
+ *   - threads: every entry point may be called from several host threads at once (on the same or on
+ *     different devices and streams). The only state the library keeps is per-device facts it looks up
+ *     once (SM count, occupancy, kernel attributes, symbol addresses), held in atomics, plus two
+ *     process-wide settings the caller owns: mgr_gemm_set_sm_limit and the shared scratch of
+ *     mgr_rmsnorm_bwd_noalloc (see there). The reference keeps no state either
+ *     (src/rmsnorm_kernel.cu has no globals).
  */
 #ifndef MGR_B200_H_
 #define MGR_B200_H_

@@ -1,20 +1,24 @@
 // Entry points of libmgr_b200.so that are not tied to one kernel family: version, status names,
 // device probe.
 
+#include <atomic>
+
 #include "mgr_common.cuh"
 
 namespace mgr {
 
 DeviceInfo current_device_info() {
+    // Filled once per device; `known` is published with release order after the entry is complete, so a thread
+    // that sees it set reads a whole entry. Two threads racing on the first call both write the same values.
     static DeviceInfo cache[kMaxDevices];
-    static bool known[kMaxDevices] = {false};
+    static std::atomic<bool> known[kMaxDevices];
     DeviceInfo di{MGR_ERR_CUDA, -1, 0};
     int dev = -1;
     if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= kMaxDevices) {
         (void)cudaGetLastError();
         return di;
     }
-    if (known[dev]) return cache[dev];
+    if (known[dev].load(std::memory_order_acquire)) return cache[dev];
     int major = 0, sms = 0;
     if (cudaDeviceGetAttribute(&major, cudaDevAttrComputeCapabilityMajor, dev) != cudaSuccess ||
         cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess) {
@@ -25,7 +29,7 @@ DeviceInfo current_device_info() {
     di.sm_count = sms;
     di.status = (major == 10) ? MGR_OK : MGR_ERR_UNSUPPORTED_ARCH;
     cache[dev] = di;
-    known[dev] = true;
+    known[dev].store(true, std::memory_order_release);
     return di;
 }
 

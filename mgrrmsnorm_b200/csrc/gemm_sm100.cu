@@ -559,8 +559,8 @@ using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t
 // cuTensorMapEncodeTiled through the runtime's driver entry-point lookup: the library does not link
 // libcuda, so it still loads (for its host-side checks) on a machine without a driver.
 EncodeTiledFn encode_tiled_fn() {
-    static EncodeTiledFn fn = nullptr;
-    if (fn == nullptr) {
+    static std::atomic<EncodeTiledFn> fn{nullptr};
+    if (fn.load(std::memory_order_relaxed) == nullptr) {
         void* p = nullptr;
         cudaDriverEntryPointQueryResult q;
         if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &p, cudaEnableDefault, &q) != cudaSuccess ||
@@ -568,9 +568,9 @@ EncodeTiledFn encode_tiled_fn() {
             (void)cudaGetLastError();
             return nullptr;
         }
-        fn = reinterpret_cast<EncodeTiledFn>(p);
+        fn.store(reinterpret_cast<EncodeTiledFn>(p), std::memory_order_relaxed);
     }
-    return fn;
+    return fn.load(std::memory_order_relaxed);
 }
 
 // Tensor map over a row-major [outer, inner] matrix of 16-bit elements with leading dimension ld
@@ -590,16 +590,16 @@ bool make_tmap(CUtensorMap* tm, const void* base, int64_t outer, int64_t inner, 
 }
 
 int* gemm_status_ptr(const DeviceInfo& di) {
-    static int* cache[kMaxDevices] = {nullptr};
-    if (cache[di.device] == nullptr) {
+    static std::atomic<int*> cache[kMaxDevices];   // racing first calls store the same address
+    if (cache[di.device].load(std::memory_order_relaxed) == nullptr) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, g_gemm_status) != cudaSuccess) {
             (void)cudaGetLastError();
             return nullptr;
         }
-        cache[di.device] = static_cast<int*>(p);
+        cache[di.device].store(static_cast<int*>(p), std::memory_order_relaxed);
     }
-    return cache[di.device];
+    return cache[di.device].load(std::memory_order_relaxed);
 }
 
 struct GemmArgs {
@@ -639,15 +639,15 @@ bool pdl_enabled() {
 
 template <int EPI, bool A_MN, bool B_MN, int CG, typename T, int BN = kBN>
 int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
-    static bool attr[kMaxDevices] = {false};
+    static std::atomic<bool> attr[kMaxDevices];
     constexpr uint32_t kGemmSmem = gemm_smem(CG, BN);
-    if (!attr[di.device]) {
+    if (!attr[di.device].load(std::memory_order_acquire)) {
         if (cudaFuncSetAttribute(gemm_kernel<EPI, A_MN, B_MN, CG, T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kGemmSmem)) != cudaSuccess) {
             (void)cudaGetLastError();
             return MGR_ERR_CUDA;
         }
-        attr[di.device] = true;
+        attr[di.device].store(true, std::memory_order_release);
     }
     CUtensorMap tmA, tmB;
     // A problem of fewer than 128 rows brings in only the rows it has (rounded up to 8): the rest of the

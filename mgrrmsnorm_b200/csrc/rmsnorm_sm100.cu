@@ -12,6 +12,7 @@
 // Shapes the packet path cannot take (cols not a multiple of the packet width, pointers not 16-byte
 // aligned, rows longer than 4096 packets) go to scalar kernels with the same arithmetic.
 
+#include <atomic>
 #include <cstdlib>
 #include <cstring>
 
@@ -474,15 +475,15 @@ int reg_shape_for(int64_t nvec) {
 }
 
 template <typename K>
-int resident_ctas(K kernel, int block, int* cache /* [kMaxDevices] */, int device) {
-    int v = cache[device];
+int resident_ctas(K kernel, int block, std::atomic<int>* cache /* [kMaxDevices] */, int device) {
+    int v = cache[device].load(std::memory_order_relaxed);
     if (v > 0) return v;
     int n = 0;
     if (cudaOccupancyMaxActiveBlocksPerMultiprocessor(&n, kernel, block, 0) != cudaSuccess || n < 1) {
         (void)cudaGetLastError();
         n = 1;
     }
-    cache[device] = n;
+    cache[device].store(n, std::memory_order_relaxed);   // idempotent: racing first calls store the same value
     return n;
 }
 
@@ -494,13 +495,13 @@ struct RegKernels {
     static constexpr int G = RegGeom<TPR>::kGroups;
 
     static int64_t fwd_grid(int64_t rows, const DeviceInfo& di) {
-        static int occ[kMaxDevices] = {0};
+        static std::atomic<int> occ[kMaxDevices];
         const int64_t ngroups = (rows + G - 1) / G;
         const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_fwd_reg<T, TPR, VPT, ADD>, BLOCK, occ, di.device);
         return ngroups < cap ? ngroups : cap;
     }
     static int64_t bwd_grid(int64_t rows, const DeviceInfo& di) {
-        static int occ[kMaxDevices] = {0};
+        static std::atomic<int> occ[kMaxDevices];
         const int64_t ngroups = (rows + G - 1) / G;
         const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_bwd_reg<T, TPR, VPT, ADD>, BLOCK, occ, di.device);
         return ngroups < cap ? ngroups : cap;
@@ -563,26 +564,26 @@ Path forced_path() {
 }
 
 int* rms_status_ptr(const DeviceInfo& di) {
-    static int* cache[kMaxDevices] = {nullptr};
-    if (cache[di.device] == nullptr) {
+    static std::atomic<int*> cache[kMaxDevices];
+    if (cache[di.device].load(std::memory_order_relaxed) == nullptr) {
         void* p = nullptr;
         if (cudaGetSymbolAddress(&p, g_rms_status) != cudaSuccess) {
             (void)cudaGetLastError();
             return nullptr;
         }
-        cache[di.device] = static_cast<int*>(p);
+        cache[di.device].store(static_cast<int*>(p), std::memory_order_relaxed);
     }
-    return cache[di.device];
+    return cache[di.device].load(std::memory_order_relaxed);
 }
 
 template <typename K>
-bool allow_big_smem(K kernel, bool* done /* [kMaxDevices] */, int device) {
-    if (done[device]) return true;
+bool allow_big_smem(K kernel, std::atomic<bool>* done /* [kMaxDevices] */, int device) {
+    if (done[device].load(std::memory_order_acquire)) return true;
     if (cudaFuncSetAttribute(kernel, cudaFuncAttributeMaxDynamicSharedMemorySize, static_cast<int>(kSmemBudget)) != cudaSuccess) {
         (void)cudaGetLastError();
         return false;
     }
-    done[device] = true;
+    done[device].store(true, std::memory_order_release);
     return true;
 }
 
@@ -590,7 +591,7 @@ bool allow_big_smem(K kernel, bool* done /* [kMaxDevices] */, int device) {
 template <typename T>
 int fwd_ring_try(T* y, float* inv, const T* x, const T* w, int64_t rows, int64_t cols, float eps, const DeviceInfo& di,
                  cudaStream_t s) {
-    static bool attr[kMaxDevices] = {false};
+    static std::atomic<bool> attr[kMaxDevices];
     const RingPlan plan = fwd_ring_plan(rows, cols, sizeof(T));
     if (!plan.ok) return 1;
     int* status = rms_status_ptr(di);
@@ -649,7 +650,7 @@ struct RingDispatch {
                    int64_t rows, int cols, int* status, const DeviceInfo& di, cudaStream_t s) {
         if (plan.shape == I) {
             constexpr int TPR = kRingShapes[I].tpr, VPT = kRingShapes[I].vpt;
-            static bool attr[kMaxDevices] = {false};
+            static std::atomic<bool> attr[kMaxDevices];
             if (!allow_big_smem(rms_bwd_ring<T, TPR, VPT>, attr, di.device)) return 1;
             rms_bwd_ring<T, TPR, VPT><<<static_cast<unsigned>(plan.grid), kBwdRingThreads, plan.smem_bytes, s>>>(
                 dx, ws, dy, x, w, inv, rows, cols, plan.nslots, plan.slot_bytes, status);

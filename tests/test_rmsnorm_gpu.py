@@ -420,3 +420,44 @@ def test_speed_against_reference_cuda_kernels(ops, built_lib, capsys):
     with capsys.disabled():
         print(f"\n[fp16 4096x4096 fwd+bwd, L2-cold] reference kernels {t_ref:.1f} us, this library {t_ours:.1f} us, ratio {t_ref / t_ours:.2f}x")
     assert t_ours <= t_ref * 1.05
+
+
+def test_concurrent_host_threads_and_streams(ops):
+    """Eight host threads call forward+backward at once, each on its own stream and tensors (different shapes,
+    so different kernels and first-use lookups race): every result equals the one computed alone."""
+    import threading
+
+    shapes = [(700, 4096, "bf16"), (300, 8192, "f16"), (1000, 1024, "f32"), (64, 5120, "bf16"),
+              (129, 1000, "f16"), (2000, 2048, "bf16"), (50, 16384, "f32"), (900, 4096, "f16")]
+    inputs = []
+    for i, (rows, cols, dtype) in enumerate(shapes):
+        x, w, dy = seeded_rmsnorm_inputs(rows, cols, dtype, seed=100 + i)
+        inputs.append((x.cuda(), w.cuda(), dy.cuda()))
+    torch.cuda.synchronize()
+    results = [None] * len(shapes)
+    errors = []
+
+    def work(i):
+        try:
+            x, w, dy = inputs[i]
+            s = torch.cuda.Stream()
+            with torch.cuda.stream(s):
+                for _ in range(5):
+                    y, inv = ops.rmsnorm_forward(x, w, 1e-6)
+                    dx, dw = ops.rmsnorm_backward(dy, x, w, inv)
+            s.synchronize()
+            results[i] = (y, dx, dw)
+        except Exception as e:  # surfaced below: an exception in a thread would otherwise pass silently
+            errors.append((i, repr(e)))
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(len(shapes))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not errors, errors
+    for i, (x, w, dy) in enumerate(inputs):
+        y, inv = ops.rmsnorm_forward(x, w, 1e-6)
+        dx, dw = ops.rmsnorm_backward(dy, x, w, inv)
+        torch.cuda.synchronize()
+        assert torch.equal(results[i][0], y) and torch.equal(results[i][1], dx) and torch.equal(results[i][2], dw), shapes[i]
