@@ -121,8 +121,41 @@ def swiglu_cases():
     np.savez_compressed(HERE / "swiglu.npz", **out)
 
 
+def add_rmsnorm_cases():
+    """The residual add in front of the norm, written the way a user of the reference writes it:
+    h = x + residual (torch), y = rmsnorm(h) -- forward by the reference's rmsnorm_cpu, forward and
+    backward by the formula its test differentiates, in fp64 -- with a gradient arriving through h as
+    well as through y (dh_total = d_norm/dh + dres). Inputs are rounded to the case's dtype and h is
+    rounded again after the add, as torch's add of two half-precision tensors does."""
+    ref = oracle.ref_lib()
+    assert ref is not None, "build oracle/_ref first: make -C oracle ref"
+    g = torch.Generator().manual_seed(2468)
+    out = {}
+    for name, rows, cols, eps, dt in [("f32", 5, 264, 1e-6, torch.float32), ("f16", 4, 256, 1e-6, torch.float16),
+                                      ("bf16", 5, 512, 1e-5, torch.bfloat16)]:
+        x = torch.randn(rows, cols, generator=g).to(dt)
+        res = torch.randn(rows, cols, generator=g).to(dt)
+        w = (1.0 + 0.1 * torch.randn(cols, generator=g)).to(dt)
+        dy = torch.randn(rows, cols, generator=g).to(dt)
+        dres = torch.randn(rows, cols, generator=g).to(dt)
+        h = (x + res)                                   # torch's add in the case's dtype: the reference user's first line
+        y_ref_cpu = ref.cpu_forward(h.float().numpy(), w.float().numpy(), eps)
+        h64 = h.double().requires_grad_(True)
+        w64 = w.double().requires_grad_(True)
+        y64 = h64 * torch.rsqrt(h64.pow(2).mean(-1, keepdim=True) + float(np.float32(eps))) * w64
+        (y64 * dy.double()).sum().backward()
+        out.update({
+            f"{name}_x": x.float().numpy(), f"{name}_res": res.float().numpy(), f"{name}_w": w.float().numpy(),
+            f"{name}_dy": dy.float().numpy(), f"{name}_dres": dres.float().numpy(), f"{name}_eps": np.float32(eps),
+            f"{name}_h": h.float().numpy(), f"{name}_y_refcpu": y_ref_cpu, f"{name}_y": y64.detach().numpy(),
+            f"{name}_dh": (h64.grad + dres.double()).numpy(), f"{name}_dw": w64.grad.numpy(),
+        })
+    np.savez_compressed(HERE / "add_rmsnorm.npz", **out)
+
+
 if __name__ == "__main__":
     rmsnorm_cases()
     swiglu_cases()
+    add_rmsnorm_cases()
     for p in sorted(HERE.glob("*.npz")):
         print(p.name, p.stat().st_size, "bytes")

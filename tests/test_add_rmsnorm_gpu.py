@@ -63,6 +63,24 @@ def test_matches_two_step_sequence_and_oracle(ops, rows, cols, dtype):
         assert torch.equal(dw32, dw32_plain) and torch.equal(dw, dw_plain)
 
 
+@pytest.mark.parametrize("case", ["f32", "f16", "bf16"])
+def test_golden_vectors(ops, golden_dir, case):
+    """Against tests/golden/add_rmsnorm.npz: torch add + the reference's CPU forward and differentiated formula."""
+    z = np.load(golden_dir / "add_rmsnorm.npz")
+    td = TORCH_DTYPES[case]
+    x, res, w, dy, dres = (torch.from_numpy(z[f"{case}_{k}"]).to(td).cuda() for k in ("x", "res", "w", "dy", "dres"))
+    eps = float(z[f"{case}_eps"])
+    y, h, inv = ops.add_rmsnorm_forward(x, res, w, eps)
+    assert np.array_equal(to_np(h), z[f"{case}_h"])
+    assert_matches_truth(y, z[f"{case}_y"], case, "y")
+    if case == "f32":   # the reference's own fp32 CPU forward: within its 1e-4 check (rmsnorm_standalone.cu:75-86)
+        assert float(np.abs(to_np(y) - z["f32_y_refcpu"]).max()) < 1e-4
+    dh, dw, dw32 = ops.add_rmsnorm_backward(dy, dres, h, w, inv, want_dw_f32=True)
+    assert_matches_truth(dh, z[f"{case}_dh"], case, "dh")
+    assert_matches_truth(dw32, z[f"{case}_dw"], "f32", "dw_f32", slack=4.0)
+    assert_matches_truth(dw, z[f"{case}_dw"], case, "dw", slack=4.0)
+
+
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 def test_in_place_residual_stream(ops, dtype):
     x, res, w, dy, dres = seeded(700, 4096, dtype, seed=5)

@@ -87,3 +87,22 @@ def test_round_to_matches_torch():
     assert np.array_equal(oracle.round_to(a, "f16"), t.to(torch.float16).float().numpy())
     assert oracle.ulp_of(np.array([1.0]), "bf16")[0] == 2.0 ** -7
     assert oracle.ulp_of(np.array([5.0]), "f16")[0] == 2.0 ** -8
+
+
+@pytest.mark.parametrize("case", ["f32", "f16", "bf16"])
+def test_add_rmsnorm_composition_matches_reference_sequence(golden_dir, case):
+    """Residual add + norm as a user of the reference writes it (torch add, then the reference's CPU forward /
+    the formula its test differentiates): the oracle's restatement of that sequence -- round(x + residual)
+    in the case's dtype, then the pinned norm oracle; backward = norm backward + the residual-stream
+    gradient -- reproduces the fixture."""
+    z = np.load(golden_dir / "add_rmsnorm.npz")
+    x, res, w, dy, dres = (z[f"{case}_{k}"] for k in ("x", "res", "w", "dy", "dres"))
+    eps = float(z[f"{case}_eps"])
+    h = oracle.round_to(x + res, case)
+    assert np.array_equal(h, z[f"{case}_h"])
+    assert np.array_equal(oracle.rmsnorm_fwd_f32seq(h, w, eps), z[f"{case}_y_refcpu"])
+    y, _ = oracle.rmsnorm_fwd(h, w, eps)
+    dx, dw = oracle.rmsnorm_bwd(dy, h, w, eps)
+    np.testing.assert_allclose(y, z[f"{case}_y"], rtol=1e-12, atol=1e-13)
+    np.testing.assert_allclose(dx + dres.astype(np.float64), z[f"{case}_dh"], rtol=1e-10, atol=1e-12)
+    np.testing.assert_allclose(dw, z[f"{case}_dw"], rtol=1e-10, atol=1e-12)
