@@ -212,7 +212,7 @@ def reference_arm(args) -> int:
 def workload_config(n_gpus: int, rows: int = ROWS_PER_GPU) -> dict:
     return {"workload": f"RMSNorm bf16 forward+backward, {rows} rows x hidden {HIDDEN} per GPU, eps 1e-6 "
                         "(x~N(0,2), w=1+0.1N(0,1), dy~N(0,1))" + ("" if rows == ROWS_PER_GPU else " [REDUCED CASE, not the benchmark]"),
-            "rows_per_gpu": rows, "hidden": HIDDEN, "sharding": f"rows x{n_gpus}, fp32 dW all-reduce" if n_gpus > 1 else "none",
+            "rows_per_gpu": rows, "hidden": HIDDEN, "sharding": f"rows x{n_gpus}, fp32 dW all-reduce every step (on a side stream, beside the next step's forward)" if n_gpus > 1 else "none",
             "l2": "inputs larger than L2 (1 GiB per tensor, 126 MB L2)", "seed": SEED}
 
 
@@ -266,6 +266,12 @@ def time_device_resident(bufsets, steps, warmup, world, sampler=None):
 
     stream = torch.cuda.current_stream()
     sp = stream.cuda_stream
+    # N > 1: the all-reduce of the fp32 dW partial (32 KB, latency-bound) and the one rounding after it run on a
+    # side stream, beside the NEXT step's forward, as in a training loop where dW is not needed before the
+    # optimizer step. The next backward that overwrites the same dW buffer waits for it, and so does the end of
+    # the timed region, so every step's collective completes inside the region it is timed in.
+    side = torch.cuda.Stream() if world > 1 else None
+    reduced = {id(b): None for b in bufsets}
 
     def step(b, evs=None):
         if evs:
@@ -273,15 +279,27 @@ def time_device_resident(bufsets, steps, warmup, world, sampler=None):
         b.fwd(sp)
         if evs:
             evs[1].record(stream)
+        if world > 1 and reduced[id(b)] is not None:
+            stream.wait_event(reduced[id(b)])        # the previous all-reduce has finished with b.dw32
         b.bwd(sp)
         if evs:
             evs[2].record(stream)
         if world > 1:
-            dist.all_reduce(b.dw32)
-            b.dw.copy_(b.dw32)
+            side.wait_stream(stream)
+            with torch.cuda.stream(side):
+                dist.all_reduce(b.dw32)
+                b.dw.copy_(b.dw32)
+                ev = torch.cuda.Event()
+                ev.record(side)
+            reduced[id(b)] = ev
+
+    def drain():
+        if world > 1:
+            stream.wait_stream(side)
 
     for i in range(warmup):
         step(bufsets[i % len(bufsets)])
+    drain()
     evs = [[torch.cuda.Event(enable_timing=True) for _ in range(3)] for _ in range(steps)]
     e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
     if world > 1:
@@ -291,6 +309,7 @@ def time_device_resident(bufsets, steps, warmup, world, sampler=None):
     e0.record(stream)
     for i in range(steps):
         step(bufsets[i % len(bufsets)], evs[i])
+    drain()
     e1.record(stream)
     torch.cuda.synchronize()
     t1 = time.perf_counter()
