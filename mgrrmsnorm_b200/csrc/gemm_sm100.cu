@@ -56,6 +56,11 @@ constexpr uint32_t kNarrowRing = 216 * 1024;
 __host__ __device__ constexpr uint32_t gemm_smem(int cg, int bn) {
     return (bn < kBN ? kNarrowRing : num_stages(cg, bn) * stage_bytes(cg, bn)) + 1024;
 }
+// The dh -> [d_gate | d_val] epilogue moves its global traffic (the stored projection in, the gradients out)
+// in a coalesced layout and converts to and from the accumulator's row-per-thread layout through a small
+// per-warp staging buffer behind the ring: 32 rows x 64 B, rows padded to 80 B against bank conflicts.
+constexpr uint32_t kEpiRowPitch = 80;
+constexpr uint32_t kEpiStageBytes = 32 * kEpiRowPitch;
 constexpr int kMaxStages = 8;
 // Narrow-tile kernels: a sub-stage is the A box actually loaded (8..128 rows) plus the 8 KB B tile of one
 // 64-element K block; a STAGE (one full/empty barrier pair) is `ksub` consecutive sub-stages, i.e. ksub K blocks
@@ -83,6 +88,13 @@ __host__ __device__ inline NarrowGeom narrow_geom(uint32_t a_box_bytes, int bn) 
 }
 
 constexpr int kEpiWarps = 8;      // epilogue warps: two per 32-lane quarter of tensor memory
+// ring depth and dynamic shared memory of a kernel instance (a CTA pair gives up one stage to the staging buffers)
+__host__ __device__ constexpr int num_stages_epi(int epi, int cg, int bn) {
+    return (epi == 4 && cg == 2) ? 6 : num_stages(cg, bn);
+}
+__host__ __device__ constexpr uint32_t gemm_smem_epi(int epi, int cg, int bn) {
+    return epi == 4 ? num_stages_epi(epi, cg, bn) * stage_bytes(cg, bn) + 1024 + kEpiWarps * kEpiStageBytes : gemm_smem(cg, bn);
+}
 constexpr int kGemmThreads = (2 + kEpiWarps) * 32;
 constexpr uint32_t kTmemCols = 512;
 
@@ -180,8 +192,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
     constexpr uint32_t kBBytes = b_bytes(BN);
     constexpr bool kNarrow = BN < kBN;
     // wide tiles: compile-time ring of one K block per stage; narrow tiles: see narrow_geom()
-    const NarrowGeom ng = kNarrow ? narrow_geom(a_box_bytes, BN) : NarrowGeom{1, num_stages(CG, BN), stage_bytes(CG, BN)};
-    const int kStages = kNarrow ? ng.stages : num_stages(CG, BN);
+    const NarrowGeom ng = kNarrow ? narrow_geom(a_box_bytes, BN) : NarrowGeom{1, num_stages_epi(EPI, CG, BN), stage_bytes(CG, BN)};
+    const int kStages = kNarrow ? ng.stages : num_stages_epi(EPI, CG, BN);
     const int kSub = kNarrow ? ng.ksub : 1;                                           // K blocks per stage
     const uint32_t kSubBytes = kNarrow ? ng.sub_bytes : stage_bytes(CG, BN);          // bytes of one K block
     const uint32_t kStageBytes = kNarrow ? ng.sub_bytes * ng.ksub : stage_bytes(CG, BN);
@@ -428,37 +440,48 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         }
                     }
                 } else if constexpr (EPI == kEpiDhDgv) {
-                    // The stored gate / value packets of the NEXT chunk are requested before this chunk is
-                    // worked on, so their latency (L2 or HBM) overlaps the arithmetic instead of heading it.
+                    // Global traffic in a coalesced layout: instruction i of four covers rows 8i..8i+7 of this warp's
+                    // 32, four lanes x 16 B = the chunk's 64 contiguous bytes of a row (whole sectors; a quarter of
+                    // the cache lines per instruction that one-row-per-lane accesses touch). The accumulator is
+                    // row-per-lane, so packets change layout through the warp's staging buffer.
+                    // The stored gate / value packets of the NEXT chunk are requested while this chunk is worked
+                    // on, so their latency (L2 or HBM) overlaps the arithmetic instead of heading it.
                     constexpr int kStride = kEpiWarps / 4;
+                    const int cr = lane >> 2, cp = lane & 3;
+                    const int row0 = tc.m0 + static_cast<int>(cta_rank) * kBM + q * 32;
+                    const uint32_t sbuf = ring + static_cast<uint32_t>(kStages) * kStageBytes + static_cast<uint32_t>(warp - 2) * kEpiStageBytes;
+                    const uint32_t s_co = sbuf + static_cast<uint32_t>(cr) * kEpiRowPitch + static_cast<uint32_t>(cp) * 16u;   // + i * 8 rows
+                    const uint32_t s_row = sbuf + static_cast<uint32_t>(lane) * kEpiRowPitch;                                    // + j * 16
                     uint32_t a[32];
                     ptx::tmem_ld_32x32(t_row + c * 32, a);
-                    if (c == chunk0) {
-                        const T* grow = aux + static_cast<int64_t>(row) * ld_aux + tc.n0 + c * 32;
+                    auto fetch = [&](int cc) {
+                        const int col = tc.n0 + cc * 32 + cp * 8;
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const bool on = row < M && tc.n0 + c * 32 + j * 8 < n_out;
-                            gp_next[j] = on ? ld_stream16(reinterpret_cast<const uint4*>(grow + j * 8)) : make_uint4(0, 0, 0, 0);
-                            vp_next[j] = on ? ld_stream16(reinterpret_cast<const uint4*>(grow + n_out + j * 8)) : make_uint4(0, 0, 0, 0);
+                        for (int i = 0; i < 4; ++i) {
+                            const int rr = row0 + i * 8 + cr;
+                            const bool on = rr < M && col < n_out;
+                            const T* gptr = aux + static_cast<int64_t>(rr) * ld_aux + col;
+                            gp_next[i] = on ? ld_stream16(reinterpret_cast<const uint4*>(gptr)) : make_uint4(0, 0, 0, 0);
+                            vp_next[i] = on ? ld_stream16(reinterpret_cast<const uint4*>(gptr + n_out)) : make_uint4(0, 0, 0, 0);
                         }
-                    }
+                    };
+                    if (c == chunk0) fetch(c);
                     uint4 gp[4], vp[4];
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) {
-                        gp[j] = gp_next[j];
-                        vp[j] = vp_next[j];
-                    }
-                    if (c + kStride < kNStep / 32) {
-                        const int cn = c + kStride;
-                        const T* grow = aux + static_cast<int64_t>(row) * ld_aux + tc.n0 + cn * 32;
+                    for (int i = 0; i < 4; ++i) ptx::sts128(s_co + static_cast<uint32_t>(i) * 8u * kEpiRowPitch, gp_next[i]);
+                    __syncwarp();
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) {
-                            const bool on = row < M && tc.n0 + cn * 32 + j * 8 < n_out;
-                            gp_next[j] = on ? ld_stream16(reinterpret_cast<const uint4*>(grow + j * 8)) : make_uint4(0, 0, 0, 0);
-                            vp_next[j] = on ? ld_stream16(reinterpret_cast<const uint4*>(grow + n_out + j * 8)) : make_uint4(0, 0, 0, 0);
-                        }
-                    }
+                    for (int j = 0; j < 4; ++j) gp[j] = ptx::lds128(s_row + 16u * j);
+                    __syncwarp();
+#pragma unroll
+                    for (int i = 0; i < 4; ++i) ptx::sts128(s_co + static_cast<uint32_t>(i) * 8u * kEpiRowPitch, vp_next[i]);
+                    __syncwarp();
+#pragma unroll
+                    for (int j = 0; j < 4; ++j) vp[j] = ptx::lds128(s_row + 16u * j);
+                    __syncwarp();
+                    if (c + kStride < kNStep / 32) fetch(c + kStride);
                     ptx::tmem_ld_wait();
+                    uint4 og[4], ov[4];
 #pragma unroll
                     for (int j = 0; j < 4; ++j) {
                         float gg[8], vv[8], dg[8], dv[8];
@@ -471,11 +494,24 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                             dv[e] = dh * (gg[e] * sig);
                             dg[e] = dh * vv[e] * (sig * (1.0f + gg[e] * (1.0f - sig)));
                         }
-                        if (row < M && tc.n0 + c * 32 + j * 8 < n_out) {
-                            // read once / written once: streaming accesses keep the GEMM operands in L2
-                            st_stream16(reinterpret_cast<uint4*>(crow + c * 32 + j * 8), pack16<T>(dg));
-                            st_stream16(reinterpret_cast<uint4*>(crow + n_out + c * 32 + j * 8), pack16<T>(dv));
+                        og[j] = pack16<T>(dg);
+                        ov[j] = pack16<T>(dv);
+                    }
+                    // read once / written once: streaming stores keep the GEMM operands in L2
+                    const int ocol = tc.n0 + c * 32 + cp * 8;
+#pragma unroll
+                    for (int half = 0; half < 2; ++half) {
+#pragma unroll
+                        for (int j = 0; j < 4; ++j) ptx::sts128(s_row + 16u * j, half == 0 ? og[j] : ov[j]);
+                        __syncwarp();
+#pragma unroll
+                        for (int i = 0; i < 4; ++i) {
+                            const int rr = row0 + i * 8 + cr;
+                            const uint4 v = ptx::lds128(s_co + static_cast<uint32_t>(i) * 8u * kEpiRowPitch);
+                            if (rr < M && ocol < n_out)
+                                st_stream16(reinterpret_cast<uint4*>(C + static_cast<int64_t>(rr) * ldc + ocol + (half == 0 ? 0 : n_out)), v);
                         }
+                        __syncwarp();
                     }
                 } else {
                     uint32_t out[16];
@@ -640,7 +676,7 @@ bool pdl_enabled() {
 template <int EPI, bool A_MN, bool B_MN, int CG, typename T, int BN = kBN>
 int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     static std::atomic<bool> attr[kMaxDevices];
-    constexpr uint32_t kGemmSmem = gemm_smem(CG, BN);
+    constexpr uint32_t kGemmSmem = gemm_smem_epi(EPI, CG, BN);
     if (!attr[di.device].load(std::memory_order_acquire)) {
         if (cudaFuncSetAttribute(gemm_kernel<EPI, A_MN, B_MN, CG, T, BN>, cudaFuncAttributeMaxDynamicSharedMemorySize,
                                  static_cast<int>(kGemmSmem)) != cudaSuccess) {
