@@ -243,3 +243,17 @@ def test_sequence_parallel_mlp_on_two_gloo_ranks():
         assert p.exitcode == 0
     assert sorted(r[0] for r in results) == [0, 1]
     assert all(r[1] for r in results), results
+
+
+def test_sequence_parallel_module_checks_its_input():
+    """Shape and dtype errors are raised before any collective or kernel is reached (no process group here)."""
+    sp = sharding.SequenceParallelSwiGLU(64, 128, world=2, rank=1)
+    assert tuple(sp.local.w12.weight.shape) == (128, 64) and tuple(sp.local.w3.weight.shape) == (64, 64)
+    with pytest.raises(RuntimeError, match="multiples of 8"):
+        sp(torch.zeros(12, 64))            # 12 rows: not a multiple of 8
+    with pytest.raises(RuntimeError, match="multiples of 8"):
+        sp(torch.zeros(0, 64))
+    with pytest.raises(RuntimeError, match="share one dtype"):
+        sp(torch.zeros(16, 64, dtype=torch.float16))
+    with pytest.raises(ValueError):
+        sharding.SequenceParallelSwiGLU(64, 100, world=3, rank=0)   # hidden not divisible by the group size
