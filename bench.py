@@ -270,8 +270,12 @@ def time_device_resident(bufsets, steps, warmup, world, sampler=None):
     # side stream, beside the NEXT step's forward, as in a training loop where dW is not needed before the
     # optimizer step. The next backward that overwrites the same dW buffer waits for it, and so does the end of
     # the timed region, so every step's collective completes inside the region it is timed in.
-    side = torch.cuda.Stream() if world > 1 else None
-    reduced = {id(b): None for b in bufsets}
+    # (mgrrmsnorm_b200.sharding.AsyncDwReduce is the library's helper for exactly this.)
+    red = None
+    if world > 1:
+        from mgrrmsnorm_b200.sharding import AsyncDwReduce
+
+        red = AsyncDwReduce(torch.cuda.current_device())
 
     def step(b, evs=None):
         if evs:
@@ -279,23 +283,17 @@ def time_device_resident(bufsets, steps, warmup, world, sampler=None):
         b.fwd(sp)
         if evs:
             evs[1].record(stream)
-        if world > 1 and reduced[id(b)] is not None:
-            stream.wait_event(reduced[id(b)])        # the previous all-reduce has finished with b.dw32
+        if red is not None:
+            red.wait_for(b.dw32)                     # the previous all-reduce has finished with b.dw32
         b.bwd(sp)
         if evs:
             evs[2].record(stream)
-        if world > 1:
-            side.wait_stream(stream)
-            with torch.cuda.stream(side):
-                dist.all_reduce(b.dw32)
-                b.dw.copy_(b.dw32)
-                ev = torch.cuda.Event()
-                ev.record(side)
-            reduced[id(b)] = ev
+        if red is not None:
+            red.start(b.dw32, b.dw)
 
     def drain():
-        if world > 1:
-            stream.wait_stream(side)
+        if red is not None:
+            red.drain()
 
     for i in range(warmup):
         step(bufsets[i % len(bufsets)])

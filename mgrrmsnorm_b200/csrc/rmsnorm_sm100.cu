@@ -443,7 +443,7 @@ struct RegShape {
 };
 // The last three are alternatives to {128,4}, {256,4} and {128,2} with one row per CTA pass; only the backward
 // picks them (bwd_shape_for), the size-ordered search of reg_shape_for never reaches them.
-constexpr RegShape kRegShapes[] = {{32, 1}, {32, 2}, {32, 4}, {128, 2}, {128, 4}, {256, 4}, {512, 4}, {1024, 4}, {256, 2}, {512, 2}, {256, 1}};
+constexpr RegShape kRegShapes[] = {{32, 1}, {32, 2}, {32, 4}, {128, 2}, {128, 4}, {256, 4}, {512, 4}, {1024, 4}, {256, 2}, {512, 2}, {256, 1}, {128, 1}};
 constexpr int kNumRegShapes = sizeof(kRegShapes) / sizeof(kRegShapes[0]);
 constexpr int kScalarDwSlices = 64;
 
@@ -451,6 +451,18 @@ constexpr int kScalarDwSlices = 64;
 // MGR_RMSNORM_BWD_SHAPE=<index into kRegShapes> pins the backward's packet shape when it can hold the row
 // (measurement aid); otherwise the default search.
 int reg_shape_for(int64_t nvec);
+// Forward: the size-ordered search, unless MGR_RMSNORM_FWD_SHAPE=<index into kRegShapes> pins a shape that can
+// hold the row (measurement aid).
+int fwd_shape_for(int64_t nvec) {
+    const char* e = std::getenv("MGR_RMSNORM_FWD_SHAPE");
+    if (e != nullptr) {
+        const int i = std::atoi(e);
+        if (i >= 0 && i < static_cast<int>(sizeof(kRegShapes) / sizeof(kRegShapes[0])) &&
+            nvec <= static_cast<int64_t>(kRegShapes[i].tpr) * kRegShapes[i].vpt)
+            return i;
+    }
+    return reg_shape_for(nvec);
+}
 int bwd_shape_for(int64_t nvec) {
     const char* e = std::getenv("MGR_RMSNORM_BWD_SHAPE");
     if (e != nullptr) {
@@ -689,7 +701,7 @@ int fwd_typed(void* y, float* inv, const void* x, const void* w, int64_t rows, i
         const int st = fwd_ring_try<T>(static_cast<T*>(y), inv, static_cast<const T*>(x), static_cast<const T*>(w), rows, cols, eps, di, s);
         if (st <= 0) return st;
     }
-    const int shape = packets ? reg_shape_for(cols / VEC) : -1;
+    const int shape = packets ? fwd_shape_for(cols / VEC) : -1;
     if (shape >= 0) {
         RegDispatch<T>::fwd(shape, static_cast<T*>(y), inv, static_cast<const T*>(x), static_cast<const T*>(w), rows,
                             static_cast<int>(cols), eps, di, s, static_cast<const T*>(res), static_cast<T*>(h_out));

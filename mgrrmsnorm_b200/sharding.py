@@ -113,6 +113,47 @@ def allreduce_dw(dw_f32: torch.Tensor, out_dtype: torch.dtype, group=None) -> to
     return dw_f32.to(out_dtype)
 
 
+class AsyncDwReduce:
+    """The cross-rank sum of the fp32 dW partials, taken OFF the compute stream.
+
+    The all-reduce of a [H] fp32 vector is latency-bound (tens of microseconds for 32 KB) and nothing needs its
+    result before the optimizer step, so it runs on a side stream beside whatever the compute stream does next
+    (the next micro-batch's forward, the rest of the backward pass):
+
+        red = AsyncDwReduce(device, group)
+        ...backward kernel writes dw_f32 on the current stream...
+        red.start(dw_f32, dw_out)       # all-reduce + the one rounding into dw_out (weight dtype), side stream
+        ...more work on the current stream...
+        red.wait_for(dw_f32)            # before dw_f32 is overwritten again
+        red.drain()                     # before dw_out is read (optimizer step / end of a timed region)
+    """
+
+    def __init__(self, device=None, group=None):
+        self.side = torch.cuda.Stream(device)
+        self.group = group
+        self.pending: dict[int, torch.cuda.Event] = {}
+
+    def start(self, dw_f32: torch.Tensor, dw_out: torch.Tensor) -> None:
+        if dw_f32.dtype != torch.float32:
+            raise TypeError("the cross-rank sum of dW is taken in fp32")
+        self.side.wait_stream(torch.cuda.current_stream(dw_f32.device))   # the partial has been produced
+        with torch.cuda.stream(self.side):
+            dist.all_reduce(dw_f32, op=dist.ReduceOp.SUM, group=self.group)
+            dw_out.copy_(dw_f32)                                          # the single rounding
+            ev = torch.cuda.Event()
+            ev.record(self.side)
+        self.pending[dw_f32.data_ptr()] = ev
+
+    def wait_for(self, dw_f32: torch.Tensor) -> None:
+        ev = self.pending.pop(dw_f32.data_ptr(), None)
+        if ev is not None:
+            torch.cuda.current_stream(dw_f32.device).wait_event(ev)
+
+    def drain(self) -> None:
+        torch.cuda.current_stream(self.side.device).wait_stream(self.side)
+        self.pending.clear()
+
+
 # ---------------------------------------------------------------------------------------------------
 # row-sharded RMSNorm
 # ---------------------------------------------------------------------------------------------------

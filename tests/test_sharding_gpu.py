@@ -57,6 +57,23 @@ def _worker(rank: int, world: int, port: int, q):
             ok_dw = (f"dw differs: column {worst}: {float(dws[worst])!r} vs {float(dwf[worst])!r}; "
                      f"{float((dws != dwf).float().mean()):.4f} of the columns differ")
 
+        # the same sum taken off the compute stream (AsyncDwReduce): identical bits to the synchronous path
+        import rmsnorm_cuda_ops as ops
+
+        _, inv_s = ops.rmsnorm_forward(xs.detach(), shard.weight.detach(), 1e-6)
+        red = sharding.AsyncDwReduce(dev)
+        outs_async = []
+        for _ in range(3):                                  # the partial buffer is reused: wait_for orders the reuse
+            _, _, dw32 = ops.rmsnorm_backward_full(dy[r0:r1].to(dev), xs.detach(), shard.weight.detach(), inv_s, want_dw_f32=True)
+            dw_out = torch.empty_like(shard.weight)
+            red.start(dw32, dw_out)
+            red.wait_for(dw32)
+            outs_async.append(dw_out)
+        red.drain()
+        torch.cuda.synchronize()
+        if ok_dw is True and not all(torch.equal(o, shard.weight.grad) for o in outs_async):
+            ok_dw = "AsyncDwReduce result differs from the synchronous all-reduce"
+
         # ---- tensor-parallel MLP: d_model 512, hidden 1024 split over 2 ranks, fp16
         torch.manual_seed(7)
         mlp = MegaGemmTriton(512, multiple_of=256, hidden_multiple=2.0).to(dev).half()
