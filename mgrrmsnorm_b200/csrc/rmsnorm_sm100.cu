@@ -443,7 +443,7 @@ struct RegShape {
 };
 // The last three are alternatives to {128,4}, {256,4} and {128,2} with one row per CTA pass; only the backward
 // picks them (bwd_shape_for), the size-ordered search of reg_shape_for never reaches them.
-constexpr RegShape kRegShapes[] = {{32, 1}, {32, 2}, {32, 4}, {128, 2}, {128, 4}, {256, 4}, {512, 4}, {1024, 4}, {256, 2}, {512, 2}, {256, 1}, {128, 1}};
+constexpr RegShape kRegShapes[] = {{32, 1}, {32, 2}, {32, 4}, {128, 2}, {128, 4}, {256, 4}, {512, 4}, {1024, 4}, {256, 2}, {512, 2}, {256, 1}};
 constexpr int kNumRegShapes = sizeof(kRegShapes) / sizeof(kRegShapes[0]);
 constexpr int kScalarDwSlices = 64;
 
