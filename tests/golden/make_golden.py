@@ -1,6 +1,6 @@
 """Generates the golden vectors under tests/golden/ by running the REFERENCE's own code on CPU.
 
-Needs the reference tree (default /root/reference, override with MGR_REFERENCE_DIR) and
+Needs the reference tree (its location comes from MGR_REFERENCE_DIR; see REF below for the default) and
 oracle/_ref/libmgr_ref.so (make -C oracle ref). The committed .npz files are its output; the tests
 only read them, so they run where the reference tree does not exist.
 
