@@ -766,7 +766,9 @@ int launch_gemm_cg(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
         const char* e = std::getenv("MGR_GEMM_NARROW");
         int bn = 0;
         if (e != nullptr) bn = e[0] == '0' ? 0 : (e[0] == '3' ? kBNTiny : kBNSmall);
-        else if (wide_tiles * 2 <= di.sm_count) bn = small_tiles * 2 <= di.sm_count ? kBNTiny : kBNSmall;
+        // Up to 384 rows only: from 4 row tiles on, every narrow tile re-reads its 128 rows of A and the wide
+        // tiling wins again (w3 GEMM at 512 rows: 37.9 us wide against 42.3 us narrow; at 256 rows 36.6 against 21.8).
+        else if (wide_tiles * 2 <= di.sm_count && m_tiles <= 3) bn = small_tiles * 2 <= di.sm_count ? kBNTiny : kBNSmall;
         if (bn == kBNTiny) return launch_gemm<EPI, A_MN, B_MN, 1, T, kBNTiny>(g, di, s);
         if (bn == kBNSmall) return launch_gemm<EPI, A_MN, B_MN, 1, T, kBNSmall>(g, di, s);
     }
