@@ -969,7 +969,7 @@ def main(argv=None) -> int:
             "e2e": None if e2e is None else {
                 "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
                 "ms_per_step": e2e["ms_per_step"], "steps": e2e["steps"],
-                "path": "pinned host x, dy -> HostRMSNormPipeline (8192-row chunks, copy-in / compute / copy-out streams) -> pinned host y, dx, dW",
+                "path": "pinned host x, dy -> HostRMSNormPipeline (32 MiB row chunks, copy-in / compute / copy-out streams) -> pinned host y, dx, dW",
                 "unpipelined_value": e2e["unpipelined_value"],
                 "unpipelined_path": "pinned host -> whole-tensor copies around the RMSNorm module fwd+bwd -> pinned host"},
             "gpu_launches": 3 * args.steps,
