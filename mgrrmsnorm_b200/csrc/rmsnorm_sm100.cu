@@ -678,7 +678,7 @@ struct RingDispatch {
 
 // Automatic choice between the register and the ring family, from back-to-back timings on B200
 // (fraction of the measured 6.55 TB/s copy bandwidth, register / ring):
-//   forward : 2-4 KB rows 0.83 / 1.00; 8 KB 0.97 / 0.95; 16 KB 0.99 / 0.92; 32 KB 0.97 / 0.89
+//   forward : 4 KB rows 0.85 / 1.00 (2 KB rows: see prefer_ring_fwd); 8 KB 0.97 / 0.95; 16 KB 0.99 / 0.92; 32 KB 0.97 / 0.89
 //   backward: 2 KB rows 0.90 / 0.80; 4 KB 0.93 / 0.84; 8 KB 0.92 / 0.83; 16 KB 0.92 / 0.82; 32 KB 0.84-0.87 / 0.90-0.94
 //   (register figures with the per-size packet shapes of bwd_shape_for)
 // The ring needs enough rows to fill its pipeline, hence the row-count floor.
