@@ -32,7 +32,8 @@ __device__ int g_rms_status = 0;
 
 template <int TPR>
 struct RegGeom {
-    static constexpr int kBlock = TPR < 256 ? 256 : TPR;
+    // 256 threads shared by several rows when TPR divides 256, else one row per CTA pass
+    static constexpr int kBlock = TPR >= 256 ? TPR : (256 % TPR == 0 ? 256 : TPR);
     static constexpr int kGroups = kBlock / TPR;
     static constexpr int kWarpsPerRow = TPR / 32;
     static constexpr int kWarps = kBlock / 32;
@@ -152,7 +153,7 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
 // ADD: dx = round_T(dx_norm + dres), the gradient that arrives along the residual stream folded into the
 // same store (one rounding). dx may be the buffer of dres.
 template <typename T, int TPR, int VPT, bool ADD = false>
-__global__ void __launch_bounds__(RegGeom<TPR>::kBlock, (VPT <= 2 && TPR >= 256) ? (VPT == 1 ? 1536 : 1024) / RegGeom<TPR>::kBlock : RegGeom<TPR>::kBwdMinBlocks)
+__global__ void __launch_bounds__(RegGeom<TPR>::kBlock, (VPT <= 2 && TPR >= 160) ? (VPT == 1 ? 1536 : 1024) / RegGeom<TPR>::kBlock : RegGeom<TPR>::kBwdMinBlocks)
 rms_bwd_reg(T* dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
             const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int cols, const T* dres = nullptr) {
     using Geo = RegGeom<TPR>;
@@ -442,48 +443,72 @@ rms_bwd_dw_scalar(float* __restrict__ ws, const T* __restrict__ dy, const T* __r
 
 struct RegShape {
     int tpr, vpt;
+    bool fwd_ok, bwd_ok;   // fitted shapes only: whether the forward / the backward may pick it (from measurements)
 };
-// The last three are alternatives to {128,4}, {256,4} and {128,2} with one row per CTA pass; only the backward
+// Indices 8-10 are alternatives to {128,4}, {256,4} and {128,2} with one row per CTA pass; only the backward
 // picks them (bwd_shape_for), the size-ordered search of reg_shape_for never reaches them.
-constexpr RegShape kRegShapes[] = {{32, 1}, {32, 2}, {32, 4}, {128, 2}, {128, 4}, {256, 4}, {512, 4}, {1024, 4}, {256, 2}, {512, 2}, {256, 1}};
+// From kFirstFitted on: shapes whose capacity TPR*VPT fits hidden sizes that are not powers of two (bf16: 2560,
+// 1536, 3072, 5120, 6144, 7168). A row of 640 packets in the {256,4} shape leaves 3 of every 8 packet slots, and the
+// loads that would fill them, empty. Measured on B200 (bf16, 2^28 elements, fraction of the copy bandwidth, fitted
+// against the power-of-two choice):
+//   backward: 1536: 0.91 / 0.80   2560: 0.92 / 0.76   3072: 0.91 / 0.83   5120: 0.89 / 0.74   6144: 0.84 / 0.80   7168: 0.87 / 0.86
+//   forward : 1536: 0.89 / 0.73   2560: 0.88 / 0.80   3072: 0.89 / 0.87 (fp32: 0.90 / 0.96)
+//             5120: 0.77 / 0.87   6144: 0.82 / 0.93   7168: 0.70 / 0.97  -- one row per pass of a 320-448 thread
+//             CTA with two packets per thread keeps too little in flight per barrier; the forward stays with {256,4}
+// ({768,2} for 12288 lost both ways, 0.53 / 0.85 and 0.70 / 0.73, and is not built.)
+constexpr RegShape kRegShapes[] = {{32, 1, true, true},   {32, 2, true, true},  {32, 4, true, true},  {128, 2, true, true},
+                                   {128, 4, true, true},  {256, 4, true, true}, {512, 4, true, true}, {1024, 4, true, true},
+                                   {256, 2, true, true},  {512, 2, true, true}, {256, 1, true, true},
+                                   {160, 2, true, true},  {192, 1, true, true}, {192, 2, false, true}, {320, 2, false, true},
+                                   {384, 2, false, true}, {448, 2, false, true}};
 constexpr int kNumRegShapes = sizeof(kRegShapes) / sizeof(kRegShapes[0]);
+constexpr int kFirstFitted = 11;
 constexpr int kScalarDwSlices = 64;
 
-// Index of the smallest packet shape that holds a row of `nvec` packets, or -1.
-// MGR_RMSNORM_BWD_SHAPE=<index into kRegShapes> pins the backward's packet shape when it can hold the row
-// (measurement aid); otherwise the default search.
-int reg_shape_for(int64_t nvec);
-// Forward: the size-ordered search, unless MGR_RMSNORM_FWD_SHAPE=<index into kRegShapes> pins a shape that can
-// hold the row (measurement aid).
-int fwd_shape_for(int64_t nvec) {
-    const char* e = std::getenv("MGR_RMSNORM_FWD_SHAPE");
-    if (e != nullptr) {
-        const int i = std::atoi(e);
-        if (i >= 0 && i < static_cast<int>(sizeof(kRegShapes) / sizeof(kRegShapes[0])) &&
-            nvec <= static_cast<int64_t>(kRegShapes[i].tpr) * kRegShapes[i].vpt)
-            return i;
+inline int64_t shape_capacity(int i) { return static_cast<int64_t>(kRegShapes[i].tpr) * kRegShapes[i].vpt; }
+
+// MGR_RMSNORM_FWD_SHAPE / MGR_RMSNORM_BWD_SHAPE=<index into kRegShapes> pin the packet shape when it can hold the
+// row (measurement aid). Returns -1 when unset or unusable.
+int pinned_shape(const char* var, int64_t nvec) {
+    const char* e = std::getenv(var);
+    if (e == nullptr) return -1;
+    const int i = std::atoi(e);
+    return (i >= 0 && i < kNumRegShapes && nvec <= shape_capacity(i)) ? i : -1;
+}
+
+// The fitted shape with the least capacity that still holds the row, if it is tighter than `base` (the choice of
+// the power-of-two shapes); else `base`.
+int tighter_fitted(int64_t nvec, int base, bool backward) {
+    int best = base;
+    for (int i = kFirstFitted; i < kNumRegShapes; ++i) {
+        if (!(backward ? kRegShapes[i].bwd_ok : kRegShapes[i].fwd_ok) || nvec > shape_capacity(i)) continue;
+        if (best < 0 || shape_capacity(i) < shape_capacity(best)) best = i;
     }
-    return reg_shape_for(nvec);
+    return best;
+}
+
+// Index of the first power-of-two packet shape (table order = capacity order) that holds a row of `nvec` packets, or -1.
+int reg_shape_for(int64_t nvec);
+int fwd_shape_for(int64_t nvec) {
+    const int pinned = pinned_shape("MGR_RMSNORM_FWD_SHAPE", nvec);
+    if (pinned >= 0) return pinned;
+    return tighter_fitted(nvec, reg_shape_for(nvec), false);
 }
 int bwd_shape_for(int64_t nvec) {
-    const char* e = std::getenv("MGR_RMSNORM_BWD_SHAPE");
-    if (e != nullptr) {
-        const int i = std::atoi(e);
-        if (i >= 0 && i < static_cast<int>(sizeof(kRegShapes) / sizeof(kRegShapes[0])) &&
-            nvec <= static_cast<int64_t>(kRegShapes[i].tpr) * kRegShapes[i].vpt)
-            return i;
-    }
+    const int pinned = pinned_shape("MGR_RMSNORM_BWD_SHAPE", nvec);
+    if (pinned >= 0) return pinned;
     // Measured on B200 (bf16, 2^29 elements, fraction of the copy bandwidth): rows of 257-512 packets run at
     // 0.92 with {256,2} (one row per pass, 4 CTAs per SM) against 0.86 with {128,4}; rows of 513-1024 packets
     // are better left with {256,4} (0.92 against 0.89 for {512,2}).
     // Rows of 129-256 packets: 0.93 with {256,1} against 0.76 with {128,2} (and 0.84 for the ring kernel).
-    if (nvec > 256 && nvec <= 512) return 8;
-    if (nvec > 128 && nvec <= 256) return 10;
-    return reg_shape_for(nvec);
+    int base = reg_shape_for(nvec);
+    if (nvec > 256 && nvec <= 512) base = 8;
+    if (nvec > 128 && nvec <= 256) base = 10;
+    return tighter_fitted(nvec, base, true);
 }
 
 int reg_shape_for(int64_t nvec) {
-    for (int i = 0; i < kNumRegShapes; ++i)
+    for (int i = 0; i < kFirstFitted; ++i)
         if (nvec <= static_cast<int64_t>(kRegShapes[i].tpr) * kRegShapes[i].vpt) return i;
     return -1;
 }

@@ -15,6 +15,7 @@ from tests.util import TORCH_DTYPES, assert_matches_truth, seeded_rmsnorm_inputs
 pytestmark = pytest.mark.gpu
 
 SHAPES = [(1, 2), (3, 8), (129, 128), (7, 1000), (33, 1024), (128, 2048), (127, 4096), (64, 5120), (300, 8192),
+          (50, 1536), (70, 2560), (40, 3072), (200, 6144), (30, 7168),
           (40, 16384), (9, 32768), (3, 40000)]
 
 

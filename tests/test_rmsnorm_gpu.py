@@ -45,6 +45,8 @@ def check_against_oracle(ops, rows, cols, dtype, eps, seed=1234, x_scale=1.0):
 
 
 SHAPES = [(1, 2), (3, 8), (5, 64), (129, 128), (7, 1000), (33, 1024), (128, 2048), (127, 4096), (64, 5120),
+          # hidden sizes that are not powers of two: the fitted packet shapes (160-448 threads per row)
+          (90, 1536), (77, 2560), (61, 3072), (300, 6144), (45, 7168), (21, 12288),
           (300, 8192), (40, 16384), (9, 32768), (3, 40000)]
 
 
