@@ -72,8 +72,8 @@ struct NarrowGeom {
     int ksub, stages;
     uint32_t sub_bytes;
 };
-__host__ __device__ inline NarrowGeom narrow_geom(uint32_t a_box_bytes, int bn) {
-    NarrowGeom g;
+__host__ __device__ constexpr NarrowGeom narrow_geom(uint32_t a_box_bytes, int bn) {
+    NarrowGeom g{0, 0, 0};
     g.sub_bytes = a_box_bytes + b_bytes(bn);
     // The MMA reads a full 128-row A operand (16 KB from the sub-stage's start) whatever the box loaded; the rows
     // beyond the box only feed output rows that are never stored, but the read itself must stay inside the ring
@@ -86,6 +86,18 @@ __host__ __device__ inline NarrowGeom narrow_geom(uint32_t a_box_bytes, int bn) 
     g.stages = n > static_cast<uint32_t>(kMaxStages) ? kMaxStages : static_cast<int>(n);
     return g;
 }
+// Checked at compile time for every A box (8..128 rows) and both narrow widths: at least two stages, the ring
+// holds them, and the 16 KB A window of the very last sub-stage ends inside the ring.
+constexpr bool narrow_geom_fits(int bn) {
+    for (uint32_t rows = 8; rows <= static_cast<uint32_t>(kBM); rows += 8) {
+        const NarrowGeom g = narrow_geom(rows * kBK * 2, bn);
+        const uint32_t last_sub = (static_cast<uint32_t>(g.stages) * g.ksub - 1) * g.sub_bytes;
+        if (g.stages < 2 || g.stages > kMaxStages || g.ksub < 1) return false;
+        if (last_sub + kABytes > kNarrowRing || last_sub + g.sub_bytes > kNarrowRing) return false;
+    }
+    return true;
+}
+static_assert(narrow_geom_fits(kBNSmall) && narrow_geom_fits(kBNTiny), "narrow-tile ring geometry leaves shared memory");
 
 constexpr int kEpiWarps = 8;      // epilogue warps: two per 32-lane quarter of tensor memory
 // ring depth and dynamic shared memory of a kernel instance (a CTA pair gives up one stage to the staging buffers)
