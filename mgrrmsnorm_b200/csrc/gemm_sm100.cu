@@ -168,7 +168,7 @@ constexpr int kBandRows = 2048;
 struct TileCoord {
     int m0, n0;
 };
-__device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_tiles, int n_step, int m_step) {
+__host__ __device__ constexpr TileCoord tile_coord(int t, int m_tiles, int n_tiles, int n_step, int m_step) {
     const int band = kBandRows / m_step;                 // M tiles per band
     const int per_band = band * n_tiles;
     const int b = t / per_band;
@@ -178,6 +178,28 @@ __device__ __forceinline__ TileCoord tile_coord(int t, int m_tiles, int n_tiles,
     const int ni = r / rows_here;
     return TileCoord{mi * m_step, ni * n_step};
 }
+// Checked at compile time: the walk visits every tile of an m_tiles x n_tiles grid exactly once, for single CTAs
+// (128-row steps, 16 row tiles per band) and pairs (256-row steps, 8 per band), full and short last bands.
+constexpr bool tile_walk_visits_each_tile_once(int m_tiles, int n_tiles, int m_step) {
+    bool seen[48 * 16] = {};
+    for (int t = 0; t < m_tiles * n_tiles; ++t) {
+        const TileCoord c = tile_coord(t, m_tiles, n_tiles, kBN, m_step);
+        if (c.m0 < 0 || c.n0 < 0 || c.m0 % m_step != 0 || c.n0 % kBN != 0) return false;
+        const int mi = c.m0 / m_step, ni = c.n0 / kBN;
+        if (mi >= m_tiles || ni >= n_tiles || seen[mi * 16 + ni]) return false;
+        seen[mi * 16 + ni] = true;
+    }
+    return true;
+}
+constexpr bool tile_walks_ok() {
+    const int steps[2] = {kBM, 2 * kBM};
+    for (int s = 0; s < 2; ++s)
+        for (int m = 1; m <= 40; ++m)
+            for (int n = 1; n <= 13; n += 3)
+                if (!tile_walk_visits_each_tile_once(m, n, steps[s])) return false;
+    return true;
+}
+static_assert(tile_walks_ok(), "the band-wise tile walk skips or repeats a tile");
 
 // C = op(A) op(B)^T on one 128 x 256 accumulator tile per step.
 //   A: K-major = stored [M, K] (tmA box 64(K) x 128);  MN-major = stored [K, M] (tmA box 64(M) x 64(K)).
