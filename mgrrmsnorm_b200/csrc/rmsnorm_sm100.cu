@@ -465,7 +465,7 @@ constexpr int kNumRegShapes = sizeof(kRegShapes) / sizeof(kRegShapes[0]);
 constexpr int kFirstFitted = 11;
 constexpr int kScalarDwSlices = 64;
 
-inline int64_t shape_capacity(int i) { return static_cast<int64_t>(kRegShapes[i].tpr) * kRegShapes[i].vpt; }
+constexpr int64_t shape_capacity(int i) { return static_cast<int64_t>(kRegShapes[i].tpr) * kRegShapes[i].vpt; }
 
 // MGR_RMSNORM_FWD_SHAPE / MGR_RMSNORM_BWD_SHAPE=<index into kRegShapes> pin the packet shape when it can hold the
 // row (measurement aid). Returns -1 when unset or unusable.
@@ -478,7 +478,7 @@ int pinned_shape(const char* var, int64_t nvec) {
 
 // The fitted shape with the least capacity that still holds the row, if it is tighter than `base` (the choice of
 // the power-of-two shapes); else `base`.
-int tighter_fitted(int64_t nvec, int base, bool backward) {
+constexpr int tighter_fitted(int64_t nvec, int base, bool backward) {
     int best = base;
     for (int i = kFirstFitted; i < kNumRegShapes; ++i) {
         if (!(backward ? kRegShapes[i].bwd_ok : kRegShapes[i].fwd_ok) || nvec > shape_capacity(i)) continue;
@@ -488,15 +488,13 @@ int tighter_fitted(int64_t nvec, int base, bool backward) {
 }
 
 // Index of the first power-of-two packet shape (table order = capacity order) that holds a row of `nvec` packets, or -1.
-int reg_shape_for(int64_t nvec);
-int fwd_shape_for(int64_t nvec) {
-    const int pinned = pinned_shape("MGR_RMSNORM_FWD_SHAPE", nvec);
-    if (pinned >= 0) return pinned;
-    return tighter_fitted(nvec, reg_shape_for(nvec), false);
+constexpr int reg_shape_for(int64_t nvec) {
+    for (int i = 0; i < kFirstFitted; ++i)
+        if (nvec <= shape_capacity(i)) return i;
+    return -1;
 }
-int bwd_shape_for(int64_t nvec) {
-    const int pinned = pinned_shape("MGR_RMSNORM_BWD_SHAPE", nvec);
-    if (pinned >= 0) return pinned;
+constexpr int default_fwd_shape(int64_t nvec) { return tighter_fitted(nvec, reg_shape_for(nvec), false); }
+constexpr int default_bwd_shape(int64_t nvec) {
     // Measured on B200 (bf16, 2^29 elements, fraction of the copy bandwidth): rows of 257-512 packets run at
     // 0.92 with {256,2} (one row per pass, 4 CTAs per SM) against 0.86 with {128,4}; rows of 513-1024 packets
     // are better left with {256,4} (0.92 against 0.89 for {512,2}).
@@ -506,11 +504,31 @@ int bwd_shape_for(int64_t nvec) {
     if (nvec > 128 && nvec <= 256) base = 10;
     return tighter_fitted(nvec, base, true);
 }
+// Checked at compile time: every row of up to 4096 packets gets a shape that holds it (forward and backward),
+// longer rows get none (they take the scalar kernels), and every shape is launchable: whole warps per row, at
+// most 1024 threads, and the backward's fold buffer within the static shared-memory limit.
+constexpr bool shape_tables_ok() {
+    for (int i = 0; i < kNumRegShapes; ++i) {
+        const int tpr = kRegShapes[i].tpr, vpt = kRegShapes[i].vpt;
+        const int block = tpr >= 256 ? tpr : (256 % tpr == 0 ? 256 : tpr);
+        if (tpr % 32 != 0 || block > 1024 || block % tpr != 0 || vpt < 1 || vpt > 4) return false;
+        if (static_cast<int64_t>(block / tpr - 1) * tpr * vpt * 8 * 4 > 44 * 1024) return false;
+    }
+    for (int64_t nvec = 1; nvec <= 4096; ++nvec) {
+        const int f = default_fwd_shape(nvec), b = default_bwd_shape(nvec);
+        if (f < 0 || b < 0 || shape_capacity(f) < nvec || shape_capacity(b) < nvec) return false;
+    }
+    return default_fwd_shape(4097) < 0 && default_bwd_shape(4097) < 0;
+}
+static_assert(shape_tables_ok(), "a row length has no packet shape, or a shape cannot be launched");
 
-int reg_shape_for(int64_t nvec) {
-    for (int i = 0; i < kFirstFitted; ++i)
-        if (nvec <= static_cast<int64_t>(kRegShapes[i].tpr) * kRegShapes[i].vpt) return i;
-    return -1;
+int fwd_shape_for(int64_t nvec) {
+    const int pinned = pinned_shape("MGR_RMSNORM_FWD_SHAPE", nvec);
+    return pinned >= 0 ? pinned : default_fwd_shape(nvec);
+}
+int bwd_shape_for(int64_t nvec) {
+    const int pinned = pinned_shape("MGR_RMSNORM_BWD_SHAPE", nvec);
+    return pinned >= 0 ? pinned : default_bwd_shape(nvec);
 }
 
 template <typename K>
