@@ -51,7 +51,7 @@ __host__ __device__ constexpr uint32_t b_bytes(int bn) { return bn * kBK * 2; } 
 __host__ __device__ constexpr uint32_t stage_bytes(int cg, int bn) { return kABytes + b_bytes(bn) / cg; }
 __host__ __device__ constexpr int num_stages(int cg, int bn) { return bn < kBN ? 8 : (cg == 1 ? 4 : 7); }
 // + slack to align to 1024 B. The narrow-tile kernels take (nearly) all the shared memory an SM has and cut it into
-// as many stages as fit at run time (a short A box makes a stage smaller, see narrow_stages()).
+// as many stages as fit at run time (a short A box makes a stage smaller, see narrow_geom()).
 constexpr uint32_t kNarrowRing = 216 * 1024;
 __host__ __device__ constexpr uint32_t gemm_smem(int cg, int bn) {
     return (bn < kBN ? kNarrowRing : num_stages(cg, bn) * stage_bytes(cg, bn)) + 1024;
