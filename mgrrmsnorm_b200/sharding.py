@@ -137,6 +137,10 @@ class AsyncDwReduce:
         if dw_f32.dtype != torch.float32:
             raise TypeError("the cross-rank sum of dW is taken in fp32")
         self.side.wait_stream(torch.cuda.current_stream(dw_f32.device))   # the partial has been produced
+        # both tensors are used on the side stream: tell the caching allocator, so that freeing one of them on
+        # the compute stream cannot hand its memory out again while the collective still runs
+        dw_f32.record_stream(self.side)
+        dw_out.record_stream(self.side)
         with torch.cuda.stream(self.side):
             dist.all_reduce(dw_f32, op=dist.ReduceOp.SUM, group=self.group)
             dw_out.copy_(dw_f32)                                          # the single rounding
