@@ -15,7 +15,7 @@ import pytest
 import torch
 
 from mgrrmsnorm_b200 import _capi
-from tests.util import TORCH_DTYPES, seeded_rmsnorm_inputs
+from tests.util import seeded_rmsnorm_inputs
 
 pytestmark = pytest.mark.gpu
 
