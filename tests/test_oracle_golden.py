@@ -45,6 +45,27 @@ def test_live_reference_library_agrees_with_fixture(rms):
     assert np.array_equal(y, rms["f32_a_y_refcpu"])
 
 
+def test_live_reference_cpu_forward_is_reproduced_on_random_shapes():
+    """The reference's compiled rmsnorm_cpu (rmsnorm_standalone.cu:17-30) against the restatement on seeded
+    random shapes, value scales and epsilons: bit-exact every time, and within fp32 rounding of the fp64 truth."""
+    ref = oracle.ref_lib()
+    if ref is None:
+        pytest.skip("oracle/_ref/libmgr_ref.so not built (no reference tree on this machine)")
+    rng = np.random.default_rng(2024)
+    for _ in range(25):
+        rows = int(rng.integers(1, 40))
+        cols = int(rng.choice([1, 2, 7, 8, 64, 100, 255, 256, 1000, 1024, 4096, 5120]))
+        scale = float(rng.choice([1e-3, 1.0, 30.0]))
+        eps = float(rng.choice([1e-5, 1e-6, 1e-12]))
+        x = (scale * rng.standard_normal((rows, cols))).astype(np.float32)
+        w = (1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+        want = ref.cpu_forward(x, w, eps)
+        got = oracle.rmsnorm_fwd_f32seq(x, w, eps)
+        assert np.array_equal(got, want), (rows, cols, scale, eps)
+        truth, _ = oracle.rmsnorm_fwd(x, w, eps)
+        np.testing.assert_allclose(want, truth, rtol=4e-6, atol=1e-6 * scale)
+
+
 @pytest.mark.parametrize("case,tol", [("act_f32", 2e-6), ("act_f16", 2e-3), ("act_bf16", 1.6e-2)])
 def test_activation_matches_reference_triton_kernels(swi, case, tol):
     """fp64 oracle vs _mg_swiglu_fwd_kernel / _mg_swiglu_bwd_kernel outputs (megagemm/swiglu.py:18-79).
