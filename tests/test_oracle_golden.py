@@ -127,3 +127,58 @@ def test_add_rmsnorm_composition_matches_reference_sequence(golden_dir, case):
     np.testing.assert_allclose(y, z[f"{case}_y"], rtol=1e-12, atol=1e-13)
     np.testing.assert_allclose(dx + dres.astype(np.float64), z[f"{case}_dh"], rtol=1e-10, atol=1e-12)
     np.testing.assert_allclose(dw, z[f"{case}_dw"], rtol=1e-10, atol=1e-12)
+
+
+_LIVE_TRITON_SCRIPT = r"""
+import os, sys
+os.environ["TRITON_INTERPRET"] = "1"
+ref_dir, out_path = sys.argv[1], sys.argv[2]
+sys.path.insert(0, ref_dir)
+import numpy as np, torch
+from megagemm.swiglu import MegaGemmFunction          # the reference package, unmodified
+g = torch.Generator().manual_seed(777)
+out = {}
+for i, (m, f, dt) in enumerate([(3, 32, torch.float32), (7, 96, torch.float32), (5, 160, torch.float16),
+                                (4, 256, torch.bfloat16), (1, 8, torch.float32), (6, 1000, torch.float16)]):
+    gv = (2.0 * torch.randn(m, 2 * f, generator=g)).to(dt).requires_grad_(True)
+    dh = torch.randn(m, f, generator=g).to(dt)
+    h = MegaGemmFunction.apply(gv, f)
+    h.backward(dh)
+    out[f"c{i}_f"] = np.int64(f)
+    out[f"c{i}_dtype"] = np.array(str(dt).split(".")[1])
+    out[f"c{i}_gv"] = gv.detach().float().numpy(); out[f"c{i}_dh"] = dh.float().numpy()
+    out[f"c{i}_h"] = h.detach().float().numpy(); out[f"c{i}_dgv"] = gv.grad.float().numpy()
+np.savez(out_path, **out)
+"""
+
+
+def test_live_reference_triton_kernels_on_random_inputs(tmp_path):
+    """Where the reference tree is present (this never runs on the GPU box): its Triton kernels
+    (_mg_swiglu_fwd_kernel / _mg_swiglu_bwd_kernel, megagemm/swiglu.py:18-79) executed by the Triton interpreter
+    on fresh random inputs, against the oracle. Outputs are stored in the input dtype; the bound is one unit in
+    the last place of that dtype (the interpreter's narrowing conversion is not always round-to-nearest-even)
+    plus fp32 evaluation error."""
+    import os
+    import subprocess
+    import sys
+    from pathlib import Path
+
+    ref_dir = Path(os.environ.get("MGR_REFERENCE_DIR", "/root/reference"))
+    if not (ref_dir / "megagemm" / "swiglu.py").exists():
+        pytest.skip("reference tree not present on this machine")
+    out_path = tmp_path / "live.npz"
+    run = subprocess.run([sys.executable, "-c", _LIVE_TRITON_SCRIPT, str(ref_dir), str(out_path)], capture_output=True,
+                         text=True, timeout=600)
+    if run.returncode != 0 and "triton" in (run.stderr or "").lower() and "interpret" in (run.stderr or "").lower():
+        pytest.skip("Triton interpreter unavailable: " + run.stderr[-200:])
+    assert run.returncode == 0, run.stderr[-1500:]
+    z = np.load(out_path)
+    n = len([k for k in z.files if k.endswith("_f")])
+    assert n == 6
+    for i in range(n):
+        f = int(z[f"c{i}_f"])
+        dtype = {"float32": "f32", "float16": "f16", "bfloat16": "bf16"}[str(z[f"c{i}_dtype"])]
+        gv, dh = z[f"c{i}_gv"], z[f"c{i}_dh"]
+        for got, truth in ((z[f"c{i}_h"], oracle.swiglu_act_fwd(gv, f)), (z[f"c{i}_dgv"], oracle.swiglu_act_bwd(dh, gv, f))):
+            bound = oracle.ulp_of(truth, dtype) * (0 if dtype == "f32" else 1) + 4e-6 * np.abs(truth) + 1e-6
+            assert (np.abs(got.astype(np.float64) - truth) <= bound).all(), (i, dtype, float(np.abs(got - truth).max()))
