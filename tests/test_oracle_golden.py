@@ -182,3 +182,44 @@ def test_live_reference_triton_kernels_on_random_inputs(tmp_path):
         for got, truth in ((z[f"c{i}_h"], oracle.swiglu_act_fwd(gv, f)), (z[f"c{i}_dgv"], oracle.swiglu_act_bwd(dh, gv, f))):
             bound = oracle.ulp_of(truth, dtype) * (0 if dtype == "f32" else 1) + 4e-6 * np.abs(truth) + 1e-6
             assert (np.abs(got.astype(np.float64) - truth) <= bound).all(), (i, dtype, float(np.abs(got - truth).max()))
+
+
+def test_oracle_backward_formulas_against_finite_differences():
+    """Independent of torch autograd: the oracle's closed-form backward (src/rmsnorm_kernel.cu:258-312 for the
+    norm, megagemm/swiglu.py:64-76 for the activation) against central differences of its own forward, in fp64."""
+    rng = np.random.default_rng(5)
+    rows, cols, eps = 3, 24, 1e-6
+    x = rng.standard_normal((rows, cols)).astype(np.float32)
+    w = (1 + 0.1 * rng.standard_normal(cols)).astype(np.float32)
+    dy = rng.standard_normal((rows, cols)).astype(np.float32)
+
+    def loss(xx, ww):
+        xx = xx.astype(np.float64); ww = ww.astype(np.float64)
+        inv = 1.0 / np.sqrt((xx * xx).mean(axis=1, keepdims=True) + float(np.float32(eps)))
+        return float((xx * inv * ww * dy).sum())
+
+    dx, dw = oracle.rmsnorm_bwd(dy, x, w, eps)
+    h = 1e-4
+    for (r, c) in [(0, 0), (1, 7), (2, 23)]:
+        xp, xm = x.astype(np.float64).copy(), x.astype(np.float64).copy()
+        xp[r, c] += h; xm[r, c] -= h
+        assert abs((loss(xp, w) - loss(xm, w)) / (2 * h) - dx[r, c]) < 1e-6
+    for c in (0, 11, 23):
+        wp, wm = w.astype(np.float64).copy(), w.astype(np.float64).copy()
+        wp[c] += h; wm[c] -= h
+        assert abs((loss(x, wp) - loss(x, wm)) / (2 * h) - dw[c]) < 1e-6
+
+    m, f = 4, 10
+    gv = (1.5 * rng.standard_normal((m, 2 * f))).astype(np.float32)
+    dh = rng.standard_normal((m, f)).astype(np.float32)
+
+    def act_loss(g):
+        g = g.astype(np.float64)
+        gate, val = g[:, :f], g[:, f:]
+        return float((gate / (1 + np.exp(-gate)) * val * dh).sum())
+
+    dgv = oracle.swiglu_act_bwd(dh, gv, f)
+    for (r, c) in [(0, 0), (2, f - 1), (1, f), (3, 2 * f - 1)]:
+        gp, gm = gv.astype(np.float64).copy(), gv.astype(np.float64).copy()
+        gp[r, c] += h; gm[r, c] -= h
+        assert abs((act_loss(gp) - act_loss(gm)) / (2 * h) - dgv[r, c]) < 1e-6
