@@ -257,3 +257,43 @@ def test_sequence_parallel_module_checks_its_input():
         sp(torch.zeros(16, 64, dtype=torch.float16))
     with pytest.raises(ValueError):
         sharding.SequenceParallelSwiGLU(64, 100, world=3, rank=0)   # hidden not divisible by the group size
+
+
+def test_index_arithmetic_properties():
+    """row_shard blocks tile [0, rows) in rank order and differ by at most one row; slab_bounds tiles a rank's rows
+    in multiples of eight; tensor-parallel weight shards put every hidden unit on exactly one rank."""
+    from hypothesis import given, settings
+    from hypothesis import strategies as st
+
+    @settings(max_examples=200, deadline=None)
+    @given(rows=st.integers(0, 5000), world=st.integers(1, 16))
+    def rows_tile(rows, world):
+        blocks = [sharding.row_shard(rows, world, r) for r in range(world)]
+        assert blocks[0][0] == 0 and blocks[-1][1] == rows
+        assert all(b0[1] == b1[0] for b0, b1 in zip(blocks, blocks[1:]))
+        sizes = [b - a for a, b in blocks]
+        assert max(sizes) - min(sizes) <= 1 and sizes == sorted(sizes, reverse=True)
+
+    @settings(max_examples=200, deadline=None)
+    @given(k=st.integers(1, 600), slabs=st.integers(1, 12))
+    def slabs_tile(k, slabs):
+        rows = 8 * k
+        cuts = sharding.slab_bounds(rows, slabs)
+        assert 1 <= len(cuts) <= slabs and cuts[0][0] == 0 and cuts[-1][1] == rows
+        assert all(c0[1] == c1[0] for c0, c1 in zip(cuts, cuts[1:]))
+        assert all((b - a) % 8 == 0 and b > a for a, b in cuts)
+
+    @settings(max_examples=50, deadline=None)
+    @given(per=st.integers(1, 6), world=st.integers(1, 8), d=st.integers(1, 5))
+    def shards_partition(per, world, d):
+        f = per * world
+        w12 = torch.arange(2 * f * d, dtype=torch.float32).view(2 * f, d)
+        w3 = torch.arange(d * f, dtype=torch.float32).view(d, f)
+        s12 = [sharding.tp_shard_w12(w12, world, r) for r in range(world)]
+        s3 = [sharding.tp_shard_w3(w3, world, r) for r in range(world)]
+        assert torch.equal(sharding.tp_unshard_w12(s12), w12) and torch.equal(sharding.tp_unshard_w3(s3), w3)
+        assert all(s.shape == (2 * per, d) for s in s12) and all(s.shape == (d, per) for s in s3)
+
+    rows_tile()
+    slabs_tile()
+    shards_partition()
