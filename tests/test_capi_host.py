@@ -104,6 +104,56 @@ def test_swiglu_act_argument_errors(built_lib, fn):
     assert call(m=0) == _capi.MGR_OK
 
 
+def test_add_rmsnorm_argument_errors(built_lib):
+    def fwd(y=P, h=P, inv=P, x=P, res=P, w=P, rows=4, cols=64, dtype=_capi.MGR_BF16):
+        return built_lib.mgr_add_rmsnorm_fwd(y, h, inv, x, res, w, rows, cols, 1e-6, dtype, None)
+
+    def bwd(dh=P, dw=P, dw32=None, dy=P, dres=P, h=P, w=P, inv=P, rows=4, cols=64, dtype=_capi.MGR_BF16, ws=P, wsb=1 << 20):
+        return built_lib.mgr_add_rmsnorm_bwd(dh, dw, dw32, dy, dres, h, w, inv, rows, cols, dtype, ws, wsb, None)
+
+    assert fwd(dtype=5) == _capi.MGR_ERR_BAD_DTYPE
+    assert fwd(cols=0) == _capi.MGR_ERR_BAD_SHAPE
+    assert fwd(res=None) == _capi.MGR_ERR_NULL_PTR          # the residual operand is required here
+    assert fwd(h=None) == _capi.MGR_ERR_NULL_PTR
+    assert fwd(res=P + 1) == _capi.MGR_ERR_MISALIGNED
+    assert fwd(rows=0) == _capi.MGR_OK
+    assert bwd(dtype=-2) == _capi.MGR_ERR_BAD_DTYPE
+    assert bwd(rows=-1) == _capi.MGR_ERR_BAD_SHAPE
+    assert bwd(dres=None) == _capi.MGR_ERR_NULL_PTR
+    assert bwd(dw=None, dw32=None) == _capi.MGR_ERR_NULL_PTR
+    assert bwd(dres=P + 1) == _capi.MGR_ERR_MISALIGNED
+    assert bwd(ws=P + 4) == _capi.MGR_ERR_MISALIGNED
+
+
+def test_gemm_family_argument_errors(built_lib):
+    """Shape, dtype, pointer and pitch errors of the tensor-core entry points come back as status codes before
+    any CUDA call is made."""
+    L, F16 = built_lib, _capi.MGR_F16
+
+    def gemm(c=P, a=P, b=P, m=16, n=64, k=64, lda=64, ldb=64, ldc=64, amn=0, bmn=0, dtype=F16):
+        return L.mgr_gemm(c, a, b, m, n, k, lda, ldb, ldc, amn, bmn, dtype, None)
+
+    assert gemm(dtype=_capi.MGR_F32) == _capi.MGR_ERR_BAD_DTYPE          # tensor-core kernels take fp16 / bf16 only
+    assert gemm(n=60) == _capi.MGR_ERR_BAD_SHAPE and gemm(k=12) == _capi.MGR_ERR_BAD_SHAPE
+    assert gemm(lda=32) == _capi.MGR_ERR_BAD_SHAPE                         # pitch shorter than the row
+    assert gemm(ldc=68) == _capi.MGR_ERR_BAD_SHAPE                         # pitch not a multiple of 8 elements
+    assert gemm(m=12, amn=1, lda=16) == _capi.MGR_ERR_BAD_SHAPE            # rows of an MN-major A are its inner dimension
+    assert gemm(m=(1 << 30) + 8) == _capi.MGR_ERR_TOO_LARGE
+    assert gemm(a=None) == _capi.MGR_ERR_NULL_PTR and gemm(c=P + 8) == _capi.MGR_ERR_MISALIGNED
+    assert gemm(m=0) == _capi.MGR_OK
+    assert L.mgr_gemm_tn(P, P, P, 16, 64, 63, 64, 64, 64, F16, None) == _capi.MGR_ERR_BAD_SHAPE
+    for fn, nargs in ((L.mgr_swiglu_fused_fwd, 3), (L.mgr_swiglu_fused_bwd, 4), (L.mgr_swiglu_fused_fwd_save, 4), (L.mgr_swiglu_dh_dgv, 4)):
+        ptrs = [P] * nargs
+        assert fn(*ptrs, 16, 64, 64, _capi.MGR_F32, None) == _capi.MGR_ERR_BAD_DTYPE
+        assert fn(*ptrs, 16, 64, 60, F16, None) == _capi.MGR_ERR_BAD_SHAPE
+        assert fn(*ptrs, 16, 63, 64, F16, None) == _capi.MGR_ERR_BAD_SHAPE
+        assert fn(*([None] + ptrs[1:]), 16, 64, 64, F16, None) == _capi.MGR_ERR_NULL_PTR
+        assert fn(*([P + 2] + ptrs[1:]), 16, 64, 64, F16, None) == _capi.MGR_ERR_MISALIGNED
+        assert fn(*ptrs, 0, 64, 64, F16, None) == _capi.MGR_OK
+    assert L.mgr_gemm_set_sm_limit(0) >= 0            # returns the previous limit; 0 = all SMs
+    assert L.mgr_gemm_set_sm_limit(100) == 0 and L.mgr_gemm_set_sm_limit(0) == 100
+
+
 def test_workspace_query_rejects_bad_arguments(built_lib):
     assert built_lib.mgr_rmsnorm_bwd_workspace_bytes(-1, 64, _capi.MGR_F32) == 0
     assert built_lib.mgr_rmsnorm_bwd_workspace_bytes(4, 0, _capi.MGR_F32) == 0
