@@ -108,6 +108,20 @@ __host__ __device__ constexpr uint32_t gemm_smem_epi(int epi, int cg, int bn) {
     return epi == 4 ? num_stages_epi(epi, cg, bn) * stage_bytes(cg, bn) + 1024 + kEpiWarps * kEpiStageBytes : gemm_smem(cg, bn);
 }
 constexpr int kGemmThreads = (2 + kEpiWarps) * 32;
+// Shared-memory budget of every kernel instance, checked at compile time: the dynamic ring (+ staging buffers)
+// plus 2 KB for the static barriers and flags stays within the 227 KB a CTA may use; stages and staging rows keep
+// the alignment the 128-byte swizzle (1024 B) and the 16-byte shared-memory vectors need.
+constexpr bool smem_budgets_ok() {
+    constexpr uint32_t kCtaLimit = 227u * 1024u, kStatic = 2048u;
+    for (int epi = 0; epi <= 4; ++epi)
+        for (int cg = 1; cg <= 2; ++cg) {
+            if (gemm_smem_epi(epi, cg, kBN) + kStatic > kCtaLimit) return false;
+            if (stage_bytes(cg, kBN) % 1024u != 0 || num_stages_epi(epi, cg, kBN) > kMaxStages) return false;
+        }
+    if (gemm_smem(1, kBNSmall) + kStatic > kCtaLimit || gemm_smem(1, kBNTiny) + kStatic > kCtaLimit) return false;
+    return kEpiRowPitch % 16u == 0 && kEpiStageBytes % 16u == 0 && kNarrowRing % 1024u == 0 && b_bytes(kBNTiny) % 1024u == 0;
+}
+static_assert(smem_budgets_ok(), "a GEMM kernel instance exceeds the shared-memory budget or breaks an alignment rule");
 constexpr uint32_t kTmemCols = 512;
 
 enum Epilogue { kEpiPlain = 0, kEpiSwiglu = 1, kEpiSwigluBwd = 2, kEpiSwigluSave = 3, kEpiDhDgv = 4 };
