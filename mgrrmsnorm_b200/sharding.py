@@ -18,6 +18,9 @@ the compute they wrap is the CUDA library and needs a GPU.
 """
 from __future__ import annotations
 
+import contextlib
+import os
+
 import torch
 import torch.distributed as dist
 import torch.nn as nn
@@ -330,9 +333,6 @@ SP_LIMIT = "all"
 
 
 def _sp_limit(kind: str, device):
-    import contextlib
-    import os
-
     mode = os.environ.get("MGR_SP_LIMIT", SP_LIMIT)
     on = mode == "all" or mode == kind
     return rmsnorm_cuda_ops.gemm_sm_limit(COMM_SMS, device) if on else contextlib.nullcontext()
