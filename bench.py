@@ -5,13 +5,19 @@
     python bench.py --impl reference --gpus N --steps K ...  # the reference's CPU path, host cores
     torchrun --nproc-per-node N ... bench.py --gpus N ...    # N > 1: one rank per GPU
 
-A step is one RMSNorm forward + backward over one batch: bf16, 65536 rows x hidden 8192 per GPU
-(x ~ N(0,2), w = 1 + 0.1 N(0,1), dy ~ N(0,1), eps 1e-6, seeded). With N > 1 every rank holds its own
-row block of that size (weak scaling) and the fp32 dW partial is all-reduced over NCCL each step.
-The metric is algorithmic bytes per second, 5*R*H*s + 3*H*s + 8*R bytes per step and GPU.
+A step is one RMSNorm forward + backward over one batch: bf16, 65536 rows x hidden 8192 IN TOTAL
+(x ~ N(0,2), w = 1 + 0.1 N(0,1), dy ~ N(0,1), eps 1e-6, seeded). With N > 1 the rows are split into N
+contiguous blocks, one per rank (strong scaling: the job is fixed), and the fp32 dW partial is all-reduced
+over NCCL each step, then rounded once. The metric is algorithmic bytes per second: every rank's
+5*R*H*s + 3*H*s + 8*R bytes, summed over the ranks, divided by the slowest rank's time.
 
 Rank 0 prints ONE JSON line. `value` is timed with inputs resident in HBM; `e2e` goes through the
-public module API with pinned host buffers and host<->device copies inside the timed region.
+library's host-tensor entry with pinned host buffers and host<->device copies inside the timed region.
+The same line carries, as compact keys, the other half of the metric -- `block`: the bf16 pre-norm block
+RMSNorm(8192) -> SwiGLU(d_ff 28672) over 16384 tokens, tensor-parallel over the N ranks (TFLOP/s); `mlp`
+(N = 1): the fp16 SwiGLU MLP of d_model 4096 -- and, for N > 1, `parity_n`: sharded results checked
+against the one-rank result on the spot, `weak`: the 65536-rows-per-GPU figure, and `allreduce`: what the
+latency-bound dW collective costs on the compute stream and beside the next forward.
 """
 from __future__ import annotations
 
@@ -33,7 +39,8 @@ import torch
 
 METRIC = "RMSNorm fwd+bwd GB/s"
 UNIT = "GB/s"
-ROWS_PER_GPU = 65536
+TOTAL_ROWS = 65536       # the benchmark's batch; split over the ranks
+ROWS_PER_GPU = 65536     # the weak-scaling side figure keeps this many rows on every GPU
 HIDDEN = 8192
 EPS = 1e-6
 SEED = 1234
@@ -181,8 +188,8 @@ def time_cpu(steps: int, warmup: int, budget_s: float | None = None) -> dict:
     per_step = sum(times) / len(times)
     nbytes = rms_bytes(CPU_SAMPLE_ROWS, HIDDEN, 2)["total"]
     return {"value": nbytes / per_step / 1e9, "unit": UNIT, "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"torch formula fwd+bwd (fp32 math on bf16 tensors) on {CPU_SAMPLE_ROWS} of the {ROWS_PER_GPU} rows x {HIDDEN}, "
-                      f"{len(times)} steps, bytes counted as for the GPU arm (2 B/element)",
+            "sample": f"torch formula fwd+bwd (fp32 math on bf16 tensors) on {CPU_SAMPLE_ROWS} of the {TOTAL_ROWS} rows x {HIDDEN} per step "
+                      f"(1/{TOTAL_ROWS // CPU_SAMPLE_ROWS} of the workload), {len(times)} steps, bytes counted as for the GPU arm (2 B/element)",
             "ms_per_step": per_step * 1e3, "steps": len(times), "os_cpu_count": os.cpu_count()}
 
 
@@ -199,8 +206,9 @@ def reference_arm(args) -> int:
     line = {
         "impl": "reference", "metric": METRIC, "value": res["value"], "unit": UNIT, "n_gpus": args.gpus,
         "steps": res["steps"], "warmup": max(args.warmup, 1), "ms_per_step": res["ms_per_step"], "higher_is_better": True,
-        "scaling": "weak", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": workload_config(args.gpus),
+        "scaling": "strong", "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
+        "config": dict(workload_config(args.gpus), cpu_sample_rows_per_step=CPU_SAMPLE_ROWS,
+                       cpu_sample=f"each CPU step covers {CPU_SAMPLE_ROWS} of the {TOTAL_ROWS} rows; one host process, whatever --gpus says"),
         "cpu_baseline": {k: res[k] for k in ("value", "unit", "cores", "kind", "sample")},
         "e2e": {"value": res["value"], "unit": UNIT, "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
         "gpu_launches": 0,
@@ -209,11 +217,14 @@ def reference_arm(args) -> int:
     return 0
 
 
-def workload_config(n_gpus: int, rows: int = ROWS_PER_GPU) -> dict:
-    return {"workload": f"RMSNorm bf16 forward+backward, {rows} rows x hidden {HIDDEN} per GPU, eps 1e-6 "
-                        "(x~N(0,2), w=1+0.1N(0,1), dy~N(0,1))" + ("" if rows == ROWS_PER_GPU else " [REDUCED CASE, not the benchmark]"),
-            "rows_per_gpu": rows, "hidden": HIDDEN, "sharding": f"rows x{n_gpus}, fp32 dW all-reduce every step (on a side stream, beside the next step's forward)" if n_gpus > 1 else "none",
-            "l2": "inputs larger than L2 (1 GiB per tensor, 126 MB L2)", "seed": SEED}
+def workload_config(n_gpus: int, rows: int = TOTAL_ROWS) -> dict:
+    per = -(-rows // n_gpus)
+    return {"workload": f"RMSNorm bf16 forward+backward, {rows} rows x hidden {HIDDEN} in total, eps 1e-6 "
+                        "(x~N(0,2), w=1+0.1N(0,1), dy~N(0,1))" + ("" if rows == TOTAL_ROWS else " [REDUCED CASE, not the benchmark]"),
+            "rows_total": rows, "rows_per_gpu": per, "hidden": HIDDEN,
+            "sharding": (f"contiguous row blocks over {n_gpus} ranks, fp32 dW all-reduce every step (on a side stream, beside the next "
+                         "step's forward), one rounding after it") if n_gpus > 1 else "none",
+            "l2": f"inputs larger than L2 ({per * HIDDEN * 2 >> 20} MiB per tensor and GPU, four tensors per step, 126 MB L2)", "seed": SEED}
 
 
 # ---------------------------------------------------------------------------------------------------
@@ -259,20 +270,23 @@ class RmsBuffers:
             raise RuntimeError(f"mgr_rmsnorm_bwd status {st}")
 
 
-def time_device_resident(bufsets, steps, warmup, world, sampler=None):
+def time_device_resident(bufsets, steps, warmup, world, sampler=None, reduce="side"):
     """K steps over `bufsets` (rotated), CUDA events on the launching stream. Returns total ms, mean
     fwd-call ms, mean bwd-call ms and the wall-clock window of the timed region."""
     import torch.distributed as dist
 
     stream = torch.cuda.current_stream()
     sp = stream.cuda_stream
-    # N > 1: the all-reduce of the fp32 dW partial (32 KB, latency-bound) and the one rounding after it run on a
-    # side stream, beside the NEXT step's forward, as in a training loop where dW is not needed before the
-    # optimizer step. The next backward that overwrites the same dW buffer waits for it, and so does the end of
+    # N > 1, reduce="side": the all-reduce of the fp32 dW partial (32 KB, latency-bound) and the one rounding after
+    # it run on a side stream, beside the NEXT step's forward, as in a training loop where dW is not needed before
+    # the optimizer step. The next backward that overwrites the same dW buffer waits for it, and so does the end of
     # the timed region, so every step's collective completes inside the region it is timed in.
     # (mgrrmsnorm_b200.sharding.AsyncDwReduce is the library's helper for exactly this.)
+    # reduce="inline": the same all-reduce and rounding on the compute stream, right after the backward
+    # (sharding.allreduce_dw), so its whole latency is exposed.
     red = None
-    if world > 1:
+    inline = world > 1 and reduce == "inline"
+    if world > 1 and reduce == "side":
         from mgrrmsnorm_b200.sharding import AsyncDwReduce
 
         red = AsyncDwReduce(torch.cuda.current_device())
@@ -290,6 +304,9 @@ def time_device_resident(bufsets, steps, warmup, world, sampler=None):
             evs[2].record(stream)
         if red is not None:
             red.start(b.dw32, b.dw)
+        elif inline:
+            dist.all_reduce(b.dw32, op=dist.ReduceOp.SUM)
+            b.dw.copy_(b.dw32)                       # the single rounding
 
     def drain():
         if red is not None:
@@ -341,16 +358,20 @@ def time_e2e(rows, cols, device, steps, warmup, world, src, pipelined=True):
     hdw = torch.empty((cols,), dtype=dt).pin_memory()
     hx.copy_(src.x)
     hdy.copy_(src.dy)
-    norm = RMSNorm(cols, epsilon=EPS).to(device).to(dt)
+    from mgrrmsnorm_b200.sharding import RowShardedRMSNorm
+
+    norm = (RowShardedRMSNorm(cols, epsilon=EPS) if world > 1 else RMSNorm(cols, epsilon=EPS)).to(device).to(dt)
     with torch.no_grad():
         norm.weight.copy_(src.w)
     stream = torch.cuda.current_stream()
     pipe = HostRMSNormPipeline(rows, cols, dt, device) if pipelined else None
 
+    from mgrrmsnorm_b200 import sharding
+
     def step_pipelined():
-        dw = pipe.run(hx, hdy, norm.weight.detach(), EPS, hy, hdx)
-        if world > 1:
-            dist.all_reduce(dw)
+        # every rank's fp32 column sum is added across the ranks first and rounded once, as on the resident path
+        dw32 = pipe.run(hx, hdy, norm.weight.detach(), EPS, hy, hdx, return_f32=True)
+        dw = sharding.allreduce_dw(dw32, dt) if world > 1 else dw32.to(dt)
         hdw.copy_(dw, non_blocking=True)
 
     def step():
@@ -359,11 +380,9 @@ def time_e2e(rows, cols, device, steps, warmup, world, src, pipelined=True):
         x = hx.to(device, non_blocking=True).requires_grad_(True)
         dy = hdy.to(device, non_blocking=True)
         norm.weight.grad = None
-        y = norm(x)
+        y = norm(x)                 # RowShardedRMSNorm when world > 1: its backward all-reduces the fp32 dW, then rounds
         y.backward(dy)
         dw = norm.weight.grad
-        if world > 1:
-            dist.all_reduce(dw)   # public-API path: the rounded dW (the resident path reduces in fp32)
         hy.copy_(y.detach(), non_blocking=True)
         hdx.copy_(x.grad, non_blocking=True)
         hdw.copy_(dw, non_blocking=True)
@@ -572,10 +591,13 @@ MLP_TOKENS = 4096
 MLP_D = 4096
 
 
-def run_mlp(args, L, device, warmup, peaks, peak_kind, sm_count) -> int:
+def mlp_line(args, device, warmup, peaks, peak_kind, sm_count, steps=None, no_e2e=None, no_cpu=None) -> dict:
     """SwiGLU MLP forward+backward (config 4: fp16, x [32,128,4096], hidden = the module's default 6912,
-    nn.Linear default init from a seed) through the public module. One JSON line; the roofline entry is
-    the fused projection kernel (tensor-bound), timed in its own loop of launches in the same run."""
+    nn.Linear default init from a seed) through the public module. Returns the JSON line; the roofline entry
+    is the fused projection kernel (tensor-bound), timed in its own loop of launches in the same run."""
+    steps = args.steps if steps is None else steps
+    no_e2e = args.no_e2e if no_e2e is None else no_e2e
+    no_cpu = args.no_cpu if no_cpu is None else no_cpu
     from mgrrmsnorm_b200 import MegaGemmTriton
     from mgrrmsnorm_b200 import rmsnorm_cuda_ops as ops
 
@@ -611,17 +633,17 @@ def run_mlp(args, L, device, warmup, peaks, peak_kind, sm_count) -> int:
 
     sampler = ClockSampler(device.index or 0)
     sampler.start()
-    ms, window = timed(step, args.steps, warmup)
+    ms, window = timed(step, steps, warmup)
     sampler.stop()
     flops = 18 * m * d * f
     xd = x.detach()
     w12 = mlp.w12.weight.detach()
-    k_ms, _ = timed(lambda: ops.swiglu_fused_forward(xd, w12, f), max(args.steps, 20), warmup)
+    k_ms, _ = timed(lambda: ops.swiglu_fused_forward(xd, w12, f), max(min(steps, 50), 20), warmup)
     k_flops = 4 * m * d * f
     peak_tf = float(peaks["bf16_tflops"])
 
     e2e = None
-    if not args.no_e2e:
+    if not no_e2e:
         hx, hdy = xd.cpu().pin_memory(), dy.cpu().pin_memory()
         hy, hdx = torch.empty_like(hx).pin_memory(), torch.empty_like(hx).pin_memory()
 
@@ -639,11 +661,11 @@ def run_mlp(args, L, device, warmup, peaks, peak_kind, sm_count) -> int:
         e2e = {"value": flops / e_ms / 1e9, "unit": "TFLOP/s", "h2d_bytes_per_step": 2 * m * d * 2, "d2h_bytes_per_step": 2 * m * d * 2,
                "ms_per_step": e_ms, "path": "pinned host x, dy -> MegaGemmTriton fwd+bwd -> pinned host y, dx (weight grads stay on the device)"}
     cpu = None
-    if not args.no_cpu:
+    if not no_cpu:
         cpu = time_cpu_mlp(mlp, f)
     reduced = m != MLP_TOKENS
     line = {
-        "metric": "SwiGLU MLP TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s", "n_gpus": 1, "steps": args.steps, "warmup": warmup,
+        "metric": "SwiGLU MLP TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s", "n_gpus": 1, "steps": steps, "warmup": warmup,
         "ms_per_step": ms, "higher_is_better": True, "scaling": "weak", "vs_baseline": None, "dtype": "fp16", "data": "synthetic",
         "config": {"workload": f"SwiGLU MLP fp16 forward+backward, {m} tokens, d_model {d}, hidden {f} (MegaGemmTriton default), "
                                "fused SiLU(gate)*value epilogue" + (" [REDUCED CASE, not the benchmark]" if reduced else ""),
@@ -654,12 +676,17 @@ def run_mlp(args, L, device, warmup, peaks, peak_kind, sm_count) -> int:
                      "achieved": k_flops / k_ms / 1e9, "peak": peak_tf, "unit": "TFLOP/s", "frac": k_flops / k_ms / 1e9 / peak_tf,
                      "peak_source": f"of {peak_kind} (cuBLAS bf16 burst)", "algorithmic_flops_per_launch": k_flops, "avg_launch_ms": k_ms,
                      "timed": "own loop of launches in this run", "traffic": None},
-        "e2e": e2e, "gpu_launches": 7 * args.steps,
+        "frac_of_bf16_sustained_peak": flops / ms / 1e9 / float(peaks["bf16_tflops_sustained"]),
+        "e2e": e2e, "gpu_launches": 6 * steps,
         "clocks": sampler.summary(*window), "sm_count": sm_count,
     }
     if cpu:
         line["cpu_baseline"] = cpu
-    print(json.dumps(line), flush=True)
+    return line
+
+
+def run_mlp(args, L, device, warmup, peaks, peak_kind, sm_count) -> int:
+    print(json.dumps(mlp_line(args, device, warmup, peaks, peak_kind, sm_count)), flush=True)
     return 0
 
 
@@ -668,13 +695,15 @@ BLOCK_D = 8192
 BLOCK_F = 28672
 
 
-def run_block(args, device, warmup, peaks, peak_kind, world, rank) -> int:
+def block_line(args, device, warmup, peaks, peak_kind, world, rank, steps=None):
     """Config 5: bf16 pre-norm MLP block, y = SwiGLU(RMSNorm(x)), d = 8192, d_ff = 28672, 16384 tokens.
     Tensor-parallel over the ranks: w12 split by hidden units (gate and value rows of each rank), w3 by
     columns, x and the norm replicated, one NCCL all-reduce of y in forward and one of dx in backward.
-    Strong scaling: the block is fixed, each GPU does 1/P of the GEMM work. Value = 18*M*D*F / time."""
+    Strong scaling: the block is fixed, each GPU does 1/P of the GEMM work. Value = 18*M*D*F / time.
+    Returns the JSON line on rank 0 and None on the other ranks."""
     import torch.distributed as dist
 
+    steps = args.steps if steps is None else steps
     from mgrrmsnorm_b200 import MegaGemmTriton, RMSNorm, sharding
 
     m, d, f = (args.tokens if args.tokens != MLP_TOKENS else BLOCK_TOKENS), BLOCK_D, BLOCK_F
@@ -729,7 +758,7 @@ def run_block(args, device, warmup, peaks, peak_kind, world, rank) -> int:
     torch.cuda.synchronize()
     t0 = time.perf_counter()
     e0.record(stream)
-    for _ in range(args.steps):
+    for _ in range(steps):
         step()
     e1.record(stream)
     torch.cuda.synchronize()
@@ -743,12 +772,13 @@ def run_block(args, device, warmup, peaks, peak_kind, world, rank) -> int:
         t = torch.tensor([ms], device=device, dtype=torch.float64)
         dist.all_reduce(t, op=dist.ReduceOp.MAX)
         ms = float(t.item())
-    ms /= args.steps
+    ms /= steps
     flops = 18 * m * d * f
+    line = None
     if rank == 0:
         peak_tf = float(peaks["bf16_tflops_sustained"])
         line = {
-            "metric": "Pre-norm MLP block TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s", "n_gpus": world, "steps": args.steps,
+            "metric": "Pre-norm MLP block TFLOP/s", "value": flops / ms / 1e9, "unit": "TFLOP/s", "n_gpus": world, "steps": steps,
             "warmup": warmup, "ms_per_step": ms, "higher_is_better": True, "scaling": "strong", "vs_baseline": None, "dtype": "bf16",
             "data": "synthetic",
             "config": {"workload": f"bf16 pre-norm block RMSNorm({d}) -> SwiGLU(d_ff {f}) over {m} tokens, forward+backward, "
@@ -758,8 +788,16 @@ def run_block(args, device, warmup, peaks, peak_kind, world, rank) -> int:
                        "allreduce_bytes_per_step": 0 if world == 1 else 2 * m * d * 2, "seed": SEED},
             "tflops_per_gpu": flops / ms / 1e9 / world,
             "frac_of_bf16_sustained_peak_per_gpu": flops / ms / 1e9 / world / peak_tf, "peak_source": f"of {peak_kind} (cuBLAS bf16 sustained)",
-            "gpu_launches": 8 * args.steps, "clocks": sampler.summary(t0, t1) if sampler else None,
+            "gpu_launches": 8 * steps, "clocks": sampler.summary(t0, t1) if sampler else None,
         }
+    return line
+
+
+def run_block(args, device, warmup, peaks, peak_kind, world, rank) -> int:
+    import torch.distributed as dist
+
+    line = block_line(args, device, warmup, peaks, peak_kind, world, rank)
+    if line is not None:
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()
@@ -864,6 +902,165 @@ def time_cpu_mlp(mlp, f) -> dict:
             "sample": f"PyTorchSwiGLU formula fwd+bwd in fp32 on {m} of the {MLP_TOKENS} tokens, {len(times)} steps"}
 
 
+
+# ---------------------------------------------------------------------------------------------------
+# compact side records of the default run
+# ---------------------------------------------------------------------------------------------------
+
+def allreduce_cost(buf, steps, warmup, world, job_bytes, side_run) -> dict:
+    """What the latency-bound dW collective costs: the same resident loop with the fp32 all-reduce and the
+    rounding on the COMPUTE stream (fully exposed), against the default (side stream, beside the next forward);
+    and the collective alone, back to back on one stream."""
+    import torch.distributed as dist
+
+    inline = time_device_resident([buf], steps, warmup, world, reduce="inline")
+    t = torch.zeros(HIDDEN, dtype=torch.float32, device=buf.x.device)
+    for _ in range(10):
+        dist.all_reduce(t)
+    e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+    n = 200
+    dist.barrier()
+    torch.cuda.synchronize()
+    e0.record()
+    for _ in range(n):
+        dist.all_reduce(t)
+    e1.record()
+    torch.cuda.synchronize()
+    alone_us = e0.elapsed_time(e1) * 1e3 / n
+    ms_inline = inline["total_ms"] / steps
+    ms_side = side_run["total_ms"] / steps
+    return {"bytes": HIDDEN * 4, "alone_us": alone_us, "on_compute_stream": {"ms_per_step": ms_inline, "value": job_bytes / ms_inline / 1e6},
+            "beside_next_forward": {"ms_per_step": ms_side, "value": job_bytes / ms_side / 1e6},
+            "exposed_us_per_step": (ms_inline - ms_side) * 1e3,
+            "note": "32 KB fp32 all-reduce per step: far below any bandwidth regime, so NCCL runs it as a single-step low-latency "
+                    "(LL protocol) exchange and its cost is launch + NVLink round-trip latency, not bytes"}
+
+
+def weak_scaling_figure(L, device, rank, world, warmup) -> dict:
+    """The same loop with 65536 rows on EVERY GPU (per-GPU work fixed as N grows)."""
+    buf = RmsBuffers(L, ROWS_PER_GPU, HIDDEN, torch.bfloat16, device, SEED + rank, x_scale=2.0 ** 0.5)
+    steps = 40
+    r = time_device_resident([buf], steps, warmup, world)
+    ms = r["total_ms"] / steps
+    out = {"scaling": "weak", "rows_per_gpu": ROWS_PER_GPU, "steps": steps, "ms_per_step": ms,
+           "value": world * rms_bytes(ROWS_PER_GPU, HIDDEN, 2)["total"] / ms / 1e6, "unit": UNIT}
+    del buf
+    torch.cuda.empty_cache()
+    return out
+
+
+def mlp_compact(args, device, peaks, peak_kind, sm_count) -> dict:
+    """Config 4 (fp16 SwiGLU MLP, 1 GPU) in two regimes: a 100-step run, long enough for the 1 kW power cap to
+    set the clock, and a 20-step burst near the maximum clock; each with its own clock sample."""
+    out = {}
+    for name, steps in (("sustained_100_steps", 100), ("burst_20_steps", 20)):
+        ln = mlp_line(args, device, 5, peaks, peak_kind, sm_count, steps=steps, no_e2e=True, no_cpu=True)
+        out[name] = {"ms_per_step": ln["ms_per_step"], "TFLOPs": ln["value"], "frac_of_bf16_burst_peak": ln["frac_of_bf16_peak"],
+                     "frac_of_bf16_sustained_peak": ln["frac_of_bf16_sustained_peak"], "clocks": ln["clocks"],
+                     "fused_projection_kernel": {"TFLOPs": ln["roofline"]["achieved"], "frac_of_burst_peak": ln["roofline"]["frac"]}}
+        torch.cuda.empty_cache()
+    out["config"] = ln["config"]["workload"]
+    out["peak_source"] = f"of {peak_kind} (cuBLAS bf16: burst {peaks['bf16_tflops']}, sustained {peaks['bf16_tflops_sustained']} TFLOP/s)"
+    return out
+
+
+def block_compact(args, device, peaks, peak_kind, world, rank):
+    """Config 5 (bf16 pre-norm block, tensor-parallel over the ranks of this run): 3 warm-up + 8 timed steps."""
+    ln = block_line(args, device, 3, peaks, peak_kind, world, rank, steps=8)
+    torch.cuda.empty_cache()
+    if ln is None:
+        return None
+    return {"metric": ln["metric"], "value": ln["value"], "unit": ln["unit"], "ms_per_step": ln["ms_per_step"], "steps": ln["steps"],
+            "scaling": "strong", "tflops_per_gpu": ln["tflops_per_gpu"],
+            "frac_of_bf16_sustained_peak_per_gpu": ln["frac_of_bf16_sustained_peak_per_gpu"], "peak_source": ln["peak_source"],
+            "allreduce_bytes_per_step": ln["config"]["allreduce_bytes_per_step"], "d_ff_per_gpu": ln["config"]["d_ff_per_gpu"],
+            "workload": ln["config"]["workload"], "clocks": ln["clocks"]}
+
+
+def parity_check(device, world, rank) -> dict:
+    """Sharded results against the one-rank result of the same library on the same seeded inputs, computed on the
+    spot on every rank: row-sharded RMSNorm (y, dx bit-equal; dW = fp32 sum across ranks, one rounding, within one
+    bf16 ulp of the one-rank dW), the side-stream all-reduce against the synchronous one (same bits), and the
+    tensor-parallel MLP against the full MLP. Reduced to booleans and worst errors; `ok` is the AND over all ranks."""
+    import torch.distributed as dist
+
+    from mgrrmsnorm_b200 import MegaGemmTriton, RMSNorm, sharding
+    from mgrrmsnorm_b200 import rmsnorm_cuda_ops as ops
+
+    dt = torch.bfloat16
+    g = torch.Generator().manual_seed(SEED)
+    rows, cols = 4096, HIDDEN
+    x = (2 ** 0.5 * torch.randn(rows, cols, generator=g)).to(dt).to(device)
+    w = (1 + 0.1 * torch.randn(cols, generator=g)).to(dt).to(device)
+    dy = torch.randn(rows, cols, generator=g).to(dt).to(device)
+    full = RMSNorm(cols, epsilon=EPS).to(device).to(dt)
+    shard = sharding.RowShardedRMSNorm(cols, epsilon=EPS).to(device).to(dt)
+    with torch.no_grad():
+        full.weight.copy_(w)
+        shard.weight.copy_(w)
+    xf = x.clone().requires_grad_(True)
+    yf = full(xf)
+    yf.backward(dy)
+    r0, r1 = sharding.row_shard(rows, world, rank)
+    xs = x[r0:r1].clone().requires_grad_(True)
+    ys = shard(xs)
+    ys.backward(dy[r0:r1])
+    rows_equal = bool(torch.equal(ys, yf[r0:r1]) and torch.equal(xs.grad, xf.grad[r0:r1]))
+    dws, dwf = shard.weight.grad.float(), full.weight.grad.float()
+    ulp = torch.maximum(dws.abs(), dwf.abs()) * 2.0 ** -7 + 1e-4     # one bf16 ulp (+ a floor for columns that cancel)
+    dw_ulps = float(((dws - dwf).abs() / ulp).max())
+    dw_differ = float((dws != dwf).float().mean())
+    _, inv = ops.rmsnorm_forward(xs.detach(), shard.weight.detach(), EPS)
+    red = sharding.AsyncDwReduce(device)
+    _, _, dw32 = ops.rmsnorm_backward_full(dy[r0:r1].contiguous(), xs.detach(), shard.weight.detach(), inv, True)
+    dw_async = torch.empty_like(shard.weight)
+    red.start(dw32, dw_async)
+    red.drain()
+    torch.cuda.synchronize()
+    async_equal = bool(torch.equal(dw_async, shard.weight.grad))
+
+    torch.manual_seed(SEED)
+    mlp = MegaGemmTriton(1024, multiple_of=256, hidden_multiple=2.0).to(device).to(dt)     # hidden 2048: divides by 2, 4, 8
+    for p_ in mlp.parameters():
+        dist.broadcast(p_.data, src=0)
+    tp = sharding.TensorParallelSwiGLU.from_full(mlp, world, rank)
+    xm = torch.randn(512, 1024, generator=g).to(dt).to(device)
+    dym = torch.randn(512, 1024, generator=g).to(dt).to(device)
+    a = xm.clone().requires_grad_(True)
+    ya = mlp(a)
+    ya.backward(dym)
+    b = xm.clone().requires_grad_(True)
+    yb = tp(b)
+    yb.backward(dym)
+    f0, f1 = sharding.tp_hidden_slice(mlp.hidden, world, rank)
+    gw12 = torch.cat([mlp.w12.weight.grad[f0:f1], mlp.w12.weight.grad[mlp.hidden + f0:mlp.hidden + f1]])
+
+    def rel(got, want):
+        return float((got.float() - want.float()).abs().max()) / max(float(want.float().abs().max()), 1e-6)
+
+    errs = {"y": rel(yb, ya), "dx": rel(b.grad, a.grad), "dw12": rel(tp.local.w12.weight.grad, gw12),
+            "dw3": rel(tp.local.w3.weight.grad, mlp.w3.weight.grad[:, f0:f1])}
+    torch.cuda.synchronize()
+    status = int(_capi_status())
+    ok = rows_equal and async_equal and dw_ulps <= 1.0 and dw_differ < 0.05 and max(errs.values()) < 2e-2 and status == 0
+    flag = torch.tensor([1.0 if ok else 0.0, dw_ulps, max(errs.values())], device=device)
+    lo = flag.clone()
+    dist.all_reduce(lo, op=dist.ReduceOp.MIN)
+    dist.all_reduce(flag, op=dist.ReduceOp.MAX)
+    return {"ok": bool(lo[0].item() == 1.0), "ranks": world,
+            "rmsnorm": {"rows": rows, "hidden": cols, "y_dx_bit_equal_to_one_rank": rows_equal, "dw_max_bf16_ulps_from_one_rank": float(flag[1].item()),
+                        "dw_columns_differing": dw_differ, "async_allreduce_bit_equal_to_sync": async_equal},
+            "tp_mlp": {"tokens": 512, "d_model": 1024, "hidden": mlp.hidden, "max_rel_err_over_ranks": float(flag[2].item()),
+                       "rank0_rel_err": errs, "tolerance": 2e-2},
+            "device_status": status}
+
+
+def _capi_status() -> int:
+    from mgrrmsnorm_b200 import _capi
+
+    return _capi.lib().mgr_device_status(1)
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
@@ -874,8 +1071,8 @@ def main(argv=None) -> int:
     ap.add_argument("--no-side", action="store_true", help="skip the other configurations (N=1 extras)")
     ap.add_argument("--no-cpu", action="store_true", help="skip the timed CPU baseline")
     ap.add_argument("--no-e2e", action="store_true", help="skip the host-buffer end-to-end leg (profiling runs)")
-    ap.add_argument("--rows", type=int, default=ROWS_PER_GPU,
-                    help="rows per GPU; anything but the default is a reduced case for profiler captures, not a bench value")
+    ap.add_argument("--rows", type=int, default=TOTAL_ROWS,
+                    help="rows in total (split over the ranks); anything but the default is a reduced case for profiler captures, not a bench value")
     ap.add_argument("--workload", choices=["rmsnorm", "mlp", "block", "decode"], default="rmsnorm",
                     help="rmsnorm (default, the headline); mlp: SwiGLU MLP fp16 d_model 4096 hidden 6912 forward+backward, 1 GPU; "
                          "block: bf16 pre-norm block RMSNorm(8192) -> SwiGLU(d_ff 28672) over 16384 tokens, tensor-parallel over --gpus; "
@@ -924,42 +1121,69 @@ def main(argv=None) -> int:
             return 2
         return run_decode(args, device, warmup, peaks, peak_kind)
 
-    main_buf = RmsBuffers(L, args.rows, HIDDEN, torch.bfloat16, device, SEED + rank, x_scale=2.0 ** 0.5)
+    from mgrrmsnorm_b200 import sharding
+
+    r0, r1 = sharding.row_shard(args.rows, world, rank)
+    local_rows = r1 - r0
+    main_buf = RmsBuffers(L, local_rows, HIDDEN, torch.bfloat16, device, SEED + rank, x_scale=2.0 ** 0.5)
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
     r = time_device_resident([main_buf], args.steps, warmup, world)
     if sampler:
         sampler.stop()
-    nb = rms_bytes(args.rows, HIDDEN, 2)
+    nb = rms_bytes(local_rows, HIDDEN, 2)                 # this rank (rank 0 holds a largest block)
+    job_bytes = sum(rms_bytes(b - a, HIDDEN, 2)["total"] for a, b in (sharding.row_shard(args.rows, world, i) for i in range(world)))
     ms_per_step = r["total_ms"] / args.steps
-    value = world * nb["total"] / (ms_per_step * 1e-3) / 1e9
+    value = job_bytes / (ms_per_step * 1e-3) / 1e9
+
+    extras = {}
+
+    def guarded(name, fn):
+        """Side measurements must not take the headline down: an exception becomes a recorded error string.
+        (Every rank takes the same path, so a failure on all ranks leaves the collectives in step.)"""
+        try:
+            out = fn()
+            if out is not None:
+                extras[name] = out
+        except Exception as e:  # noqa: BLE001
+            extras[name] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
+
+    if world > 1:
+        guarded("allreduce", lambda: allreduce_cost(main_buf, args.steps, warmup, world, job_bytes, r))
 
     e2e = None
     if not args.no_e2e:
-        e2e = time_e2e(args.rows, HIDDEN, device, args.e2e_steps, 1, world, main_buf, pipelined=True)
-        e2e_value = world * nb["total"] / (e2e["ms_per_step"] * 1e-3) / 1e9
-        e2e_plain = time_e2e(args.rows, HIDDEN, device, args.e2e_steps, 1, world, main_buf, pipelined=False)
-        e2e["unpipelined_value"] = world * nb["total"] / (e2e_plain["ms_per_step"] * 1e-3) / 1e9
+        e2e = time_e2e(local_rows, HIDDEN, device, args.e2e_steps, 1, world, main_buf, pipelined=True)
+        e2e_value = job_bytes / (e2e["ms_per_step"] * 1e-3) / 1e9
+        e2e_plain = time_e2e(local_rows, HIDDEN, device, args.e2e_steps, 1, world, main_buf, pipelined=False)
+        e2e["unpipelined_value"] = job_bytes / (e2e_plain["ms_per_step"] * 1e-3) / 1e9
 
+    del main_buf
+    torch.cuda.empty_cache()
+    if world > 1 and not args.no_side:
+        guarded("weak", lambda: weak_scaling_figure(L, device, rank, world, warmup))
+        guarded("parity_n", lambda: parity_check(device, world, rank))
     side = {}
     if world == 1 and not args.no_side:
-        del main_buf
-        torch.cuda.empty_cache()
         side = side_results(L, device, peak_gbs)
+        guarded("mlp", lambda: mlp_compact(args, device, peaks, peak_kind, sms.value))
+    if not args.no_side:
+        guarded("block", lambda: block_compact(args, device, peaks, peak_kind, world, rank))
     cpu = None
     if world == 1 and rank == 0 and not args.no_cpu:
         cpu = time_cpu(steps=40, warmup=1, budget_s=15.0)
+    status = L.mgr_device_status(1)       # the host is idle here: did any kernel give up a bounded wait?
 
     if rank == 0:
         bwd_gbs = nb["bwd"] / (r["bwd_ms"] * 1e-3) / 1e9
         fwd_gbs = nb["fwd"] / (r["fwd_ms"] * 1e-3) / 1e9
         line = {
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
-            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "weak", "vs_baseline": None,
+            "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(world, args.rows),
             "frac_of_hbm_peak": value / world / peak_gbs,
-            "roofline": {"bound": "hbm", "kernel": "rms_bwd_reg + rms_dw_reduce (one mgr_rmsnorm_bwd call)",
+            "roofline": {"bound": "hbm", "kernel": "rms_bwd_reg (one mgr_rmsnorm_bwd call: dx, and the dW column sum after a grid-wide barrier in the same launch)",
                          "achieved": bwd_gbs, "peak": peak_gbs, "unit": "GB/s", "frac": bwd_gbs / peak_gbs,
                          "peak_source": f"of {peak_kind}",
                          "algorithmic_bytes_per_launch": nb["bwd"], "avg_launch_ms": r["bwd_ms"],
@@ -967,19 +1191,27 @@ def main(argv=None) -> int:
             "roofline_fwd": {"bound": "hbm", "kernel": "rms_fwd_reg", "achieved": fwd_gbs, "peak": peak_gbs, "unit": "GB/s",
                              "frac": fwd_gbs / peak_gbs, "algorithmic_bytes_per_launch": nb["fwd"], "avg_launch_ms": r["fwd_ms"]},
             "e2e": None if e2e is None else {
-                "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                "value": e2e_value, "unit": UNIT, "h2d_bytes_per_step": e2e["h2d"] * world, "d2h_bytes_per_step": e2e["d2h"] * world,
                 "ms_per_step": e2e["ms_per_step"], "steps": e2e["steps"],
-                "path": "pinned host x, dy -> HostRMSNormPipeline (32 MiB row chunks, copy-in / compute / copy-out streams) -> pinned host y, dx, dW",
+                "per_gpu": {"h2d_bytes_per_step": e2e["h2d"], "d2h_bytes_per_step": e2e["d2h"],
+                            "h2d_GBps": e2e["h2d"] / e2e["ms_per_step"] / 1e6, "d2h_GBps": e2e["d2h"] / e2e["ms_per_step"] / 1e6},
+                "bound": "the host side: every step moves each rank's x, dy in and y, dx out over its PCIe link, both directions at once; "
+                         "the kernels need under 2 % of the step. With several ranks on one host the links share the host's memory "
+                         "and root-complex bandwidth (all pinned buffers of this process tree come from the same host DRAM), so the "
+                         "per-GPU rate falls as ranks are added; no collective is involved beyond the 32 KB dW all-reduce",
+                "path": "pinned host x, dy -> HostRMSNormPipeline (32 MiB row chunks, copy-in / compute / copy-out streams) -> pinned host y, dx; "
+                        "dW: fp32 sum all-reduced across ranks, rounded once, copied to pinned host memory",
                 "unpipelined_value": e2e["unpipelined_value"],
                 "unpipelined_path": "pinned host -> whole-tensor copies around the RMSNorm module fwd+bwd -> pinned host"},
-            "gpu_launches": 3 * args.steps,
+            "gpu_launches": 2 * args.steps, "launches_per_step": {"mgr_rmsnorm_fwd": 1, "mgr_rmsnorm_bwd": 1},
             "clocks": sampler.summary(*r["window"]) if sampler else None,
-            "sm_count": sms.value,
+            "sm_count": sms.value, "device_status": status,
         }
         if cpu:
             line["cpu_baseline"] = {k: cpu[k] for k in ("value", "unit", "cores", "kind", "sample")}
         if side:
             line["also"] = side
+        line.update(extras)           # compact keys last: block, mlp (N = 1), weak / allreduce / parity_n (N > 1)
         print(json.dumps(line), flush=True)
     if world > 1:
         dist.destroy_process_group()

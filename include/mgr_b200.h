@@ -64,6 +64,13 @@ int mgr_abi_version(void);
  * (src/rmsnorm_kernel.cu:534,538,546). Host pointer; never NULL. */
 const char* mgr_status_str(int status);
 
+/* Re-reads the MGR_* environment variables that pin kernel choices for measurements and tests
+ * (MGR_RMSNORM_PATH, MGR_RMSNORM_FWD_SHAPE, MGR_RMSNORM_BWD_SHAPE, MGR_RMSNORM_BWD_FAT, MGR_GEMM_CTA_GROUP,
+ * MGR_GEMM_PDL, MGR_GEMM_NARROW). The library reads them once, at its first launch, so that no call pays
+ * for getenv; a process that changes them afterwards calls this. No reference counterpart (the reference
+ * has no environment switches). */
+void mgr_reload_env(void);
+
 /* Number of SMs of the current device and whether it can run this library (compute capability 10.x).
  * Returns MGR_OK or MGR_ERR_UNSUPPORTED_ARCH / MGR_ERR_CUDA; *sm_count (host pointer, may be NULL)
  * receives the SM count. No reference counterpart (the reference never asks the device). */
@@ -76,6 +83,13 @@ int mgr_device_check(int* sm_count);
  * reference's kernels have no device-side waits and its wrappers only see launch errors
  * (src/rmsnorm_kernel.cu:544-548). */
 int mgr_device_status(int clear);
+
+/* Test hook: writes `value` into the status word that the kernels of one family set when a bounded wait runs
+ * out (family 0: the RMSNorm bulk-copy ring kernels; 1: the tensor-core GEMM kernels), from the host, with a
+ * plain copy to the device. It lets a host test walk the path "a kernel gave up -> mgr_device_status reports
+ * MGR_ERR_DEVICE_TIMEOUT once -> cleared" without making any kernel wait. Synchronises like mgr_device_status.
+ * No reference counterpart. */
+int mgr_debug_poke_device_status(int family, int value);
 
 /* ------------------------------------------------------------------------------------------------
  * RMSNorm forward.   y[r,j] = round_dtype((x[r,j] * inv[r]) * w[j]),  inv[r] = 1/sqrt(mean_j x[r,j]^2 + eps)

@@ -36,8 +36,10 @@ _sz = ctypes.c_size_t
 SIGNATURES = {
     "mgr_abi_version": (_int, []),
     "mgr_status_str": (ctypes.c_char_p, [_int]),
+    "mgr_reload_env": (None, []),
     "mgr_device_check": (_int, [ctypes.POINTER(_int)]),
     "mgr_device_status": (_int, [_int]),
+    "mgr_debug_poke_device_status": (_int, [_int, _int]),
     "mgr_rmsnorm_fwd": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _int, _vp]),
     "mgr_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "mgr_rmsnorm_bwd": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _sz, _vp]),
@@ -93,6 +95,11 @@ def lib() -> ctypes.CDLL:
         fn.argtypes = args
     _lib = L
     return L
+
+
+def reload_env() -> None:
+    """Makes the library read the MGR_* environment overrides again (it reads them once, at first use)."""
+    lib().mgr_reload_env()
 
 
 def status_str(status: int) -> str:

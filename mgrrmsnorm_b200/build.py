@@ -5,7 +5,11 @@ loaded by ctypes. It replaces the reference's `CUDAExtension('rmsnorm_cuda_ops',
 (setup.py:23-42): one architecture (sm_100a), no Triton, no multi-backend dispatch, no CPU fallback,
 and no `--use_fast_math` (the kernels are memory-bound; IEEE sqrt/divide cost nothing).
 
-Usage:  python -m mgrrmsnorm_b200.build [--force] [--verbose]
+`build_binding()` then compiles pytorch_binding/binding.cpp into the torch extension
+mgrrmsnorm_b200/pybind/rmsnorm_cuda_ops*.so by running the repository's setup.py (torch's BuildExtension,
+ninja), the route `pip install -e .` takes as well.
+
+Usage:  python -m mgrrmsnorm_b200.build [--force] [--verbose] [--binding]
 """
 from __future__ import annotations
 
@@ -89,12 +93,43 @@ def build(force: bool = False, verbose: bool = False) -> Path:
     return LIB_PATH
 
 
+ROOT = PKG_DIR.parent
+BINDING_SRC = ROOT / "pytorch_binding" / "binding.cpp"
+BINDING_DIR = PKG_DIR / "pybind"
+
+
+def binding_path() -> Path | None:
+    hits = sorted(BINDING_DIR.glob("rmsnorm_cuda_ops*.so"))
+    return hits[0] if hits else None
+
+
+def build_binding(force: bool = False) -> Path:
+    """Compiles the torch extension (after the kernel library it links against). Returns its path."""
+    build()
+    h = hashlib.sha256()
+    for f in (BINDING_SRC, ROOT / "setup.py", *sorted(INCLUDE.glob("*.h"))):
+        h.update(f.read_bytes())
+    fp = h.hexdigest()
+    stamp = BINDING_DIR / "rmsnorm_cuda_ops.sha"
+    have = binding_path()
+    if not force and have is not None and stamp.exists() and stamp.read_text() == fp:
+        return have
+    proc = subprocess.run([sys.executable, "setup.py", "-q", "build_ext", "--inplace"], cwd=str(ROOT), capture_output=True, text=True)
+    if proc.returncode != 0 or binding_path() is None:
+        raise RuntimeError(f"building pytorch_binding/binding.cpp failed:\n{proc.stdout[-4000:]}\n{proc.stderr[-4000:]}")
+    stamp.write_text(fp)
+    return binding_path()
+
+
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__)
     ap.add_argument("--force", action="store_true", help="recompile even if sources are unchanged")
     ap.add_argument("--verbose", action="store_true", help="print ptxas register/shared-memory reports")
+    ap.add_argument("--binding", action="store_true", help="also build the torch extension from pytorch_binding/binding.cpp")
     args = ap.parse_args(argv)
     print(build(force=args.force, verbose=args.verbose))
+    if args.binding:
+        print(build_binding(force=args.force))
     return 0
 
 

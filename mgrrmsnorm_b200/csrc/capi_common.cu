@@ -2,10 +2,57 @@
 // device probe.
 
 #include <atomic>
+#include <cstdlib>
+#include <cstring>
 
 #include "mgr_common.cuh"
 
 namespace mgr {
+
+namespace {
+std::atomic<bool> g_env_loaded{false};
+std::atomic<int> g_env[7];
+
+void load_env() {
+    auto num = [](const char* name, int unset) {
+        const char* e = std::getenv(name);
+        return (e == nullptr || e[0] == '\0') ? unset : std::atoi(e);
+    };
+    int path = 0;
+    if (const char* e = std::getenv("MGR_RMSNORM_PATH")) {
+        if (std::strcmp(e, "reg") == 0) path = 1;
+        else if (std::strcmp(e, "ring") == 0) path = 2;
+        else if (std::strcmp(e, "scalar") == 0) path = 3;
+    }
+    int cg = 0;
+    if (const char* e = std::getenv("MGR_GEMM_CTA_GROUP")) cg = e[0] == '2' ? 2 : (e[0] == '1' ? 1 : 0);
+    int pdl = 1;
+    if (const char* e = std::getenv("MGR_GEMM_PDL")) pdl = e[0] != '0';
+    int narrow = -1;
+    if (const char* e = std::getenv("MGR_GEMM_NARROW")) narrow = e[0] == '0' ? 0 : (e[0] == '3' ? 32 : 64);
+    g_env[0].store(path, std::memory_order_relaxed);
+    g_env[1].store(num("MGR_RMSNORM_FWD_SHAPE", -1), std::memory_order_relaxed);
+    g_env[2].store(num("MGR_RMSNORM_BWD_SHAPE", -1), std::memory_order_relaxed);
+    g_env[3].store(num("MGR_RMSNORM_BWD_FAT", -1), std::memory_order_relaxed);
+    g_env[4].store(cg, std::memory_order_relaxed);
+    g_env[5].store(pdl, std::memory_order_relaxed);
+    g_env[6].store(narrow, std::memory_order_relaxed);
+    g_env_loaded.store(true, std::memory_order_release);
+}
+}  // namespace
+
+Overrides overrides() {
+    if (!g_env_loaded.load(std::memory_order_acquire)) load_env();   // racing first calls read the same environment
+    Overrides o;
+    o.rms_path = g_env[0].load(std::memory_order_relaxed);
+    o.fwd_shape = g_env[1].load(std::memory_order_relaxed);
+    o.bwd_shape = g_env[2].load(std::memory_order_relaxed);
+    o.bwd_fat = g_env[3].load(std::memory_order_relaxed);
+    o.cta_group = g_env[4].load(std::memory_order_relaxed);
+    o.pdl = g_env[5].load(std::memory_order_relaxed);
+    o.narrow = g_env[6].load(std::memory_order_relaxed);
+    return o;
+}
 
 DeviceInfo current_device_info() {
     // Filled once per device; `known` is published with release order after the entry is complete, so a thread
@@ -35,6 +82,8 @@ DeviceInfo current_device_info() {
 
 int rmsnorm_status_fetch(int clear);  // rmsnorm_sm100.cu
 int gemm_status_fetch(int clear);     // gemm_sm100.cu
+int rmsnorm_status_poke(int value);   // rmsnorm_sm100.cu
+int gemm_status_poke(int value);      // gemm_sm100.cu
 
 }  // namespace mgr
 
@@ -45,6 +94,16 @@ extern "C" int mgr_device_status(int clear) {
     const int b = mgr::gemm_status_fetch(clear);
     return a != MGR_OK ? a : b;
 }
+
+extern "C" int mgr_debug_poke_device_status(int family, int value) {
+    const mgr::DeviceInfo di = mgr::current_device_info();
+    if (di.status != MGR_OK) return di.status;
+    if (family == 0) return mgr::rmsnorm_status_poke(value);
+    if (family == 1) return mgr::gemm_status_poke(value);
+    return MGR_ERR_BAD_SHAPE;
+}
+
+extern "C" void mgr_reload_env(void) { mgr::load_env(); }
 
 extern "C" int mgr_abi_version(void) { return MGR_ABI_VERSION; }
 

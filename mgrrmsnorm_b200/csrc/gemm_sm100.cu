@@ -703,22 +703,14 @@ struct GemmArgs {
 std::atomic<int> g_sm_limit{0};
 
 // MGR_GEMM_CTA_GROUP=1|2 pins the single-CTA or the CTA-pair kernels; unset = automatic.
-int forced_cta_group() {
-    const char* e = std::getenv("MGR_GEMM_CTA_GROUP");
-    if (e == nullptr) return 0;
-    return e[0] == '2' ? 2 : (e[0] == '1' ? 1 : 0);
-}
+int forced_cta_group() { return overrides().cta_group; }
 
 // GEMM kernels are launched with programmatic stream serialization: the prologue (barriers, tensor memory,
 // descriptor prefetch) of a GEMM overlaps the tail of the kernel before it in the stream (1-2.5 us per launch in a
 // chain of short GEMMs). Not while an SM limit is set: the early CTAs of the next GEMM would park on the SMs that
 // the limit keeps free for a collective. MGR_GEMM_PDL=0 switches it off.
 bool pdl_enabled() {
-    static const bool on = [] {
-        const char* e = std::getenv("MGR_GEMM_PDL");
-        return e == nullptr || e[0] != '0';
-    }();
-    return on && g_sm_limit.load(std::memory_order_relaxed) == 0;
+    return overrides().pdl != 0 && g_sm_limit.load(std::memory_order_relaxed) == 0;
 }
 
 template <int EPI, bool A_MN, bool B_MN, int CG, typename T, int BN = kBN>
@@ -811,9 +803,9 @@ int launch_gemm_cg(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
         // Measured on B200 (fp16, D 4096, F 6912, CUDA graphs): the w3 GEMM of a 16-row batch has 16 / 64 / 128
         // tiles at 256 / 64 / 32 columns and takes 32 / 18 / 16 us; the fused projection (54 / 216 / 432 tiles)
         // 36 / 26 / 27 us. So: 32 columns only while 64 would still leave half the SMs idle.
-        const char* e = std::getenv("MGR_GEMM_NARROW");
+        const int pinned = overrides().narrow;
         int bn = 0;
-        if (e != nullptr) bn = e[0] == '0' ? 0 : (e[0] == '3' ? kBNTiny : kBNSmall);
+        if (pinned >= 0) bn = pinned == 0 ? 0 : (pinned == 32 ? kBNTiny : kBNSmall);
         // Up to 384 rows only: from 4 row tiles on, every narrow tile re-reads its 128 rows of A and the wide
         // tiling wins again (w3 GEMM at 512 rows: 37.9 us wide against 42.3 us narrow; at 256 rows 36.6 against 21.8).
         else if (wide_tiles * 2 <= di.sm_count && m_tiles <= 3) bn = small_tiles * 2 <= di.sm_count ? kBNTiny : kBNSmall;
@@ -860,6 +852,10 @@ int gemm_status_fetch(int clear) {
         if (cudaMemcpyToSymbol(g_gemm_status, &zero, sizeof(int)) != cudaSuccess) (void)cudaGetLastError();
     }
     return v;
+}
+
+int gemm_status_poke(int value) {
+    return cudaMemcpyToSymbol(g_gemm_status, &value, sizeof(int)) == cudaSuccess ? MGR_OK : ((void)cudaGetLastError(), MGR_ERR_CUDA);
 }
 
 }  // namespace mgr

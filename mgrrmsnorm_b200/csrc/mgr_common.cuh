@@ -24,6 +24,22 @@ struct DeviceInfo {
 // concurrent first calls compute the same values).
 DeviceInfo current_device_info();
 
+// Measurement and test overrides read from the environment ONCE per process (first use) and again only when
+// mgr_reload_env() is called, so that no launch pays for getenv:
+//   MGR_RMSNORM_PATH=reg|ring|scalar   kernel family            MGR_RMSNORM_FWD_SHAPE / _BWD_SHAPE=<index>  packet shape
+//   MGR_RMSNORM_BWD_FAT=0|1            backward packet kernel: one CTA per row group / one fat CTA per SM, for every shape
+//   MGR_GEMM_CTA_GROUP=1|2             MGR_GEMM_PDL=0           MGR_GEMM_NARROW=0|1|32
+struct Overrides {
+    int rms_path;    // 0 automatic, 1 reg, 2 ring, 3 scalar
+    int fwd_shape;   // -1 unset
+    int bwd_shape;   // -1 unset
+    int bwd_fat;     // -1 per packet shape (the table's choice), 0 never, 1 always
+    int cta_group;   // 0 automatic, 1, 2
+    int pdl;         // 0 off, 1 on
+    int narrow;      // -1 automatic, 0 never, 64, 32
+};
+Overrides overrides();
+
 inline size_t dtype_size(int dtype) {
     switch (dtype) {
         case MGR_F32: return 4;

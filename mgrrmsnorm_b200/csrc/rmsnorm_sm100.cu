@@ -13,8 +13,6 @@
 // aligned, rows longer than 4096 packets) go to scalar kernels with the same arithmetic.
 
 #include <atomic>
-#include <cstdlib>
-#include <cstring>
 
 #include "mgr_common.cuh"
 #include "rmsnorm_ring.cuh"
@@ -325,6 +323,298 @@ rms_bwd_reg(T* dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __
     }
 }
 
+// Geometry of the backward kernel. One FAT CTA per SM where the register budget allows it: G = kGroups row groups
+// of TPR threads each run their own rows independently (they meet only on their own named barrier), and are
+// folded in shared memory at the end, so a CTA writes ONE partial row of dW however many rows it had in flight.
+// (With one small CTA per row group the same SM wrote 2-6 partial rows; the column sum that follows reads them all.)
+// kBudget = resident threads per SM the register allocation is held to: 128 registers per thread in general, 64
+// (40) where a thread holds at most two (one) packets of a row.
+constexpr int bwd_budget(int tpr, int vpt) { return (vpt <= 2 && tpr >= 160) ? (vpt == 1 ? 1536 : 1024) : 512; }
+constexpr int bwd_groups(int tpr, int vpt) {
+    const int budget = bwd_budget(tpr, vpt);
+    const int max_block = budget < 1024 ? budget : 1024;
+    if (tpr >= max_block) return 1;
+    for (int g = max_block / tpr; g >= 1; --g)
+        if (budget % (g * tpr) == 0) return g;       // whole CTAs fill the budget
+    return max_block / tpr;
+}
+
+template <int TPR, int VPT>
+struct BwdGeom {
+    static constexpr int kGroups = bwd_groups(TPR, VPT);
+    static constexpr int kBlock = kGroups * TPR;
+    static constexpr int kMinBlocks = bwd_budget(TPR, VPT) / kBlock < 1 ? 1 : bwd_budget(TPR, VPT) / kBlock;
+    static constexpr int kWarpsPerRow = TPR / 32;
+    static constexpr int kWarps = kBlock / 32;
+    static constexpr int kFoldRows = kGroups / 2;    // partial rows parked in shared memory during the fold
+};
+
+// Sum of `v` over the TPR threads of one row group. `red` is this group's own [2][TPR/32] slice of shared memory,
+// used alternately; the group meets on ITS named barrier (id group + 1), so other groups of the CTA are not held up.
+template <int TPR>
+__device__ __forceinline__ float group_sum(float v, float* red_all, int& buf, int group) {
+    v = warp_sum(v);
+    if constexpr (TPR > 32) {
+        constexpr int WPR = TPR / 32;
+        float* red = red_all + (group * 2 + buf) * WPR;
+        if ((threadIdx.x & 31) == 0) red[(threadIdx.x >> 5) - group * WPR] = v;
+        asm volatile("bar.sync %0, %1;" ::"r"(group + 1), "n"(TPR) : "memory");
+        float s = 0.f;
+#pragma unroll
+        for (int i = 0; i < WPR; ++i) s += red[i];
+        buf ^= 1;
+        v = s;
+    }
+    return v;
+}
+
+// Backward. Each thread owns the same VPT*VEC columns for every row its group visits, so the dW partial sums
+// stay in registers until the CTA is done; the G groups are then folded pairwise in shared memory (distance 1,
+// 2, 4, ...: a fixed tree) and the CTA writes ONE fp32 partial row ws[blockIdx.x, :].
+// ADD: dx = round_T(dx_norm + dres), the gradient that arrives along the residual stream folded into the
+// same store (one rounding). dx may be the buffer of dres.
+template <typename T, int TPR, int VPT, bool ADD = false>
+__global__ void __launch_bounds__(BwdGeom<TPR, VPT>::kBlock, BwdGeom<TPR, VPT>::kMinBlocks)
+rms_bwd_fat(T* dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
+            const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int cols, const T* dres = nullptr) {
+    using Geo = BwdGeom<TPR, VPT>;
+    constexpr int VEC = Elem<T>::kVec;
+    constexpr int G = Geo::kGroups;
+    constexpr bool kTwoPass = TPR >= 1024;   // 64 registers per thread: the row cannot stay resident
+    // Residual gradient fetched together with x and dy (all of a row's loads in flight at once) where the
+    // register budget is 128 per thread; elsewhere it is fetched just before the store.
+    constexpr bool kEarlyRes = ADD && !kTwoPass;
+    constexpr int kRow = TPR * VPT * VEC;
+    __shared__ float red_all[2 * Geo::kWarps];
+    __shared__ __align__(16) float fold[Geo::kFoldRows > 0 ? Geo::kFoldRows * kRow : 4];
+    int buf = 0;
+
+    const int group = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int nvec = cols / VEC;
+    float* const red = red_all;
+
+    uint4 wv[VPT];
+    float acc[VPT][VEC];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k) {
+        const int v = t + k * TPR;
+        wv[k] = (!kTwoPass && v < nvec) ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[k][i] = 0.f;
+    }
+
+    const float inv_cols = 1.0f / static_cast<float>(cols);
+    // Rows are dealt G at a time to the CTAs round robin, one to each group; every thread of a group sees the same
+    // rows, so the early exit below is taken by whole groups. (Written with the row-group counter as the loop
+    // variable: the form that counts rows directly costs the half-precision kernels 50-80 bytes more in spills.)
+    const int64_t ngroups = (rows + G - 1) / G;
+    for (int64_t rg = blockIdx.x; rg < ngroups; rg += gridDim.x) {
+        const int64_t r = rg * G + group;
+        if (r >= rows) break;
+        const int64_t off = r * static_cast<int64_t>(cols);
+        const uint4* xr = reinterpret_cast<const uint4*>(x + off);
+        const uint4* gr = reinterpret_cast<const uint4*>(dy + off);
+        const float rinv = __ldg(inv_rms + r);
+        if constexpr (!kTwoPass) {
+            uint4 xv[VPT], gv[VPT];
+            uint4 dv[kEarlyRes ? VPT : 1];
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int v = t + k * TPR;
+                const bool on = v < nvec;
+                xv[k] = on ? ld_stream16(xr + v) : make_uint4(0, 0, 0, 0);
+                gv[k] = on ? ld_stream16(gr + v) : make_uint4(0, 0, 0, 0);
+                if constexpr (kEarlyRes) dv[k] = on ? ld_stream16(reinterpret_cast<const uint4*>(dres + off) + v) : make_uint4(0, 0, 0, 0);
+                keep_packed(wv[k]);
+            }
+
+            float c = 0.f;
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                float fx[VEC], fg[VEC], fw[VEC];
+                unpack16<T>(xv[k], fx);
+                unpack16<T>(gv[k], fg);
+                unpack16<T>(wv[k], fw);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) {
+                    c += (fg[i] * fw[i]) * fx[i];
+                    acc[k][i] += (fg[i] * fx[i]) * rinv;
+                }
+            }
+            c = group_sum<TPR>(c, red, buf, group);
+            const float term2 = c * (rinv * rinv) * inv_cols;
+
+            uint4* dr = reinterpret_cast<uint4*>(dx + off);
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int v = t + k * TPR;
+                if (v < nvec) {
+                    float fx[VEC], fg[VEC], fw[VEC], o[VEC];
+                    unpack16<T>(xv[k], fx);
+                    unpack16<T>(gv[k], fg);
+                    unpack16<T>(wv[k], fw);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) o[i] = rinv * (fg[i] * fw[i] - fx[i] * term2);
+                    if constexpr (ADD) {
+                        float fr[VEC];
+                        if constexpr (kEarlyRes) unpack16<T>(dv[k], fr);
+                        else unpack16<T>(ld_stream16(reinterpret_cast<const uint4*>(dres + off) + v), fr);
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) o[i] += fr[i];
+                    }
+                    st_stream16(dr + v, pack16<T>(o));
+                }
+            }
+        } else {
+            // Rows too long to hold in the registers of 1024 threads next to the dW partials: the row is
+            // read twice, packet by packet. The first read comes from HBM and stays cached (plain loads); the
+            // second, right behind it, is served by L1/L2, so HBM traffic does not grow.
+            float c = 0.f;
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int v = t + k * TPR;
+                const bool on = v < nvec;
+                const uint4 px = on ? __ldg(xr + v) : make_uint4(0, 0, 0, 0);
+                const uint4 pg = on ? __ldg(gr + v) : make_uint4(0, 0, 0, 0);
+                const uint4 pw = on ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
+                float fx[VEC], fg[VEC], fw[VEC];
+                unpack16<T>(px, fx);
+                unpack16<T>(pg, fg);
+                unpack16<T>(pw, fw);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) c += (fg[i] * fw[i]) * fx[i];
+            }
+            c = group_sum<TPR>(c, red, buf, group);
+            const float term2 = c * (rinv * rinv) * inv_cols;
+            uint4* dr = reinterpret_cast<uint4*>(dx + off);
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int v = t + k * TPR;
+                if (v < nvec) {
+                    const uint4 px = ld_stream16(xr + v);
+                    const uint4 pg = ld_stream16(gr + v);
+                    const uint4 pw = __ldg(reinterpret_cast<const uint4*>(w) + v);   // weights are not kept in registers here
+                    float fx[VEC], fg[VEC], fw[VEC], o[VEC];
+                    unpack16<T>(px, fx);
+                    unpack16<T>(pg, fg);
+                    unpack16<T>(pw, fw);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) {
+                        acc[k][i] += (fg[i] * fx[i]) * rinv;
+                        o[i] = rinv * (fg[i] * fw[i] - fx[i] * term2);
+                    }
+                    if constexpr (ADD) {
+                        float fr[VEC];
+                        unpack16<T>(ld_stream16(reinterpret_cast<const uint4*>(dres + off) + v), fr);
+#pragma unroll
+                        for (int i = 0; i < VEC; ++i) o[i] += fr[i];
+                    }
+                    st_stream16(dr + v, pack16<T>(o));
+                }
+            }
+        }
+    }
+
+    // Fold the G groups of this CTA: at distance d = 1, 2, 4, ... group g with g % 2d == d hands its sums to group
+    // g - d through shared memory. A fixed tree, so the CTA's partial row does not depend on timing.
+    if constexpr (G > 1) {
+#pragma unroll
+        for (int d = 1; d < G; d <<= 1) {
+            const int pos = group & (2 * d - 1);
+            float* slot = fold + (group / (2 * d)) * kRow;
+            if (pos == d) {
+#pragma unroll
+                for (int k = 0; k < VPT; ++k)
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) slot[(k * VEC + i) * TPR + t] = acc[k][i];
+            }
+            __syncthreads();
+            if (pos == 0 && group + d < G) {
+#pragma unroll
+                for (int k = 0; k < VPT; ++k)
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) acc[k][i] += slot[(k * VEC + i) * TPR + t];
+            }
+            __syncthreads();
+        }
+    }
+    if (group == 0) {
+        float* out = ws + static_cast<int64_t>(blockIdx.x) * cols;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int v = t + k * TPR;
+            if (v < nvec) {
+#pragma unroll
+                for (int i = 0; i < VEC; i += 4)
+                    *reinterpret_cast<float4*>(out + static_cast<int64_t>(v) * VEC + i) =
+                        make_float4(acc[k][i], acc[k][i + 1], acc[k][i + 2], acc[k][i + 3]);
+            }
+        }
+    }
+}
+
+// dw[j] = sum_{p<P} ws[p, j] for cols % 4 == 0. A CTA of 1024 threads takes 8 packets of four columns (128 bytes of
+// every partial row) and cuts the P rows into 128 slices, so that a thread loads only ceil(P / 128) packets, all at
+// once: the sum is one round trip to L2 deep instead of a chain of them. Fixed order: a thread adds its rows in
+// increasing p; the four slices of a warp are folded by shuffles (distance 1, then 2); the 32 warp sums of a
+// column packet are added in increasing warp order by one thread. One rounding to T at the end.
+template <typename T>
+__global__ void __launch_bounds__(1024)
+rms_dw_reduce4(T* __restrict__ dw, float* __restrict__ dw_f32, const float* __restrict__ ws, int P, int cols) {
+    __shared__ float4 part[32][8];
+    asm volatile("griddepcontrol.wait;" ::: "memory");   // see rms_dw_reduce
+    const int c4 = cols >> 2;
+    const int lane_col = threadIdx.x & 7;
+    const int slice = threadIdx.x >> 3;                  // 0..127
+    const int col = static_cast<int>(blockIdx.x) * 8 + lane_col;
+    float4 a = make_float4(0.f, 0.f, 0.f, 0.f);
+    if (col < c4) {
+        const float4* src = reinterpret_cast<const float4*>(ws) + col;
+        int p = slice;
+        for (; p + 128 < P; p += 256) {
+            const float4 v0 = __ldcg(src + static_cast<int64_t>(p) * c4);
+            const float4 v1 = __ldcg(src + static_cast<int64_t>(p + 128) * c4);
+            a.x += v0.x, a.y += v0.y, a.z += v0.z, a.w += v0.w;
+            a.x += v1.x, a.y += v1.y, a.z += v1.z, a.w += v1.w;
+        }
+        if (p < P) {
+            const float4 v0 = __ldcg(src + static_cast<int64_t>(p) * c4);
+            a.x += v0.x, a.y += v0.y, a.z += v0.z, a.w += v0.w;
+        }
+    }
+#pragma unroll
+    for (int m = 8; m <= 16; m <<= 1) {                   // lanes 8 apart hold neighbouring slices of the same packet
+        a.x += __shfl_xor_sync(0xffffffffu, a.x, m);
+        a.y += __shfl_xor_sync(0xffffffffu, a.y, m);
+        a.z += __shfl_xor_sync(0xffffffffu, a.z, m);
+        a.w += __shfl_xor_sync(0xffffffffu, a.w, m);
+    }
+    if ((threadIdx.x & 31) < 8) part[threadIdx.x >> 5][lane_col] = a;
+    __syncthreads();
+    if (threadIdx.x < 8 && col < c4) {
+        float4 s = part[0][threadIdx.x];
+#pragma unroll
+        for (int i = 1; i < 32; ++i) {
+            const float4 v = part[i][threadIdx.x];
+            s.x += v.x, s.y += v.y, s.z += v.z, s.w += v.w;
+        }
+        const int64_t j = static_cast<int64_t>(col) * 4;
+        if (dw != nullptr) {
+            dw[j] = from_f32<T>(s.x);
+            dw[j + 1] = from_f32<T>(s.y);
+            dw[j + 2] = from_f32<T>(s.z);
+            dw[j + 3] = from_f32<T>(s.w);
+        }
+        if (dw_f32 != nullptr) {
+            dw_f32[j] = s.x;
+            dw_f32[j + 1] = s.y;
+            dw_f32[j + 2] = s.z;
+            dw_f32[j + 3] = s.w;
+        }
+    }
+}
+
 // dw[j] = sum_{p<P} ws[p, j], summed in a fixed order: each of the 32 slices adds its rows
 // p = slice, slice+32, ... in increasing p, then the 32 slice sums are added in increasing slice.
 // One rounding to T at the end; the unrounded fp32 sum goes to dw_f32 when asked for.
@@ -444,6 +734,7 @@ rms_bwd_dw_scalar(float* __restrict__ ws, const T* __restrict__ dy, const T* __r
 struct RegShape {
     int tpr, vpt;
     bool fwd_ok, bwd_ok;   // fitted shapes only: whether the forward / the backward may pick it (from measurements)
+    bool fat_bwd;          // backward: one fat CTA per SM (rms_bwd_fat) instead of one CTA per row group (rms_bwd_reg)
 };
 // Indices 8-10 are alternatives to {128,4}, {256,4} and {128,2} with one row per CTA pass; only the backward
 // picks them (bwd_shape_for), the size-ordered search of reg_shape_for never reaches them.
@@ -456,11 +747,17 @@ struct RegShape {
 //             5120: 0.77 / 0.87   6144: 0.82 / 0.93   7168: 0.70 / 0.97  -- one row per pass of a 320-448 thread
 //             CTA with two packets per thread keeps too little in flight per barrier; the forward stays with {256,4}
 // ({768,2} for 12288 lost both ways, 0.53 / 0.85 and 0.70 / 0.73, and is not built.)
-constexpr RegShape kRegShapes[] = {{32, 1, true, true},   {32, 2, true, true},  {32, 4, true, true},  {128, 2, true, true},
-                                   {128, 4, true, true},  {256, 4, true, true}, {512, 4, true, true}, {1024, 4, true, true},
-                                   {256, 2, true, true},  {512, 2, true, true}, {256, 1, true, true},
-                                   {160, 2, true, true},  {192, 1, true, true}, {192, 2, false, true}, {320, 2, false, true},
-                                   {384, 2, false, true}, {448, 2, false, true}};
+// fat_bwd, measured on B200 (bf16, 2^29 elements, fraction of the copy bandwidth, fat / thin): warp-per-row shapes
+// (16 independent warps in one CTA, no barrier in the row loop) 0.98 / 0.90 at hidden 1024; {512,4} 0.84 / 0.82 at
+// hidden 16384. The other shapes keep one CTA per row group: their fat forms need a register or two more than the
+// 64 (128) they are held to and lose more to spills than the fewer partial rows give back (hidden 4096: 0.67 / 0.90;
+// 8192: 0.88 / 0.93).
+constexpr RegShape kRegShapes[] = {{32, 1, true, true, true},     {32, 2, true, true, true},    {32, 4, true, true, true},
+                                   {128, 2, true, true, false},   {128, 4, true, true, false},  {256, 4, true, true, false},
+                                   {512, 4, true, true, true},    {1024, 4, true, true, false}, {256, 2, true, true, false},
+                                   {512, 2, true, true, false},   {256, 1, true, true, false},  {160, 2, true, true, false},
+                                   {192, 1, true, true, false},   {192, 2, false, true, false}, {320, 2, false, true, false},
+                                   {384, 2, false, true, false},  {448, 2, false, true, false}};
 constexpr int kNumRegShapes = sizeof(kRegShapes) / sizeof(kRegShapes[0]);
 constexpr int kFirstFitted = 11;
 constexpr int kScalarDwSlices = 64;
@@ -469,10 +766,7 @@ constexpr int64_t shape_capacity(int i) { return static_cast<int64_t>(kRegShapes
 
 // MGR_RMSNORM_FWD_SHAPE / MGR_RMSNORM_BWD_SHAPE=<index into kRegShapes> pin the packet shape when it can hold the
 // row (measurement aid). Returns -1 when unset or unusable.
-int pinned_shape(const char* var, int64_t nvec) {
-    const char* e = std::getenv(var);
-    if (e == nullptr) return -1;
-    const int i = std::atoi(e);
+int pinned_shape(int i, int64_t nvec) {
     return (i >= 0 && i < kNumRegShapes && nvec <= shape_capacity(i)) ? i : -1;
 }
 
@@ -512,7 +806,9 @@ constexpr bool shape_tables_ok() {
         const int tpr = kRegShapes[i].tpr, vpt = kRegShapes[i].vpt;
         const int block = tpr >= 256 ? tpr : (256 % tpr == 0 ? 256 : tpr);
         if (tpr % 32 != 0 || block > 1024 || block % tpr != 0 || vpt < 1 || vpt > 4) return false;
-        if (static_cast<int64_t>(block / tpr - 1) * tpr * vpt * 8 * 4 > 44 * 1024) return false;
+        const int bg = bwd_groups(tpr, vpt);
+        if (bg * tpr > 1024 || bg < 1 || (tpr > 32 && bg > 15)) return false;                       // a launchable CTA; named barriers 1..15
+        if (static_cast<int64_t>(bg / 2) * tpr * vpt * 8 * 4 > 44 * 1024) return false;              // the fold buffer (static shared memory)
     }
     for (int64_t nvec = 1; nvec <= 4096; ++nvec) {
         const int f = default_fwd_shape(nvec), b = default_bwd_shape(nvec);
@@ -523,11 +819,11 @@ constexpr bool shape_tables_ok() {
 static_assert(shape_tables_ok(), "a row length has no packet shape, or a shape cannot be launched");
 
 int fwd_shape_for(int64_t nvec) {
-    const int pinned = pinned_shape("MGR_RMSNORM_FWD_SHAPE", nvec);
+    const int pinned = pinned_shape(overrides().fwd_shape, nvec);
     return pinned >= 0 ? pinned : default_fwd_shape(nvec);
 }
 int bwd_shape_for(int64_t nvec) {
-    const int pinned = pinned_shape("MGR_RMSNORM_BWD_SHAPE", nvec);
+    const int pinned = pinned_shape(overrides().bwd_shape, nvec);
     return pinned >= 0 ? pinned : default_bwd_shape(nvec);
 }
 
@@ -550,6 +846,13 @@ struct RegKernels {
     static constexpr int VPT = kRegShapes[I].vpt;
     static constexpr int BLOCK = RegGeom<TPR>::kBlock;
     static constexpr int G = RegGeom<TPR>::kGroups;
+    static constexpr int BWD_BLOCK = BwdGeom<TPR, VPT>::kBlock;
+    static constexpr int BWD_G = BwdGeom<TPR, VPT>::kGroups;
+    // which backward kernel this shape runs: the table's choice unless MGR_RMSNORM_BWD_FAT pins it
+    static bool fat_bwd() {
+        const int pinned = overrides().bwd_fat;
+        return pinned >= 0 ? pinned != 0 : kRegShapes[I].fat_bwd;
+    }
 
     static int64_t fwd_grid(int64_t rows, const DeviceInfo& di) {
         static std::atomic<int> occ[kMaxDevices];
@@ -559,6 +862,12 @@ struct RegKernels {
     }
     static int64_t bwd_grid(int64_t rows, const DeviceInfo& di) {
         static std::atomic<int> occ[kMaxDevices];
+        static std::atomic<int> occ_fat[kMaxDevices];
+        if (fat_bwd()) {
+            const int64_t ngroups = (rows + BWD_G - 1) / BWD_G;
+            const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_bwd_fat<T, TPR, VPT, ADD>, BWD_BLOCK, occ_fat, di.device);
+            return ngroups < cap ? ngroups : cap;
+        }
         const int64_t ngroups = (rows + G - 1) / G;
         const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_bwd_reg<T, TPR, VPT, ADD>, BLOCK, occ, di.device);
         return ngroups < cap ? ngroups : cap;
@@ -569,7 +878,10 @@ struct RegKernels {
     }
     static void bwd(T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv, int64_t rows,
                     int cols, int64_t grid, cudaStream_t s, const T* dres) {
-        rms_bwd_reg<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres);
+        if (fat_bwd())
+            rms_bwd_fat<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BWD_BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres);
+        else
+            rms_bwd_reg<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres);
     }
 };
 
@@ -612,12 +924,12 @@ enum class Path { kAuto, kReg, kRing, kScalar };
 
 // MGR_RMSNORM_PATH=reg|ring|scalar pins the kernel family (benchmarking and tests); unset = automatic.
 Path forced_path() {
-    const char* e = std::getenv("MGR_RMSNORM_PATH");
-    if (e == nullptr) return Path::kAuto;
-    if (std::strcmp(e, "reg") == 0) return Path::kReg;
-    if (std::strcmp(e, "ring") == 0) return Path::kRing;
-    if (std::strcmp(e, "scalar") == 0) return Path::kScalar;
-    return Path::kAuto;
+    switch (overrides().rms_path) {
+        case 1: return Path::kReg;
+        case 2: return Path::kRing;
+        case 3: return Path::kScalar;
+        default: return Path::kAuto;
+    }
 }
 
 int* rms_status_ptr(const DeviceInfo& di) {
@@ -838,6 +1150,14 @@ int bwd_typed(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, 
     at[0].val.programmaticStreamSerializationAllowed = 1;
     cfg.attrs = at;
     cfg.numAttrs = 1;
+    if (cols % 4 == 0) {   // rows of the workspace start on 16-byte boundaries: the packet form of the column sum
+        cfg.blockDim = dim3(1024);
+        if (cudaLaunchKernelEx(&cfg, rms_dw_reduce4<T>, static_cast<T*>(dw), dw_f32, static_cast<const float*>(ws), static_cast<int>(P),
+                               static_cast<int>(cols)) == cudaSuccess)
+            return launch_status();
+        (void)cudaGetLastError();
+        cfg.blockDim = dim3(32, 32);
+    }
     if (cudaLaunchKernelEx(&cfg, rms_dw_reduce<T>, static_cast<T*>(dw), dw_f32, static_cast<const float*>(ws), static_cast<int>(P),
                            static_cast<int>(cols)) != cudaSuccess) {
         (void)cudaGetLastError();
@@ -970,6 +1290,10 @@ int rmsnorm_status_fetch(int clear) {
     }
     return v;
 }
+
+int rmsnorm_status_poke(int value) {
+    return cudaMemcpyToSymbol(g_rms_status, &value, sizeof(int)) == cudaSuccess ? MGR_OK : ((void)cudaGetLastError(), MGR_ERR_CUDA);
+}
 }  // namespace mgr
 
 // ------------------------------------------------------------------------------------------------
@@ -996,17 +1320,19 @@ namespace {
 // handle for the runtime, not an address a kernel can use: the address comes from
 // cudaGetSymbolAddress, asked once per device with that device current, and is cached.
 float* noalloc_scratch(const DeviceInfo& di) {
-    static float* cache[kMaxDevices] = {nullptr};
-    if (cache[di.device] == nullptr) {
+    static std::atomic<float*> cache[kMaxDevices];   // racing first calls store the same address
+    float* known = cache[di.device].load(std::memory_order_relaxed);
+    if (known == nullptr) {
         void* p = nullptr;
         const cudaError_t e = cudaGetSymbolAddress(&p, g_noalloc_scratch);
         if (e != cudaSuccess || p == nullptr) {
             (void)cudaGetLastError();
             return nullptr;
         }
-        cache[di.device] = static_cast<float*>(p);
+        known = static_cast<float*>(p);
+        cache[di.device].store(known, std::memory_order_relaxed);
     }
-    return cache[di.device];
+    return known;
 }
 
 }  // namespace

@@ -26,6 +26,9 @@ class HostRMSNormPipeline:
     """Reusable pipeline for one (rows, cols, dtype, device): device staging buffers are allocated once.
 
     run(x_host, dy_host, weight_dev, eps, y_host, dx_host) -> dW (device tensor, weight dtype)
+    run(..., return_f32=True) -> the fp32 column sum before its rounding: what a rank that holds a row
+    block of a larger batch all-reduces across ranks first (sharding.allreduce_dw) so that dW is rounded
+    once, after the cross-rank sum. The returned tensor is the pipeline's own buffer, valid until the next run.
     Host tensors should be pinned (torch.Tensor.pin_memory) for the copies to be asynchronous.
     """
 
@@ -56,7 +59,7 @@ class HostRMSNormPipeline:
             self.s_in = torch.cuda.Stream(self.device)
             self.s_out = torch.cuda.Stream(self.device)
 
-    def run(self, x_host, dy_host, weight, eps: float, y_host, dx_host) -> torch.Tensor:
+    def run(self, x_host, dy_host, weight, eps: float, y_host, dx_host, return_f32: bool = False) -> torch.Tensor:
         L, cols, code = self.L, self.cols, self.code
         for t in (x_host, dy_host, y_host, dx_host):
             if t.dtype != self.dtype or tuple(t.shape) != (self.rows, cols) or not t.is_contiguous():
@@ -93,4 +96,4 @@ class HostRMSNormPipeline:
                 dx_host[r0:r0 + n].copy_(slot["dx"][:n], non_blocking=True)
                 slot["drained"].record(self.s_out)
         main.wait_stream(self.s_out)
-        return self.dw_sum.to(self.dtype)
+        return self.dw_sum if return_f32 else self.dw_sum.to(self.dtype)

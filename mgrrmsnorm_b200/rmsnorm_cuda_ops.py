@@ -10,8 +10,16 @@ launch on torch's current stream (the reference launches on the legacy default s
 device is current, src/rmsnorm_kernel.cu:542,564).
 
 torch is used for device memory and streams only; all arithmetic is in libmgr_b200.so.
+
+Two routes to the same C ABI: the functions below (ctypes, need no compiler beyond the one that built the
+library), and the compiled torch extension built from pytorch_binding/binding.cpp by setup.py, which has
+the same functions with less per-call overhead. When the extension is present in mgrrmsnorm_b200/pybind/ it
+replaces the functions listed in `ENTRY_POINTS` at import (`BINDING` says which route is active;
+MGR_BINDING=ctypes keeps the ctypes route). The ctypes versions stay reachable as `ctypes_impl[name]`.
 """
 from __future__ import annotations
+
+import os
 
 import torch
 
@@ -393,3 +401,38 @@ class gemm_sm_limit:
     def __exit__(self, *exc):
         _capi.lib().mgr_gemm_set_sm_limit(self.prev)
         return False
+
+
+def device_status(clear: bool = True) -> None:
+    """Raises if a kernel on the current device gave up a bounded wait since the last clearing read
+    (mgr_device_status). Outputs of such a launch are incomplete. This call synchronises with the device, so
+    it belongs where the host waits anyway: after a step's final synchronisation, before results are used."""
+    _capi.check("device status", _capi.lib().mgr_device_status(1 if clear else 0))
+
+
+# ---------------------------------------------------------------------------------------------------
+# route selection
+# ---------------------------------------------------------------------------------------------------
+
+ENTRY_POINTS = ("rmsnorm_forward", "rmsnorm_backward", "rmsnorm_backward_full", "add_rmsnorm_forward", "add_rmsnorm_backward",
+                "swiglu_act_forward", "swiglu_act_backward", "swiglu_fused_forward", "swiglu_fused_forward_save", "linear_tn",
+                "gemm", "swiglu_fused_backward", "swiglu_dh_dgv")
+ctypes_impl = {name: globals()[name] for name in ENTRY_POINTS}
+
+
+def _compiled_binding():
+    if os.environ.get("MGR_BINDING", "") == "ctypes":
+        return None
+    try:
+        _capi.lib()                      # the extension links against the library: load it (or fail loudly) first
+        from .pybind import rmsnorm_cuda_ops as ext
+    except ImportError:
+        return None
+    return ext
+
+
+compiled = _compiled_binding()
+BINDING = "ctypes" if compiled is None else "pybind"
+if compiled is not None:
+    for _name in ENTRY_POINTS:
+        globals()[_name] = getattr(compiled, _name)

@@ -132,13 +132,20 @@ class AsyncDwReduce:
     """
 
     def __init__(self, device=None, group=None):
-        self.side = torch.cuda.Stream(device)
+        # Host tensors (a CPU process group, as in the tests of the host logic) have no streams: the same sum and
+        # rounding then run synchronously inside start().
+        on_cpu = device is not None and torch.device(device).type == "cpu"
+        self.side = None if on_cpu else torch.cuda.Stream(device)
         self.group = group
         self.pending: dict[int, torch.cuda.Event] = {}
 
     def start(self, dw_f32: torch.Tensor, dw_out: torch.Tensor) -> None:
         if dw_f32.dtype != torch.float32:
             raise TypeError("the cross-rank sum of dW is taken in fp32")
+        if self.side is None:
+            dist.all_reduce(dw_f32, op=dist.ReduceOp.SUM, group=self.group)
+            dw_out.copy_(dw_f32)
+            return
         self.side.wait_stream(torch.cuda.current_stream(dw_f32.device))   # the partial has been produced
         # both tensors are used on the side stream: tell the caching allocator, so that freeing one of them on
         # the compute stream cannot hand its memory out again while the collective still runs
@@ -157,7 +164,8 @@ class AsyncDwReduce:
             torch.cuda.current_stream(dw_f32.device).wait_event(ev)
 
     def drain(self) -> None:
-        torch.cuda.current_stream(self.side.device).wait_stream(self.side)
+        if self.side is not None:
+            torch.cuda.current_stream(self.side.device).wait_stream(self.side)
         self.pending.clear()
 
 

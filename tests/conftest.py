@@ -37,9 +37,35 @@ def golden_dir() -> Path:
 
 @pytest.fixture(scope="session")
 def built_lib():
-    """libmgr_b200.so, built on demand (nvcc cross-compiles without a GPU)."""
+    """libmgr_b200.so, brought up to date with its sources (nvcc cross-compiles without a GPU). The build is
+    incremental: with unchanged sources it only compares fingerprints, so a stale library is never tested."""
     from mgrrmsnorm_b200 import _capi, build
 
-    if not _capi.LIB_PATH.exists():
-        build.build()
+    build.build()
     return _capi.lib()
+
+
+@pytest.fixture
+def mgr_env():
+    """Setter for the library's MGR_* overrides: `mgr_env("MGR_RMSNORM_PATH", "ring")`. The library reads its
+    environment once, so every change is followed by mgr_reload_env(); the old values come back (and are
+    re-read) when the test ends."""
+    import os
+
+    from mgrrmsnorm_b200 import _capi
+
+    saved = {}
+
+    def set_(name: str, value: str) -> None:
+        saved.setdefault(name, os.environ.get(name))
+        os.environ[name] = value
+        _capi.reload_env()
+
+    yield set_
+    for name, old in saved.items():
+        if old is None:
+            os.environ.pop(name, None)
+        else:
+            os.environ[name] = old
+    if saved:
+        _capi.reload_env()

@@ -23,7 +23,7 @@ os.environ["TRITON_INTERPRET"] = "1"
 
 HERE = Path(__file__).resolve().parent
 ROOT = HERE.parent.parent
-REF = Path(os.environ.get("MGR_REFERENCE_DIR", "/root/reference"))
+REF = Path(os.environ.get("MGR_REFERENCE_DIR") or ROOT.parent / "reference")   # default: `reference` beside this repository
 sys.path.insert(0, str(ROOT))
 sys.path.insert(0, str(REF))
 

@@ -163,7 +163,8 @@ def test_live_reference_triton_kernels_on_random_inputs(tmp_path):
     import sys
     from pathlib import Path
 
-    ref_dir = Path(os.environ.get("MGR_REFERENCE_DIR", "/root/reference"))
+    # the reference tree: MGR_REFERENCE_DIR, else a directory `reference` beside this repository
+    ref_dir = Path(os.environ.get("MGR_REFERENCE_DIR") or Path(__file__).resolve().parents[2] / "reference")
     if not (ref_dir / "megagemm" / "swiglu.py").exists():
         pytest.skip("reference tree not present on this machine")
     out_path = tmp_path / "live.npz"

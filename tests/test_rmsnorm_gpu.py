@@ -309,23 +309,58 @@ def test_against_reference_cuda_kernels(ops, dtype):
         assert ours <= theirs + 1e-9, f"dW error {ours} vs reference {theirs}"
 
 
+# ---- the two forms of the packet backward: one CTA per row group, or one fat CTA per SM ----
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("rows,cols", [(1, 8), (3, 64), (64, 16384), (128, 8192), (700, 4096), (1024, 1024), (5000, 2560),
+                                        (2100, 8192), (333, 7168), (70000, 512), (900, 12288), (4099, 1536), (33, 32768)])
+def test_fat_and_thin_backward_kernels_agree(ops, built_lib, mgr_env, dtype, rows, cols):
+    """MGR_RMSNORM_BWD_FAT pins the backward packet kernel for every shape: 0 = one CTA per row group, 1 = one
+    CTA per SM whose row groups run independently and are folded at the end (fewer partial rows of dW).
+    Each row's arithmetic is the same in both, so dx is bit-identical; dW sums the same products in
+    another fixed grouping, so both meet the oracle and each is bit-reproducible."""
+    x, w, dy = seeded_rmsnorm_inputs(rows, cols, dtype, rows + cols)
+    xd, wd, dyd = x.cuda(), w.cuda(), dy.cuda()
+    _, inv = ops.rmsnorm_forward(xd, wd, 1e-6)
+    mgr_env("MGR_RMSNORM_PATH", "reg")
+    out = {}
+    for fat in ("0", "1"):
+        mgr_env("MGR_RMSNORM_BWD_FAT", fat)
+        runs = []
+        for _ in range(4):
+            dx, dw, dw32 = ops.rmsnorm_backward_full(dyd, xd, wd, inv, True)
+            torch.cuda.synchronize()
+            runs.append((dx.clone(), dw.clone(), dw32.clone()))
+        for r in runs[1:]:
+            assert all(torch.equal(a, b) for a, b in zip(runs[0], r)), f"fat={fat}: not bit-reproducible"
+        out[fat] = runs[0]
+    assert built_lib.mgr_device_status(1) == 0
+    assert torch.equal(out["0"][0], out["1"][0]), "dx differs between the two forms of the backward kernel"
+    tdx, tdw = oracle.rmsnorm_bwd(to_np(dy), to_np(x), to_np(w), 1e-6)
+    assert_matches_truth(out["1"][0], tdx, dtype, "dx")
+    for fat in ("0", "1"):
+        _, dw, dw32 = out[fat]
+        assert_matches_truth(dw32, tdw, "f32", f"dw_f32 (fat={fat})", slack=4.0)
+        assert torch.equal(dw, dw32.to(dw.dtype)), "dw must be exactly the rounded fp32 sum"
+
+
 # ---- every kernel family on the same inputs --------------------------------------------------------
 
 @pytest.mark.parametrize("path", ["reg", "ring", "scalar"])
 @pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
 @pytest.mark.parametrize("rows,cols", [(3, 8), (129, 128), (1200, 1024), (2500, 2048), (1531, 4096), (777, 5120), (1300, 8192),
                                         (600, 16384)])
-def test_each_kernel_family_matches_oracle(ops, built_lib, monkeypatch, path, dtype, rows, cols):
+def test_each_kernel_family_matches_oracle(ops, built_lib, mgr_env, path, dtype, rows, cols):
     """MGR_RMSNORM_PATH pins the register, bulk-copy-ring or scalar kernels (a family that cannot take
     the shape falls through to the next one); all must meet the same tolerances."""
-    monkeypatch.setenv("MGR_RMSNORM_PATH", path)
+    mgr_env("MGR_RMSNORM_PATH", path)
     check_against_oracle(ops, rows, cols, dtype, 1e-6, seed=rows + cols)
     assert built_lib.mgr_device_status(1) == 0
 
 
 @pytest.mark.parametrize("path", ["reg", "ring"])
-def test_families_are_each_bit_reproducible(ops, monkeypatch, path):
-    monkeypatch.setenv("MGR_RMSNORM_PATH", path)
+def test_families_are_each_bit_reproducible(ops, mgr_env, path):
+    mgr_env("MGR_RMSNORM_PATH", path)
     x, w, dy = seeded_rmsnorm_inputs(5000, 4096, "bf16", 17)
     xd, wd, dyd = x.cuda(), w.cuda(), dy.cuda()
     first = None
@@ -340,7 +375,7 @@ def test_families_are_each_bit_reproducible(ops, monkeypatch, path):
             assert all(torch.equal(a, b) for a, b in zip(first, cur))
 
 
-def test_host_tensor_pipeline_matches_module(ops, monkeypatch):
+def test_host_tensor_pipeline_matches_module(ops, mgr_env):
     """HostRMSNormPipeline (row chunks streamed over PCIe) against one whole-tensor call. With the kernel
     family pinned (the automatic choice depends on the row count, which differs between a chunk and the
     whole tensor) y and dx come from the same kernels on the same rows and are bit-identical; dW sums the
@@ -348,7 +383,7 @@ def test_host_tensor_pipeline_matches_module(ops, monkeypatch):
     and is itself reproducible."""
     from mgrrmsnorm_b200.hostpipe import HostRMSNormPipeline
 
-    monkeypatch.setenv("MGR_RMSNORM_PATH", "reg")
+    mgr_env("MGR_RMSNORM_PATH", "reg")
 
     rows, cols = 5000, 2048
     x, w, dy = seeded_rmsnorm_inputs(rows, cols, "bf16", 99)

@@ -97,6 +97,23 @@ def _gloo_worker(rank: int, world: int, port: int, q):
         with pytest.raises(TypeError):
             sharding.allreduce_dw(torch.zeros(4, dtype=torch.float16), torch.float16)
 
+        # The two legs of the benchmark take the cross-rank sum of dW through different helpers: the resident
+        # loop through AsyncDwReduce (all-reduce + rounding off the compute stream), the host-tensor leg through
+        # allreduce_dw on the pipeline's fp32 sum. Same shards in, same bits out: fp32 sum first, ONE rounding.
+        # A sum of already-rounded partials (what the host leg once did) is a different number.
+        big = 4096
+        part = torch.from_numpy(np.random.default_rng(100 + rank).standard_normal(big).astype(np.float32) * 37.0)
+        leg_host = sharding.allreduce_dw(part.clone(), torch.bfloat16)
+        red = sharding.AsyncDwReduce("cpu")
+        leg_resident = torch.empty(big, dtype=torch.bfloat16)
+        scratch = part.clone()
+        red.start(scratch, leg_resident)
+        red.wait_for(scratch)
+        red.drain()
+        rounded_first = part.to(torch.bfloat16)
+        dist.all_reduce(rounded_first)
+        ok_dw = ok_dw and torch.equal(leg_host, leg_resident) and not torch.equal(leg_host, rounded_first)
+
         # forward-reduce / backward-reduce pair around a rank-local linear map
         t = torch.full((3,), float(rank + 1), requires_grad=True)
         a = sharding._ReduceBackward.apply(t, None)

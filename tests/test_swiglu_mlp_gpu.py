@@ -236,6 +236,95 @@ def test_config4_shape_forward_backward(dtype):
         assert float((got.float() - want).abs().max()) < 1e-2 * scale
 
 
+def _fp32_library_mlp(x, w12, w3, dy, f):
+    """The reference's formulas (w12 -> silu(gate) * value -> w3, megagemm/swiglu.py:35-41,166-169) evaluated by
+    library GEMMs in fp32 (no tf32) on the GPU, with autograd for the backward: the truth proxy for problems too
+    large for the fp64 CPU oracle. Returns y, dx, dw12, dw3 in fp32."""
+    xr = x.float().requires_grad_(True)
+    w12r, w3r = w12.float().requires_grad_(True), w3.float().requires_grad_(True)
+    prev = torch.backends.cuda.matmul.allow_tf32
+    torch.backends.cuda.matmul.allow_tf32 = False
+    try:
+        gv = torch.nn.functional.linear(xr, w12r)
+        yr = torch.nn.functional.linear(torch.nn.functional.silu(gv[..., :f]) * gv[..., f:], w3r)
+        yr.backward(dy.float())
+    finally:
+        torch.backends.cuda.matmul.allow_tf32 = prev
+    return yr.detach(), xr.grad, w12r.grad, w3r.grad
+
+
+def _check_mlp_against_library_and_oracle(mlp, x, dy, dtype, sample_rows):
+    """Whole tensors against the fp32 library evaluation; `sample_rows` rows of y and dx (rows of an MLP are
+    independent given the weights) against the fp64 CPU oracle, which also anchors the library proxy."""
+    f = mlp.hidden
+    xin = x.clone().requires_grad_(True)
+    y = mlp(xin)
+    y.backward(dy)
+    torch.cuda.synchronize()
+    w12, w3 = mlp.w12.weight.detach(), mlp.w3.weight.detach()
+    yr, dxr, dw12r, dw3r = _fp32_library_mlp(x, w12, w3, dy, f)
+    m, d = x.shape
+    # activations: one output rounding + fp32 accumulation over the contraction lengths involved
+    for name, got, want, k in (("y", y, yr, f), ("dx", xin.grad, dxr, 2 * f)):
+        tol = gemm_tolerance(k, dtype, float(want.abs().max())) * 2 + 1e-4      # x2: the 16-bit intermediates h / dgv
+        err = float((got.float() - want).abs().max())
+        assert err <= max(tol, 1e-2 if float(want.abs().max()) < 4 else tol), f"{name}: max err {err:.3e} > {tol:.3e}"
+        assert err < 1e-2 * max(1.0, float(want.abs().max())), name
+    # weight gradients contract over the m tokens
+    for name, got, want in (("dw12", mlp.w12.weight.grad, dw12r), ("dw3", mlp.w3.weight.grad, dw3r)):
+        tol = gemm_tolerance(m, dtype, float(want.abs().max())) * 2 + 1e-4
+        err = float((got.float() - want).abs().max())
+        assert err <= tol, f"{name}: max err {err:.3e} > {tol:.3e} (max |truth| {float(want.abs().max()):.3g})"
+    # fp64 oracle on sampled rows (first tile, a tile edge, the last rows)
+    rows = torch.tensor(sample_rows, device=x.device)
+    o = oracle.swiglu_mlp(to_np(x[rows]), to_np(w12), to_np(w3), dy=to_np(dy[rows]))
+    for name, got, want, k in (("y", y[rows], o["y"], f), ("dx", xin.grad[rows], o["dx"], 2 * f)):
+        err = float(np.abs(to_np(got).astype(np.float64) - want).max())
+        tol = gemm_tolerance(k, dtype, float(np.abs(want).max())) * 2 + 1e-4
+        assert err <= tol, f"{name} vs fp64 oracle on sampled rows: {err:.3e} > {tol:.3e}"
+        lib = float(np.abs(to_np((yr if name == "y" else dxr)[rows]).astype(np.float64) - want).max())
+        assert lib <= 1e-4 * max(1.0, float(np.abs(want).max())), f"the fp32 library proxy is off the oracle by {lib:.3e}"
+
+
+@pytest.mark.parametrize("dtype", ["f16", "bf16"])
+def test_config4_full_size(built_lib, dtype):
+    """Config 4 at its full size: x [32,128,4096] (4096 tokens), d_model 4096, hidden 6912 (the module's default),
+    nn.Linear default init from a seed, forward + backward through the module."""
+    from megagemm import MegaGemmTriton
+
+    td = TORCH_DTYPES[dtype]
+    torch.manual_seed(1234)
+    mlp = MegaGemmTriton(4096).cuda().to(td)
+    assert mlp.hidden == 6912
+    g = torch.Generator(device="cuda").manual_seed(1234)
+    x = torch.randn(4096, 4096, device="cuda", generator=g).to(td)
+    dy = torch.randn(4096, 4096, device="cuda", generator=g).to(td)
+    _check_mlp_against_library_and_oracle(mlp, x, dy, dtype, [0, 1, 127, 128, 255, 256, 2047, 2048, 4094, 4095])
+    assert built_lib.mgr_device_status(1) == 0
+
+
+def test_config5_rank_slice_full_size(built_lib):
+    """One rank's share of config 5 at 8 GPUs: bf16, 16384 tokens, d_model 8192, 3584 of the 28672 hidden units
+    (w12 slice [7168, 8192], w3 slice [8192, 3584]); all six GEMMs at their real sizes, including the two weight
+    gradients that contract over 16384 tokens and the 128 / 64 row-tile walks of the projection."""
+    from mgrrmsnorm_b200 import sharding
+
+    td = torch.bfloat16
+    d, f_full, world, m = 8192, 28672, 8, 16384
+    tp = sharding.TensorParallelSwiGLU(d, f_full, world, rank=3).cuda().to(td)
+    mlp = tp.local
+    f = mlp.hidden
+    assert f == 3584
+    g = torch.Generator(device="cuda").manual_seed(99)
+    with torch.no_grad():       # nn.Linear default init; fan_in of w3 is the FULL d_ff
+        mlp.w12.weight.copy_((torch.rand(2 * f, d, device="cuda", generator=g) * 2 - 1) / d ** 0.5)
+        mlp.w3.weight.copy_((torch.rand(d, f, device="cuda", generator=g) * 2 - 1) / f_full ** 0.5)
+    x = torch.randn(m, d, device="cuda", generator=g).to(td)
+    dy = torch.randn(m, d, device="cuda", generator=g).to(td)
+    _check_mlp_against_library_and_oracle(mlp, x, dy, "bf16", [0, 127, 128, 8191, 8192, 16383])
+    assert built_lib.mgr_device_status(1) == 0
+
+
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 @pytest.mark.parametrize("m,d,f", [(128, 64, 128), (200, 256, 384), (1024, 4096, 6912), (296, 512, 1000)])
 def test_kept_projection_forward_and_fused_dh_backward(ops, built_lib, dtype, m, d, f):
@@ -287,7 +376,7 @@ def test_module_backward_modes_agree_with_oracle(monkeypatch, recompute):
 
 @pytest.mark.parametrize("dtype", ["f16", "bf16"])
 @pytest.mark.parametrize("m,d,f", [(256, 64, 128), (128, 128, 256), (520, 256, 384), (1024, 1024, 1536), (296, 512, 1000)])
-def test_cta_pair_kernels_equal_single_cta_kernels(ops, built_lib, monkeypatch, dtype, m, d, f):
+def test_cta_pair_kernels_equal_single_cta_kernels(ops, built_lib, mgr_env, dtype, m, d, f):
     """MGR_GEMM_CTA_GROUP=2 runs every GEMM on pairs of CTAs sharing one MMA (256-row tiles, each CTA
     loading half of B). The K order of the accumulation is the same, so every output must be bit-identical
     to the single-CTA kernels' -- for all operand layouts and all epilogues."""
@@ -311,9 +400,9 @@ def test_cta_pair_kernels_equal_single_cta_kernels(ops, built_lib, monkeypatch, 
         torch.cuda.synchronize()
         return out
 
-    monkeypatch.setenv("MGR_GEMM_CTA_GROUP", "1")
+    mgr_env("MGR_GEMM_CTA_GROUP", "1")
     one = everything()
-    monkeypatch.setenv("MGR_GEMM_CTA_GROUP", "2")
+    mgr_env("MGR_GEMM_CTA_GROUP", "2")
     two = everything()
     assert built_lib.mgr_device_status(1) == 0
     for k in one:
@@ -324,7 +413,7 @@ def test_cta_pair_kernels_equal_single_cta_kernels(ops, built_lib, monkeypatch, 
 @pytest.mark.parametrize("m,d,f", [(8, 64, 128), (16, 512, 1000), (64, 4096, 6912), (130, 256, 320), (600, 1024, 1536),
                                    # short A boxes whose contraction wraps the (run-time sized) stage ring several times
                                    (8, 4096, 1024), (1, 2048, 256), (24, 2048, 512), (56, 1600, 384), (120, 1536, 256)])
-def test_narrow_tile_kernels_equal_wide_tile_kernels(ops, built_lib, monkeypatch, dtype, m, d, f):
+def test_narrow_tile_kernels_equal_wide_tile_kernels(ops, built_lib, mgr_env, dtype, m, d, f):
     """Skinny problems run on 64- or 32-column tiles (MGR_GEMM_NARROW=1 / =32 forces them, =0 forbids them) so
     that more CTAs share the weight stream. Same K order, so the fused projection and the plain GEMM must be
     bit-identical to the 256-column kernels."""
@@ -335,8 +424,8 @@ def test_narrow_tile_kernels_equal_wide_tile_kernels(ops, built_lib, monkeypatch
     w3 = (torch.randn(d, f, generator=g) / f ** 0.5).to(td).cuda()
     outs = {}
     for narrow in ("0", "1", "32"):
-        monkeypatch.setenv("MGR_GEMM_NARROW", narrow)
-        monkeypatch.setenv("MGR_GEMM_CTA_GROUP", "1")
+        mgr_env("MGR_GEMM_NARROW", narrow)
+        mgr_env("MGR_GEMM_CTA_GROUP", "1")
         h = ops.swiglu_fused_forward(x, w12, f)
         outs[narrow] = (h, ops.linear_tn(h, w3))
         torch.cuda.synchronize()
