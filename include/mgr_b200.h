@@ -107,6 +107,13 @@ int mgr_debug_poke_device_status(int family, int value);
 int mgr_rmsnorm_fwd(void* y, float* inv_rms, const void* x, const void* w,
                     int64_t rows, int64_t cols, float eps, int dtype, void* stream);
 
+/* Row scales alone: inv_rms[r] = 1/sqrt(mean_j x[r,j]^2 + eps), the same kernels as mgr_rmsnorm_fwd with the
+ * output stores left out, hence the same bits as the inv_rms that call writes. One read of x, nothing else.
+ * It is the first half of an RMSNorm folded into the GEMM that consumes it (mgr_swiglu_fused_fwd_scaled); the
+ * reference always materialises the normalised tensor (megagemm/rmsnorm.py:74-75 then megagemm/swiglu.py:167),
+ * so it has no counterpart there. */
+int mgr_rms_inv(float* inv_rms, const void* x, int64_t rows, int64_t cols, float eps, int dtype, void* stream);
+
 /* Scratch bytes mgr_rmsnorm_bwd needs for this problem on the current device (per-CTA fp32 partial
  * sums of dW). Returns 0 on invalid arguments. Host-only; no reference counterpart (the reference
  * accumulates dW with atomics into the output, src/rmsnorm_kernel.cu:315-325). */
@@ -214,6 +221,15 @@ int mgr_swiglu_act_bwd(void* dgv, const void* dh, const void* gv, int64_t m, int
  * the library GEMM it would have used with the reference).
  */
 int mgr_swiglu_fused_fwd(void* h, const void* x, const void* w12, int64_t m, int64_t d, int64_t f, int dtype, void* stream);
+
+/* mgr_swiglu_fused_fwd with a scale per row applied to both halves of the projection before the activation:
+ *   h[r, :] = silu(s_r * (x[r] w12[0:f]^T)) * (s_r * (x[r] w12[f:2f]^T)),   s = row_scale [m] fp32 (NULL = all ones).
+ * With s = mgr_rms_inv(x) and w12 = w12_original * w_norm (each column k scaled by the norm weight w_norm[k], folded
+ * once by the caller) this is the pre-norm block's `w12(norm(x))` + activation (megagemm/rmsnorm.py:74-75,
+ * megagemm/swiglu.py:167-168) without the normalised [m, d] tensor ever being written or read: an inference-time
+ * form (the folded weight is only valid while w_norm and w12 do not change). */
+int mgr_swiglu_fused_fwd_scaled(void* h, const void* x, const void* w12, const float* row_scale, int64_t m, int64_t d,
+                                int64_t f, int dtype, void* stream);
 int mgr_gemm_tn(void* c, const void* a, const void* b, int64_t m, int64_t n, int64_t k,
                 int64_t lda, int64_t ldb, int64_t ldc, int dtype, void* stream);
 

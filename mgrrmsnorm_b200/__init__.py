@@ -17,6 +17,7 @@ _EXPORTS = {
     "AddRMSNormFunction": "rmsnorm",
     "MegaGemmTriton": "swiglu",
     "MegaGemmFunction": "swiglu",
+    "PreNormSwiGLU": "swiglu",
 }
 
 

@@ -41,6 +41,7 @@ SIGNATURES = {
     "mgr_device_status": (_int, [_int]),
     "mgr_debug_poke_device_status": (_int, [_int, _int]),
     "mgr_rmsnorm_fwd": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _f32, _int, _vp]),
+    "mgr_rms_inv": (_int, [_vp, _vp, _i64, _i64, _f32, _int, _vp]),
     "mgr_rmsnorm_bwd_workspace_bytes": (_sz, [_i64, _i64, _int]),
     "mgr_rmsnorm_bwd": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp, _sz, _vp]),
     "mgr_rmsnorm_bwd_noalloc": (_int, [_vp, _vp, _vp, _vp, _vp, _vp, _vp, _i64, _i64, _int, _vp]),
@@ -49,6 +50,7 @@ SIGNATURES = {
     "mgr_swiglu_act_fwd": (_int, [_vp, _vp, _i64, _i64, _int, _vp]),
     "mgr_swiglu_act_bwd": (_int, [_vp, _vp, _vp, _i64, _i64, _int, _vp]),
     "mgr_swiglu_fused_fwd": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
+    "mgr_swiglu_fused_fwd_scaled": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "mgr_gemm_tn": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _int, _vp]),
     "mgr_gemm": (_int, [_vp, _vp, _vp, _i64, _i64, _i64, _i64, _i64, _i64, _int, _int, _int, _vp]),
     "mgr_swiglu_fused_bwd": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),

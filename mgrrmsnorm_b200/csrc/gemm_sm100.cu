@@ -193,9 +193,11 @@ __host__ __device__ constexpr TileCoord tile_coord(int t, int m_tiles, int n_til
     return TileCoord{mi * m_step, ni * n_step};
 }
 // Checked at compile time: the walk visits every tile of an m_tiles x n_tiles grid exactly once, for single CTAs
-// (128-row steps, 16 row tiles per band) and pairs (256-row steps, 8 per band), full and short last bands.
+// (128-row steps, 16 row tiles per band) and pairs (256-row steps, 8 per band), full and short last bands -- up to
+// 40 row tiles exhaustively, and at the row-tile counts of the 16384-token block (128 single / 64 paired) and
+// their neighbours.
 constexpr bool tile_walk_visits_each_tile_once(int m_tiles, int n_tiles, int m_step) {
-    bool seen[48 * 16] = {};
+    bool seen[136 * 16] = {};
     for (int t = 0; t < m_tiles * n_tiles; ++t) {
         const TileCoord c = tile_coord(t, m_tiles, n_tiles, kBN, m_step);
         if (c.m0 < 0 || c.n0 < 0 || c.m0 % m_step != 0 || c.n0 % kBN != 0) return false;
@@ -211,6 +213,11 @@ constexpr bool tile_walks_ok() {
         for (int m = 1; m <= 40; ++m)
             for (int n = 1; n <= 13; n += 3)
                 if (!tile_walk_visits_each_tile_once(m, n, steps[s])) return false;
+    const int big[8] = {63, 64, 65, 96, 127, 128, 129, 136};
+    for (int s = 0; s < 2; ++s)
+        for (int i = 0; i < 8; ++i)
+            for (int n = 1; n <= 15; n += 7)
+                if (!tile_walk_visits_each_tile_once(big[i], n, steps[s])) return false;
     return true;
 }
 static_assert(tile_walks_ok(), "the band-wise tile walk skips or repeats a tile");
@@ -220,7 +227,9 @@ static_assert(tile_walks_ok(), "the band-wise tile walk skips or repeats a tile"
 //   B: K-major = stored [Nb, K] (tmB box 64(K) x 128); MN-major = stored [K, Nb] (tmB box 64(N) x 64(K)).
 // kEpiPlain    : C[M, n_out] = acc; a tile covers 256 columns of C (B rows n0 .. n0+255).
 // kEpiSwiglu   : B K-major = [gate rows | value rows] of n_out rows each. C[M, n_out] = silu(G) * V; a tile
-//                covers 128 columns of C (B rows n0.. and n_out+n0..).
+//                covers 128 columns of C (B rows n0.. and n_out+n0..). With row_scale != NULL both halves of row r
+//                are multiplied by row_scale[r] first: G = s_r (x w_g^T), V = s_r (x w_v^T) -- an RMSNorm in front
+//                of the projection whose weight has been folded into w12 (s_r = 1 / rms of row r).
 // kEpiSwigluBwd: same tile; aux = dh [M, n_out]. C = [d_gate | d_val] of shape [M, 2 n_out]:
 //                d_val = dh * G * sig(G), d_gate = dh * V * sig(G) * (1 + G * (1 - sig(G))).
 // kEpiSwigluSave: kEpiSwiglu that also stores the projection, rounded to T, in C2 = [G | V] of shape
@@ -231,7 +240,7 @@ template <int EPI, bool A_MN, bool B_MN, int CG, typename T, int BN = kBN>
 __global__ void __launch_bounds__(kGemmThreads, 1)
 gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUtensorMap tmB, T* __restrict__ C,
             T* __restrict__ C2, const T* __restrict__ aux, int M, int n_out, int K, int64_t ldc, int64_t ld_aux,
-            uint32_t a_box_bytes,
+            uint32_t a_box_bytes, const float* __restrict__ row_scale,
             int* __restrict__ status) {
     static_assert(n_step_of(EPI, BN) == BN || !B_MN, "the gate/value split reads w12 K-major");
     static_assert(BN == kBN || ((BN == kBNSmall || BN == kBNTiny) && CG == 1 && !A_MN && !B_MN && (EPI == kEpiPlain || EPI == kEpiSwiglu)),
@@ -422,6 +431,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             const int row = tc.m0 + static_cast<int>(cta_rank) * kBM + q * 32 + lane;
             const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * BN;
             T* crow = C + static_cast<int64_t>(row) * ldc + tc.n0;
+            [[maybe_unused]] float rs = 1.0f;                 // kEpiSwiglu: this row's scale
+            if constexpr (EPI == kEpiSwiglu) {
+                if (row_scale != nullptr && row < M) rs = __ldg(row_scale + row);
+            }
             [[maybe_unused]] uint4 gp_next[4], vp_next[4];   // kEpiDhDgv: packets requested one chunk ahead
             if constexpr (BN == kBNTiny && EPI == kEpiSwiglu) {
                 // one 32-column read holds the whole accumulator: 16 gate columns, then the 16 value columns
@@ -432,8 +445,8 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     uint32_t out[8];
 #pragma unroll
                     for (int j = 0; j < 8; ++j)
-                        out[j] = pack2<T>(silu_mul(__uint_as_float(a[2 * j]), __uint_as_float(a[16 + 2 * j])),
-                                          silu_mul(__uint_as_float(a[2 * j + 1]), __uint_as_float(a[16 + 2 * j + 1])));
+                        out[j] = pack2<T>(silu_mul(rs * __uint_as_float(a[2 * j]), rs * __uint_as_float(a[16 + 2 * j])),
+                                          silu_mul(rs * __uint_as_float(a[2 * j + 1]), rs * __uint_as_float(a[16 + 2 * j + 1])));
                     if (row < M) {
 #pragma unroll
                         for (int j = 0; j < 2; ++j)
@@ -568,10 +581,17 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                         ptx::tmem_ld_32x32(t_row + c * 32, g);
                         ptx::tmem_ld_32x32(t_row + BN / 2 + c * 32, v);
                         ptx::tmem_ld_wait();
+                        if constexpr (EPI == kEpiSwiglu) {
 #pragma unroll
-                        for (int j = 0; j < 16; ++j)
-                            out[j] = pack2<T>(silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(v[2 * j])),
-                                              silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(v[2 * j + 1])));
+                            for (int j = 0; j < 16; ++j)
+                                out[j] = pack2<T>(silu_mul(rs * __uint_as_float(g[2 * j]), rs * __uint_as_float(v[2 * j])),
+                                                  silu_mul(rs * __uint_as_float(g[2 * j + 1]), rs * __uint_as_float(v[2 * j + 1])));
+                        } else {
+#pragma unroll
+                            for (int j = 0; j < 16; ++j)
+                                out[j] = pack2<T>(silu_mul(__uint_as_float(g[2 * j]), __uint_as_float(v[2 * j])),
+                                                  silu_mul(__uint_as_float(g[2 * j + 1]), __uint_as_float(v[2 * j + 1])));
+                        }
                         if constexpr (EPI == kEpiSwigluSave) {
                             if (row < M) {
                                 T* prow = C2 + static_cast<int64_t>(row) * ld_aux + tc.n0 + c * 32;
@@ -696,6 +716,7 @@ struct GemmArgs {
     int64_t b_rows;            // logical rows of B (n_out, or 2 n_out for the gate|value split)
     int64_t lda, ldb, ldc, ld_aux;
     int dtype;
+    const float* row_scale = nullptr;   // kEpiSwiglu only
 };
 
 // SMs the GEMM kernels may occupy (0 = all). A caller that overlaps a collective with a GEMM lowers it so
@@ -771,7 +792,7 @@ int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     cfg.attrs = at;
     cfg.numAttrs = na;
     if (cudaLaunchKernelEx(&cfg, gemm_kernel<EPI, A_MN, B_MN, CG, T, BN>, tmA, tmB, c, c2, aux, m, n_out, k, g.ldc, g.ld_aux,
-                           a_box_bytes, status) != cudaSuccess) {
+                           a_box_bytes, g.row_scale, status) != cudaSuccess) {
         (void)cudaGetLastError();
         return MGR_ERR_LAUNCH_FAILED;
     }
@@ -892,17 +913,23 @@ extern "C" int mgr_gemm_tn(void* c, const void* a, const void* b, int64_t m, int
     return mgr_gemm(c, a, b, m, n, k, lda, ldb, ldc, 0, 0, dtype, stream);
 }
 
-extern "C" int mgr_swiglu_fused_fwd(void* h, const void* x, const void* w12, int64_t m, int64_t d, int64_t f, int dtype,
-                                    void* stream) {
+extern "C" int mgr_swiglu_fused_fwd_scaled(void* h, const void* x, const void* w12, const float* row_scale, int64_t m, int64_t d,
+                                           int64_t f, int dtype, void* stream) {
     int st = gemm_check(m, f, d, dtype);
     if (st != MGR_OK) return st;
     if (m == 0) return MGR_OK;
     if (h == nullptr || x == nullptr || w12 == nullptr) return MGR_ERR_NULL_PTR;
-    if (!aligned_to(h, 16) || !aligned_to(x, 16) || !aligned_to(w12, 16)) return MGR_ERR_MISALIGNED;
+    if (!aligned_to(h, 16) || !aligned_to(x, 16) || !aligned_to(w12, 16) || !aligned_to(row_scale, 4)) return MGR_ERR_MISALIGNED;
     const DeviceInfo di = current_device_info();
     if (di.status != MGR_OK) return di.status;
-    const GemmArgs g{nullptr, h, x, w12, nullptr, m, f, d, 2 * f, d, d, f, 0, dtype};
+    GemmArgs g{nullptr, h, x, w12, nullptr, m, f, d, 2 * f, d, d, f, 0, dtype};
+    g.row_scale = row_scale;
     return launch_gemm_dtype<kEpiSwiglu, false, false>(g, di, static_cast<cudaStream_t>(stream));
+}
+
+extern "C" int mgr_swiglu_fused_fwd(void* h, const void* x, const void* w12, int64_t m, int64_t d, int64_t f, int dtype,
+                                    void* stream) {
+    return mgr_swiglu_fused_fwd_scaled(h, x, w12, nullptr, m, d, f, dtype, stream);
 }
 
 extern "C" int mgr_swiglu_fused_bwd(void* dgv, const void* dh, const void* x, const void* w12, int64_t m, int64_t d,

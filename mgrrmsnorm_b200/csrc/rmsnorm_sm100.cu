@@ -126,8 +126,8 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
         }
         ss = row_sum<TPR>(ss, red, buf, group);
         const float inv = 1.0f / sqrtf(ss * inv_cols + eps);
-        if (live) {
-            if (t == 0 && inv_rms != nullptr) inv_rms[r] = inv;
+        if (live && t == 0 && inv_rms != nullptr) inv_rms[r] = inv;
+        if (live && y != nullptr) {   // y == NULL: only the row scales are wanted (mgr_rms_inv)
             uint4* yr = reinterpret_cast<uint4*>(y + r * static_cast<int64_t>(cols));
 #pragma unroll
             for (int k = 0; k < VPT; ++k) {
@@ -686,6 +686,7 @@ rms_fwd_scalar(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
         ss = block_sum_256(ss, red);
         const float inv = 1.0f / sqrtf(ss * inv_cols + eps);
         if (threadIdx.x == 0 && inv_rms != nullptr) inv_rms[r] = inv;
+        if (y == nullptr) continue;   // only the row scales are wanted
         for (int64_t j = threadIdx.x; j < cols; j += 256)
             yr[j] = from_f32<T>((to_f32(xr[j]) * inv) * to_f32(w[j]));
     }
@@ -747,11 +748,12 @@ struct RegShape {
 //             5120: 0.77 / 0.87   6144: 0.82 / 0.93   7168: 0.70 / 0.97  -- one row per pass of a 320-448 thread
 //             CTA with two packets per thread keeps too little in flight per barrier; the forward stays with {256,4}
 // ({768,2} for 12288 lost both ways, 0.53 / 0.85 and 0.70 / 0.73, and is not built.)
-// fat_bwd, measured on B200 (bf16, 2^29 elements, fraction of the copy bandwidth, fat / thin): warp-per-row shapes
-// (16 independent warps in one CTA, no barrier in the row loop) 0.98 / 0.90 at hidden 1024; {512,4} 0.84 / 0.82 at
-// hidden 16384. The other shapes keep one CTA per row group: their fat forms need a register or two more than the
-// 64 (128) they are held to and lose more to spills than the fewer partial rows give back (hidden 4096: 0.67 / 0.90;
-// 8192: 0.88 / 0.93).
+// fat_bwd, measured on B200 (2^29 elements, fraction of the copy bandwidth, fat / thin): warp-per-row shapes (16
+// independent warps in one CTA, no barrier in the row loop) 0.98 / 0.90 at bf16 hidden 1024 and 0.98 / 0.80 at fp32
+// hidden 128, equal elsewhere; {512,4} 0.84 / 0.82 at bf16 hidden 16384, 0.96 / 0.95 at fp32 hidden 8192. The other
+// shapes keep one CTA per row group: their fat forms need a few registers more than the 64 (128) they are held to
+// and lose more to spills than the fewer partial rows give back (bf16 hidden 4096: 0.67 / 0.90; 8192: 0.88 / 0.93;
+// fp32 hidden 1024: 0.95 / 1.00).
 constexpr RegShape kRegShapes[] = {{32, 1, true, true, true},     {32, 2, true, true, true},    {32, 4, true, true, true},
                                    {128, 2, true, true, false},   {128, 4, true, true, false},  {256, 4, true, true, false},
                                    {512, 4, true, true, true},    {1024, 4, true, true, false}, {256, 2, true, true, false},
@@ -848,10 +850,13 @@ struct RegKernels {
     static constexpr int G = RegGeom<TPR>::kGroups;
     static constexpr int BWD_BLOCK = BwdGeom<TPR, VPT>::kBlock;
     static constexpr int BWD_G = BwdGeom<TPR, VPT>::kGroups;
-    // which backward kernel this shape runs: the table's choice unless MGR_RMSNORM_BWD_FAT pins it
-    static bool fat_bwd() {
+    // Which backward kernel this problem runs: the table's choice unless MGR_RMSNORM_BWD_FAT pins it. A problem with
+    // too few rows to give every group of every fat CTA a few of them stays with one CTA per row group (2048 x 512
+    // bf16: 5.1 us against 5.4 us).
+    static bool fat_bwd(int64_t rows, const DeviceInfo& di) {
         const int pinned = overrides().bwd_fat;
-        return pinned >= 0 ? pinned != 0 : kRegShapes[I].fat_bwd;
+        if (pinned >= 0) return pinned != 0;
+        return kRegShapes[I].fat_bwd && rows >= 4ll * BWD_G * di.sm_count;
     }
 
     static int64_t fwd_grid(int64_t rows, const DeviceInfo& di) {
@@ -863,7 +868,7 @@ struct RegKernels {
     static int64_t bwd_grid(int64_t rows, const DeviceInfo& di) {
         static std::atomic<int> occ[kMaxDevices];
         static std::atomic<int> occ_fat[kMaxDevices];
-        if (fat_bwd()) {
+        if (fat_bwd(rows, di)) {
             const int64_t ngroups = (rows + BWD_G - 1) / BWD_G;
             const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_bwd_fat<T, TPR, VPT, ADD>, BWD_BLOCK, occ_fat, di.device);
             return ngroups < cap ? ngroups : cap;
@@ -877,8 +882,8 @@ struct RegKernels {
         rms_fwd_reg<T, TPR, VPT, ADD><<<static_cast<unsigned>(fwd_grid(rows, di)), BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps, res, h_out);
     }
     static void bwd(T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv, int64_t rows,
-                    int cols, int64_t grid, cudaStream_t s, const T* dres) {
-        if (fat_bwd())
+                    int cols, int64_t grid, const DeviceInfo& di, cudaStream_t s, const T* dres) {
+        if (fat_bwd(rows, di))
             rms_bwd_fat<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BWD_BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres);
         else
             rms_bwd_reg<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres);
@@ -903,12 +908,12 @@ struct RegDispatch {
         return 0;
     }
     static void bwd(int shape, T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv,
-                    int64_t rows, int cols, int64_t grid, cudaStream_t s, const T* dres = nullptr) {
+                    int64_t rows, int cols, int64_t grid, const DeviceInfo& di, cudaStream_t s, const T* dres = nullptr) {
         if (shape == I) {
-            if (dres != nullptr) RegKernels<T, I, true>::bwd(dx, ws, dy, x, w, inv, rows, cols, grid, s, dres);
-            else RegKernels<T, I, false>::bwd(dx, ws, dy, x, w, inv, rows, cols, grid, s, nullptr);
+            if (dres != nullptr) RegKernels<T, I, true>::bwd(dx, ws, dy, x, w, inv, rows, cols, grid, di, s, dres);
+            else RegKernels<T, I, false>::bwd(dx, ws, dy, x, w, inv, rows, cols, grid, di, s, nullptr);
         } else if constexpr (I + 1 < kNumRegShapes) {
-            RegDispatch<T, I + 1>::bwd(shape, dx, ws, dy, x, w, inv, rows, cols, grid, s, dres);
+            RegDispatch<T, I + 1>::bwd(shape, dx, ws, dy, x, w, inv, rows, cols, grid, di, s, dres);
         }
     }
 };
@@ -1056,7 +1061,7 @@ int fwd_typed(void* y, float* inv, const void* x, const void* w, int64_t rows, i
     const bool add = res != nullptr;   // the residual-add variants exist in the register and scalar families
     const bool packets = forced != Path::kScalar && cols % VEC == 0 && aligned_to(y, 16) && aligned_to(x, 16) && aligned_to(w, 16) &&
                          aligned_to(res, 16) && aligned_to(h_out, 16);
-    if (!add && packets && forced != Path::kReg && (forced == Path::kRing || prefer_ring_fwd(rows, cols, sizeof(T), di))) {
+    if (!add && y != nullptr && packets && forced != Path::kReg && (forced == Path::kRing || prefer_ring_fwd(rows, cols, sizeof(T), di))) {
         const int st = fwd_ring_try<T>(static_cast<T*>(y), inv, static_cast<const T*>(x), static_cast<const T*>(w), rows, cols, eps, di, s);
         if (st <= 0) return st;
     }
@@ -1119,7 +1124,7 @@ int bwd_typed(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, 
         if (shape >= 0) {
             P = RegDispatch<T>::bwd_grid(shape, rows, di, add);
             RegDispatch<T>::bwd(shape, static_cast<T*>(dx), ws, static_cast<const T*>(dy), static_cast<const T*>(x),
-                                static_cast<const T*>(w), inv, rows, static_cast<int>(cols), P, s, static_cast<const T*>(dres));
+                                static_cast<const T*>(w), inv, rows, static_cast<int>(cols), P, di, s, static_cast<const T*>(dres));
         } else {
             P = rows < kScalarDwSlices ? rows : kScalarDwSlices;
             if (add)
@@ -1183,11 +1188,18 @@ namespace mgr {
 namespace {
 // Shared by the plain and the residual-add forward; `add` says which (then res and h_out are required).
 int fwd_entry(void* y, float* inv_rms, const void* x, const void* w, int64_t rows, int64_t cols, float eps, int dtype,
-              void* stream, bool add, const void* res, void* h_out) {
+              void* stream, bool add, const void* res, void* h_out, bool inv_only = false) {
     int st = check_common(rows, cols, dtype);
     if (st != MGR_OK) return st;
     if (rows == 0) return MGR_OK;
-    if (y == nullptr || x == nullptr || w == nullptr) return MGR_ERR_NULL_PTR;
+    if (inv_only) {            // no output tensor and no weight: the kernels skip the stores, and read x as the "weight"
+        if (inv_rms == nullptr) return MGR_ERR_NULL_PTR;
+        y = nullptr;
+        w = x;
+    } else if (y == nullptr) {
+        return MGR_ERR_NULL_PTR;
+    }
+    if (x == nullptr || w == nullptr) return MGR_ERR_NULL_PTR;
     if (add && (res == nullptr || h_out == nullptr)) return MGR_ERR_NULL_PTR;
     const size_t es = dtype_size(dtype);
     if (!aligned_to(y, es) || !aligned_to(x, es) || !aligned_to(w, es) || !aligned_to(inv_rms, 4)) return MGR_ERR_MISALIGNED;
@@ -1208,6 +1220,10 @@ int fwd_entry(void* y, float* inv_rms, const void* x, const void* w, int64_t row
 extern "C" int mgr_rmsnorm_fwd(void* y, float* inv_rms, const void* x, const void* w, int64_t rows, int64_t cols,
                                float eps, int dtype, void* stream) {
     return fwd_entry(y, inv_rms, x, w, rows, cols, eps, dtype, stream, false, nullptr, nullptr);
+}
+
+extern "C" int mgr_rms_inv(float* inv_rms, const void* x, int64_t rows, int64_t cols, float eps, int dtype, void* stream) {
+    return fwd_entry(nullptr, inv_rms, x, nullptr, rows, cols, eps, dtype, stream, false, nullptr, nullptr, true);
 }
 
 extern "C" int mgr_add_rmsnorm_fwd(void* y, void* h, float* inv_rms, const void* x, const void* residual, const void* w,

@@ -16,6 +16,9 @@ The arithmetic is the library's (C ABI); torch supplies streams, events and memo
 """
 from __future__ import annotations
 
+import os
+from pathlib import Path
+
 import torch
 
 from . import _capi
@@ -97,3 +100,50 @@ class HostRMSNormPipeline:
                 slot["drained"].record(self.s_out)
         main.wait_stream(self.s_out)
         return self.dw_sum if return_f32 else self.dw_sum.to(self.dtype)
+
+
+# ---------------------------------------------------------------------------------------------------
+# where the host side of a rank runs
+# ---------------------------------------------------------------------------------------------------
+
+def _cpulist(text: str) -> set[int]:
+    cpus: set[int] = set()
+    for part in text.strip().split(","):
+        if not part:
+            continue
+        lo, _, hi = part.partition("-")
+        cpus.update(range(int(lo), int(hi or lo) + 1))
+    return cpus
+
+
+def gpu_numa_node(device) -> int | None:
+    """NUMA node the GPU's PCIe slot hangs off (sysfs), or None where the platform does not say."""
+    try:
+        p = torch.cuda.get_device_properties(device)
+        pci = f"{p.pci_domain_id:04x}:{p.pci_bus_id:02x}:{p.pci_device_id:02x}.0"
+        node = int((Path("/sys/bus/pci/devices") / pci / "numa_node").read_text())
+        return node if node >= 0 else None
+    except (OSError, ValueError, AttributeError, RuntimeError):
+        return None
+
+
+def place_near_gpu(device) -> dict:
+    """Restricts the calling process to the CPUs of the GPU's NUMA node (where the scheduler allows any of
+    them), so that pinned buffers allocated afterwards come from the memory next to that GPU's PCIe root and
+    the copies do not cross the socket interconnect. With several ranks on one host this is what keeps each
+    rank's host traffic on its own side of the machine. Returns what was found and done; never raises."""
+    info = {"gpu_numa_node": gpu_numa_node(device), "bound": False}
+    try:
+        nodes = sorted(int(d.name[4:]) for d in Path("/sys/devices/system/node").glob("node[0-9]*"))
+        info["numa_nodes"] = len(nodes)
+        allowed = os.sched_getaffinity(0)
+        info["cpus_allowed"] = len(allowed)
+        if info["gpu_numa_node"] is not None and len(nodes) > 1:
+            local = _cpulist((Path("/sys/devices/system/node") / f"node{info['gpu_numa_node']}" / "cpulist").read_text()) & allowed
+            if local and local != allowed:
+                os.sched_setaffinity(0, local)
+                info["bound"] = True
+                info["cpus_allowed"] = len(local)
+    except (OSError, ValueError, AttributeError):
+        pass
+    return info

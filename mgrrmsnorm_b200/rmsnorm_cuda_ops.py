@@ -83,6 +83,22 @@ def rmsnorm_forward(input: torch.Tensor, weight: torch.Tensor, epsilon: float):
     return [output, inv_rms]
 
 
+def rms_inv(input: torch.Tensor, epsilon: float) -> torch.Tensor:
+    """inv_rms[R] (fp32) of a 2-D tensor alone: the forward's row scales without its output (one read of the
+    input). Same bits as the inv_rms rmsnorm_forward returns."""
+    _check_input(input, "input")
+    if input.dim() != 2:
+        raise RuntimeError("Input must be 2D")
+    rows, cols = input.shape
+    code = _dtype_code(input, "")
+    L = _capi.lib()
+    with torch.cuda.device(input.device):
+        inv_rms = torch.empty((rows,), dtype=torch.float32, device=input.device)
+        st = L.mgr_rms_inv(inv_rms.data_ptr(), input.data_ptr(), rows, cols, float(epsilon), code, _stream_ptr(input.device))
+    _capi.check("RMSNorm row-scale CUDA kernel", st)
+    return inv_rms
+
+
 def rmsnorm_backward_full(grad_output: torch.Tensor, input: torch.Tensor, weight: torch.Tensor,
                           inv_rms: torch.Tensor, want_dw_f32: bool = False):
     """[grad_input, grad_weight, grad_weight_fp32 | None]; the fp32 sum is what a row-sharded caller
@@ -252,12 +268,18 @@ def _gemm_ok(*tensors: torch.Tensor) -> bool:
     return True
 
 
-def swiglu_fused_forward(x: torch.Tensor, w12: torch.Tensor, hidden_dim: int, out: torch.Tensor | None = None) -> torch.Tensor:
+def swiglu_fused_forward(x: torch.Tensor, w12: torch.Tensor, hidden_dim: int, out: torch.Tensor | None = None,
+                         row_scale: torch.Tensor | None = None) -> torch.Tensor:
     """h[M, hidden] = silu(x w12[:hidden]^T) * (x w12[hidden:]^T) in one tensor-core kernel: what
     `self.w12(x)` followed by MegaGemmFunction computes (megagemm/swiglu.py:167-168), without the
-    [M, 2*hidden] intermediate."""
+    [M, 2*hidden] intermediate. `row_scale` [M] fp32, if given, multiplies both halves of row r before the
+    activation (an RMSNorm in front whose weight has been folded into w12: see swiglu.PreNormSwiGLU)."""
     _check_input(x, "x")
     _check_input(w12, "w12")
+    if row_scale is not None:
+        _check_input(row_scale, "row_scale")
+        if row_scale.dtype != torch.float32 or tuple(row_scale.shape) != (x.shape[0],) or row_scale.device != x.device:
+            raise RuntimeError("row_scale must be a float32 tensor [M] on the operands' device")
     if x.dim() != 2 or w12.dim() != 2 or w12.shape[0] != 2 * hidden_dim or w12.shape[1] != x.shape[1]:
         raise RuntimeError("expected x [M, d_model] and w12 [2*hidden_dim, d_model]")
     if x.dtype != w12.dtype or x.device != w12.device:
@@ -267,7 +289,9 @@ def swiglu_fused_forward(x: torch.Tensor, w12: torch.Tensor, hidden_dim: int, ou
     L = _capi.lib()
     with torch.cuda.device(x.device):
         h = _out_or_new(out, (m, hidden_dim), x, "out")
-        st = L.mgr_swiglu_fused_fwd(h.data_ptr(), x.data_ptr(), w12.data_ptr(), m, d, hidden_dim, code, _stream_ptr(x.device))
+        st = L.mgr_swiglu_fused_fwd_scaled(h.data_ptr(), x.data_ptr(), w12.data_ptr(),
+                                           row_scale.data_ptr() if row_scale is not None else None, m, d, hidden_dim, code,
+                                           _stream_ptr(x.device))
     _capi.check("fused SwiGLU projection kernel", st)
     return h
 
@@ -414,7 +438,7 @@ def device_status(clear: bool = True) -> None:
 # route selection
 # ---------------------------------------------------------------------------------------------------
 
-ENTRY_POINTS = ("rmsnorm_forward", "rmsnorm_backward", "rmsnorm_backward_full", "add_rmsnorm_forward", "add_rmsnorm_backward",
+ENTRY_POINTS = ("rmsnorm_forward", "rms_inv", "rmsnorm_backward", "rmsnorm_backward_full", "add_rmsnorm_forward", "add_rmsnorm_backward",
                 "swiglu_act_forward", "swiglu_act_backward", "swiglu_fused_forward", "swiglu_fused_forward_save", "linear_tn",
                 "gemm", "swiglu_fused_backward", "swiglu_dh_dgv")
 ctypes_impl = {name: globals()[name] for name in ENTRY_POINTS}

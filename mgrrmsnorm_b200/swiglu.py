@@ -135,3 +135,51 @@ class MegaGemmTriton(nn.Module):
 
     def extra_repr(self) -> str:
         return f"d_model={self.w12.in_features}, hidden={self.hidden} (sm_100a)"
+
+
+class PreNormSwiGLU(nn.Module):
+    """The pre-norm MLP block y = mlp(norm(x)) with the norm folded into the projection at inference time.
+
+    A user of the reference writes `mlp(norm(x))`: RMSNorm writes the normalised [M, D] tensor
+    (megagemm/rmsnorm.py:74-75) and `self.w12` reads it back (megagemm/swiglu.py:167). Here, when no gradient
+    is wanted, that tensor never exists: since norm(x)[r, k] = x[r, k] * inv_rms[r] * w[k],
+
+        w12(norm(x))[r, n] = inv_rms[r] * sum_k x[r, k] * (w[k] * w12[n, k]),
+
+    so the norm weight is folded into the columns of w12 once (kept until either parameter changes), one
+    light kernel reads x for the row scales (rms_inv), and the projection kernel multiplies its accumulator
+    rows by inv_rms[r] before the activation. With gradients enabled the block runs as the two modules it is
+    made of (the folded weight would have to be rebuilt every step, which costs more than it saves).
+
+    Results differ from the two-step path by rounding only: there norm(x) is rounded to the tensor dtype
+    before the GEMM, here w * w12 is.
+    """
+
+    def __init__(self, norm: nn.Module, mlp: MegaGemmTriton):
+        super().__init__()
+        self.norm = norm
+        self.mlp = mlp
+        self._folded = None
+        self._folded_key = None
+
+    def folded_w12(self) -> torch.Tensor:
+        w, w12 = self.norm.weight, self.mlp.w12.weight
+        key = (w.data_ptr(), w._version, w12.data_ptr(), w12._version, w12.dtype, w12.device)
+        if self._folded is None or self._folded_key != key:
+            with torch.no_grad():
+                self._folded = (w12.float() * w.float().unsqueeze(0)).to(w12.dtype).contiguous()
+            self._folded_key = key
+        return self._folded
+
+    def forward(self, x: torch.Tensor) -> torch.Tensor:
+        w12, w3 = self.mlp.w12.weight, self.mlp.w3.weight
+        fused = (not torch.is_grad_enabled() and x.is_cuda and x.dtype == w12.dtype and x.numel() > 0
+                 and x.shape[-1] % 8 == 0 and x.is_contiguous() and rmsnorm_cuda_ops._gemm_ok(w12, w3)
+                 and self.norm.weight.dtype == w12.dtype)
+        if not fused:
+            return self.mlp(self.norm(x))
+        x2d = x.view(-1, x.shape[-1])
+        inv = rmsnorm_cuda_ops.rms_inv(x2d, self.norm.epsilon)
+        h = rmsnorm_cuda_ops.swiglu_fused_forward(x2d, self.folded_w12(), self.mlp.hidden, row_scale=inv)
+        y = rmsnorm_cuda_ops.linear_tn(h, w3)
+        return y.view(x.shape[:-1] + (w3.shape[0],))

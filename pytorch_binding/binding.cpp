@@ -84,6 +84,18 @@ std::vector<Tensor> rmsnorm_forward(const Tensor& input, const Tensor& weight, d
     return {output, inv_rms};
 }
 
+// The forward's row scales alone (one read of the input); same bits as the inv_rms rmsnorm_forward returns.
+Tensor rms_inv(const Tensor& input, double epsilon) {
+    check_input(input, "input");
+    TORCH_CHECK(input.dim() == 2, "Input must be 2D");
+    const int code = dtype_code(input, "");
+    c10::cuda::CUDAGuard guard(input.device());
+    Tensor inv_rms = at::empty({input.size(0)}, input.options().dtype(at::kFloat));
+    check_status("RMSNorm row-scale CUDA kernel", mgr_rms_inv(inv_rms.data_ptr<float>(), input.data_ptr(), input.size(0), input.size(1),
+                                                            static_cast<float>(epsilon), code, current_stream()));
+    return inv_rms;
+}
+
 // [grad_input, grad_weight, grad_weight_fp32 or None]; the fp32 sum is what a row-sharded caller all-reduces
 // across ranks before the one rounding.
 std::vector<std::optional<Tensor>> rmsnorm_backward_full(const Tensor& grad_output, const Tensor& input, const Tensor& weight,
@@ -214,14 +226,23 @@ void check_projection_operands(const Tensor& x, const Tensor& w12, int64_t hidde
     TORCH_CHECK(x.scalar_type() == w12.scalar_type() && x.device() == w12.device(), "x and w12 must share dtype and device");
 }
 
-Tensor swiglu_fused_forward(const Tensor& x, const Tensor& w12, int64_t hidden_dim, const std::optional<Tensor>& out) {
+Tensor swiglu_fused_forward(const Tensor& x, const Tensor& w12, int64_t hidden_dim, const std::optional<Tensor>& out,
+                            const std::optional<Tensor>& row_scale) {
     check_projection_operands(x, w12, hidden_dim);
     const int code = dtype_code(x, "");
     const int64_t m = x.size(0), d = x.size(1);
+    const float* scale = nullptr;
+    if (row_scale.has_value()) {
+        check_input(*row_scale, "row_scale");
+        TORCH_CHECK(row_scale->scalar_type() == at::kFloat && row_scale->dim() == 1 && row_scale->size(0) == m &&
+                        row_scale->device() == x.device(),
+                    "row_scale must be a float32 tensor [M] on the operands' device");
+        scale = row_scale->data_ptr<float>();
+    }
     c10::cuda::CUDAGuard guard(x.device());
     Tensor h = out_or_new(out, {m, hidden_dim}, x, "out");
     check_status("fused SwiGLU projection kernel",
-                 mgr_swiglu_fused_fwd(h.data_ptr(), x.data_ptr(), w12.data_ptr(), m, d, hidden_dim, code, current_stream()));
+                 mgr_swiglu_fused_fwd_scaled(h.data_ptr(), x.data_ptr(), w12.data_ptr(), scale, m, d, hidden_dim, code, current_stream()));
     return h;
 }
 
@@ -319,7 +340,9 @@ PYBIND11_MODULE(TORCH_EXTENSION_NAME, m) {
           py::arg("want_dw_f32") = false);
     m.def("swiglu_act_forward", &swiglu_act_forward, py::arg("w12_out"), py::arg("hidden_dim"));
     m.def("swiglu_act_backward", &swiglu_act_backward, py::arg("grad_out"), py::arg("w12_out"), py::arg("hidden_dim"));
-    m.def("swiglu_fused_forward", &swiglu_fused_forward, py::arg("x"), py::arg("w12"), py::arg("hidden_dim"), py::arg("out") = py::none());
+    m.def("swiglu_fused_forward", &swiglu_fused_forward, py::arg("x"), py::arg("w12"), py::arg("hidden_dim"), py::arg("out") = py::none(),
+          py::arg("row_scale") = py::none());
+    m.def("rms_inv", &rms_inv, "inv_rms [rows] fp32 of a 2-D tensor (the forward's row scales alone)", py::arg("input"), py::arg("epsilon"));
     m.def("swiglu_fused_forward_save", &swiglu_fused_forward_save, py::arg("x"), py::arg("w12"), py::arg("hidden_dim"),
           py::arg("out_h") = py::none(), py::arg("out_gv") = py::none());
     m.def("linear_tn", &linear_tn, py::arg("a"), py::arg("b"), py::arg("out") = py::none());

@@ -9,7 +9,8 @@ def test_package_exports_are_lazy_and_complete():
     import mgrrmsnorm_b200 as pkg
 
     reference_names = {"RMSNorm", "RMSNormFunction", "MegaGemmTriton", "MegaGemmFunction", "__version__"}
-    added = {"AddRMSNorm", "AddRMSNormFunction"}   # residual add fused into the norm; not in the reference
+    # not in the reference: the residual add fused into the norm, and the norm folded into the projection
+    added = {"AddRMSNorm", "AddRMSNormFunction", "PreNormSwiGLU"}
     assert set(pkg.__all__) == reference_names | added
     for name in sorted((reference_names | added) - {"__version__"}):
         assert getattr(pkg, name).__name__ == name

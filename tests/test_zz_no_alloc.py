@@ -82,3 +82,33 @@ def test_noalloc_backward_refuses_what_does_not_fit(built_lib):
     assert L.mgr_rmsnorm_bwd_noalloc(p, p, None, p, p, p, p, -1, 64, _capi.MGR_F32, None) == _capi.MGR_ERR_BAD_SHAPE
     assert L.mgr_rmsnorm_bwd_noalloc(p, p, None, p, p, p, p, 4, 64, 9, None) == _capi.MGR_ERR_BAD_DTYPE
     assert L.mgr_rmsnorm_bwd_noalloc(None, p, None, p, p, p, p, 4, 64, _capi.MGR_F32, None) == _capi.MGR_ERR_NULL_PTR
+
+
+def test_noalloc_backward_from_several_host_threads_one_call_at_a_time(built_lib):
+    """Host threads may share the entry point (its per-device address lookup is held in an atomic), but the
+    scratch array is one per GPU: a call is two launches that hand partial rows through it, so callers take
+    turns -- here under a lock, all on one stream. Every thread's results equal the regular entry point's."""
+    import threading
+
+    L = built_lib
+    shapes = [(700, 4096, "bf16"), (300, 8192, "f32"), (1000, 1024, "f16"), (129, 1000, "f32"), (2000, 2048, "bf16"), (64, 5120, "f16")]
+    turn = threading.Lock()
+    failures = []
+
+    def work(i):
+        rows, cols, dtype = shapes[i]
+        try:
+            for rep in range(3):
+                with turn:
+                    ref, got = both_backwards(L, rows, cols, dtype, seed=500 + 10 * i + rep)
+                assert_same(ref, got, dtype)
+        except Exception as e:  # noqa: BLE001 -- surfaced below; an exception in a thread would otherwise pass silently
+            failures.append((shapes[i], repr(e)))
+
+    threads = [threading.Thread(target=work, args=(i,)) for i in range(len(shapes))]
+    for t in threads:
+        t.start()
+    for t in threads:
+        t.join()
+    assert not failures, failures
+    assert L.mgr_device_status(1) == 0
