@@ -256,6 +256,15 @@ class RmsBuffers:
         nws = int(L.mgr_rmsnorm_bwd_workspace_bytes(rows, cols, self.code))
         self.ws = torch.empty(max(nws, 16), dtype=torch.uint8, device=device)
         self._fwd_args = self._bwd_args = None
+        self.dw_pairs = [(self.dw32, self.dw)]
+
+    def second_dw_pair(self):
+        """A second (dw_f32, dw) output pair, used alternately with the first when the cross-rank sum of dW runs off
+        the compute stream: the backward of step i+1 then writes other buffers than the ones step i's all-reduce
+        still reads, as the backward passes of two different layers (or micro-batches) do in a training loop."""
+        if len(self.dw_pairs) == 1:
+            self.dw_pairs.append((torch.empty_like(self.dw32), torch.empty_like(self.dw)))
+            self._fwd_args = None
 
     def _pointers(self):
         # device addresses looked up once per buffer set (they are re-read if a tensor is swapped): a 10 us kernel
@@ -266,6 +275,10 @@ class RmsBuffers:
             self._key = key
             self._fwd_args = (y, inv, x, w, self.rows, self.cols, EPS, self.code)
             self._bwd_args = (dx, dw, dw32, dy, x, w, inv, self.rows, self.cols, self.code, ws, self.ws.numel())
+            self._bwd_args_alt = None
+            if len(self.dw_pairs) > 1:
+                d32, d = self.dw_pairs[1]
+                self._bwd_args_alt = (dx, d.data_ptr(), d32.data_ptr(), dy, x, w, inv, self.rows, self.cols, self.code, ws, self.ws.numel())
 
     def freeze(self):
         """Fixes the argument lists (call after any tensor of the set has been replaced)."""
@@ -279,10 +292,10 @@ class RmsBuffers:
         if st:
             raise RuntimeError(f"mgr_rmsnorm_fwd status {st}")
 
-    def bwd(self, stream):
-        if self._bwd_args is None:
+    def bwd(self, stream, pair=0):
+        if self._bwd_args is None or self._fwd_args is None:
             self._pointers()
-        st = self.L.mgr_rmsnorm_bwd(*self._bwd_args, stream)
+        st = self.L.mgr_rmsnorm_bwd(*(self._bwd_args if pair == 0 else self._bwd_args_alt), stream)
         if st:
             raise RuntimeError(f"mgr_rmsnorm_bwd status {st}")
 
@@ -307,6 +320,9 @@ def time_device_resident(bufsets, steps, warmup, world, sampler=None, reduce="si
         from mgrrmsnorm_b200.sharding import AsyncDwReduce
 
         red = AsyncDwReduce(torch.cuda.current_device())
+        for b in bufsets:
+            b.second_dw_pair()
+    turn = [0]
 
     def step(b, evs=None):
         if evs:
@@ -314,13 +330,19 @@ def time_device_resident(bufsets, steps, warmup, world, sampler=None, reduce="si
         b.fwd(sp)
         if evs:
             evs[1].record(stream)
+        pair = 0
         if red is not None:
-            red.wait_for(b.dw32)                     # the previous all-reduce has finished with b.dw32
-        b.bwd(sp)
+            # two output pairs used alternately: this backward only waits for the all-reduce of TWO steps ago (the
+            # persistent forward kernel fills every SM, so the collective of the previous step may still be queued
+            # behind it; waiting for it here would put its latency back between forward and backward)
+            pair = turn[0] & 1
+            turn[0] += 1
+            red.wait_for(b.dw_pairs[pair][0])
+        b.bwd(sp, pair)
         if evs:
             evs[2].record(stream)
         if red is not None:
-            red.start(b.dw32, b.dw)
+            red.start(*b.dw_pairs[pair])
         elif inline:
             dist.all_reduce(b.dw32, op=dist.ReduceOp.SUM)
             b.dw.copy_(b.dw32)                       # the single rounding

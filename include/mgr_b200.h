@@ -153,9 +153,12 @@ int mgr_rmsnorm_bwd(void* dx, void* dw, float* dw_f32, const void* dy, const voi
  * synchronise the device and may fail once memory is fragmented. The call itself allocates nothing
  * (no cudaMalloc, no cudaFree, no allocating library routine).
  *   - Limit: problems whose mgr_rmsnorm_bwd_workspace_bytes(rows, cols, dtype) exceeds
- *     MGR_NOALLOC_SCRATCH_BYTES return MGR_ERR_TOO_LARGE before anything is launched (on a 148-SM B200
- *     every problem with cols <= 16384 fits, whatever the dtype and row count; fp16/bf16 rows of 32768
- *     columns, whose packet kernel writes 148 partial rows of 128 KiB, do not).
+ *     MGR_NOALLOC_SCRATCH_BYTES return MGR_ERR_TOO_LARGE ("dimension exceeds the supported maximum": here the
+ *     maximum is this scratch size) before anything is launched. The need is one fp32 row of `cols` per CTA of
+ *     the backward kernel, i.e. cols * 4 * (SM count x resident CTAs of the kernel chosen for that row length),
+ *     so it is a property of the device: on a 148-SM B200 every row length up to 16384 columns fits whatever
+ *     the dtype and row count (largest: 9.25 MiB at fp32 x 16384 columns; a test sweeps every multiple of 8);
+ *     fp16/bf16 rows of 32768 columns, whose kernels write 148 partial rows of 128 KiB, do not.
  *   - Every GPU whose context loads the library holds the array until the process ends.
  *   - The first call on a device looks up the array's device address (cudaGetSymbolAddress, once per
  *     device, with that device current). Make that first call before starting any stream capture.
@@ -265,17 +268,17 @@ int mgr_swiglu_fused_bwd(void* dgv, const void* dh, const void* x, const void* w
  *   dh = dy w3 (Linear(w3).backward) with _mg_swiglu_bwd_kernel (megagemm/swiglu.py:46-79) as its
  *   epilogue; dh stays in fp32 in tensor memory and is never written.
  */
+int mgr_swiglu_fused_fwd_save(void* h, void* gv, const void* x, const void* w12, int64_t m, int64_t d, int64_t f,
+                              int dtype, void* stream);
+int mgr_swiglu_dh_dgv(void* dgv, const void* dy, const void* w3, const void* gv, int64_t m, int64_t d, int64_t f,
+                      int dtype, void* stream);
+
 /* Limits the GEMM kernels of this process to `sms` SMs (0 = all of them); returns the previous limit.
  * The GEMM kernels are persistent (one CTA per SM), so a collective launched beside one finds no free SM
  * unless some are left out: a tensor-parallel caller lowers the limit around the GEMMs it overlaps with an
  * all-reduce and restores it afterwards. Host-side setting, read at each launch. No reference counterpart
  * (the reference has no distributed code). */
 int mgr_gemm_set_sm_limit(int sms);
-
-int mgr_swiglu_fused_fwd_save(void* h, void* gv, const void* x, const void* w12, int64_t m, int64_t d, int64_t f,
-                              int dtype, void* stream);
-int mgr_swiglu_dh_dgv(void* dgv, const void* dy, const void* w3, const void* gv, int64_t m, int64_t d, int64_t f,
-                      int dtype, void* stream);
 
 #ifdef __cplusplus
 }
