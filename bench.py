@@ -482,8 +482,12 @@ def graph_timed(sets, nb, peak_gbs, l2_note) -> dict:
         gf = graph_of(lambda b, sp: b.fwd(sp))
         gb = graph_of(lambda b, sp: b.bwd(sp))
         gfb = graph_of(lambda b, sp: (b.fwd(sp), b.bwd(sp)))
-        f_us, b_us, fb_us = replay_us(gf), replay_us(gb), replay_us(gfb)
-        return {"l2": l2_note, "fwd_us": f_us, "bwd_us": b_us, "us_per_step": fb_us,
+        # the same bytes as one forward (read x, write y) moved by a plain device copy, same protocol: what a kernel
+        # of this size can reach at all (launch ramp and first-touch latency weigh more the smaller the tensor)
+        gc = graph_of(lambda b, sp: b.y.copy_(b.x))
+        f_us, b_us, fb_us, c_us = replay_us(gf), replay_us(gb), replay_us(gfb), replay_us(gc)
+        return {"l2": l2_note, "fwd_us": f_us, "bwd_us": b_us, "us_per_step": fb_us, "copy_of_x_to_y_us": c_us,
+                "fwd_time_over_copy_time": f_us / c_us,
                 "GBps": nb["total"] / (fb_us * 1e-6) / 1e9,
                 "fwd_frac_of_peak": nb["fwd"] / (f_us * 1e-6) / 1e9 / peak_gbs,
                 "bwd_frac_of_peak": nb["bwd"] / (b_us * 1e-6) / 1e9 / peak_gbs}

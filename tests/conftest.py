@@ -69,3 +69,16 @@ def mgr_env():
             os.environ[name] = old
     if saved:
         _capi.reload_env()
+
+
+@pytest.fixture(scope="session", autouse=True)
+def no_kernel_gave_up_a_wait():
+    """After the last test on a GPU machine: no kernel of the session may have left the timeout status behind
+    (tests that write the status word on purpose clear it themselves)."""
+    yield
+    if not _has_gpu():
+        return
+    from mgrrmsnorm_b200 import _capi
+
+    if _capi.LIB_PATH.exists():
+        assert _capi.lib().mgr_device_status(1) == _capi.MGR_OK, "a kernel's bounded wait ran out during the test session"
