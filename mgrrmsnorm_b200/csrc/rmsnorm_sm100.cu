@@ -331,7 +331,10 @@ rms_bwd_reg(T* dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __
 // (40) where a thread holds at most two (one) packets of a row.
 // (Giving {256,2} 85 registers -- three row groups per SM instead of four, no spills -- was measured too: 0.84 against
 // 0.93 for one CTA per row group at bf16 hidden 4096, 24.6 against 22.9 us at 4096 x 4096. Rows in flight matter more.)
-constexpr int bwd_budget(int tpr, int vpt) { return (vpt <= 2 && tpr >= 160) ? (vpt == 1 ? 1536 : 1024) : 512; }
+constexpr int bwd_budget(int tpr, int vpt) {
+    if (tpr == 128 && vpt == 2) return 1024;   // eight groups of 128 threads (rms_bwd_wsm): measured ahead of four, 0.93 against 0.89
+    return (vpt <= 2 && tpr >= 160) ? (vpt == 1 ? 1536 : 1024) : 512;
+}
 constexpr int bwd_groups(int tpr, int vpt) {
     const int budget = bwd_budget(tpr, vpt);
     const int max_block = budget < 1024 ? budget : 1024;
@@ -556,6 +559,154 @@ rms_bwd_fat(T* dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __
     }
 }
 
+// Backward, fat CTA with the weight row in shared memory (one copy per CTA, read by every group) instead of VPT
+// packets per thread. The registers this frees are what lets four groups of {128,4} (eight of {128,2}) run without
+// spills at one CTA per SM, so the kernel writes 148 partial rows where one CTA per row group wrote 592-888, and the
+// column sum behind it reads a quarter of the bytes. The fill is ordered behind the first row's loads: a thread
+// requests its first packets, then the CTA meets once, so the weights cost no round trip of their own. After the row
+// loop the same shared memory is the fold buffer.
+// Measured on B200 (bf16, fraction of the copy bandwidth, backward call with its column sum, this form against one
+// CTA per row group): hidden 4096 at 65 536 / 16 384 / 8192 / 4096 rows 0.95 / 0.86 / 0.79 / 0.68 against
+// 0.92 / 0.84 / 0.76 / 0.64; hidden 2048 at 262 144 / 8192 rows 0.96 / 0.69 against 0.93 / 0.67.
+// The row loop counts rows in 32 bits and fetches the row scale behind the packets: both forms were timed, and the
+// 64-bit row-group counter of rms_bwd_fat costs this kernel 2.5 % and the scale fetched first another 0.7 %.
+// The host sends problems of 2^31 rows or more to the other kernels.
+template <typename T, int TPR, int VPT, bool ADD = false>
+__global__ void __launch_bounds__(BwdGeom<TPR, VPT>::kBlock, BwdGeom<TPR, VPT>::kMinBlocks)
+// (dx carries __restrict__ although the residual-add form allows dx == dres: a thread reads its packets of a row
+// before it writes them and no other thread touches them, so no reordering the qualifier permits can change a value)
+rms_bwd_wsm(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
+            const T* __restrict__ w, const float* __restrict__ inv_rms, int rows, int cols, const T* dres = nullptr) {
+    using Geo = BwdGeom<TPR, VPT>;
+    constexpr int VEC = Elem<T>::kVec;
+    constexpr int G = Geo::kGroups;
+    constexpr int kRow = TPR * VPT * VEC;
+    constexpr int kBlock = G * TPR;
+    static_assert(TPR < 1024, "rows that need the two-pass form keep their weights in global memory");
+    __shared__ float red_all[2 * (kBlock / 32)];
+    constexpr int kFoldBytes = G / 2 > 0 ? (G / 2) * kRow * 4 : 16;
+    constexpr int kWeightBytes = TPR * VPT * 16;
+    __shared__ __align__(16) unsigned char pool[kFoldBytes > kWeightBytes ? kFoldBytes : kWeightBytes];   // weights during the row loop, fold buffer after it
+    float* fold = reinterpret_cast<float*>(pool);
+    uint4* wsm = reinterpret_cast<uint4*>(pool);
+    int buf = 0;
+    const int group = threadIdx.x / TPR;
+    const int t = threadIdx.x % TPR;
+    const int nvec = cols / VEC;
+    float acc[VPT][VEC];
+#pragma unroll
+    for (int k = 0; k < VPT; ++k)
+#pragma unroll
+        for (int i = 0; i < VEC; ++i) acc[k][i] = 0.f;
+    const float inv_cols = 1.0f / static_cast<float>(cols);
+    int r = blockIdx.x * G + group;
+    uint4 xv[VPT], gv[VPT];
+    [[maybe_unused]] uint4 dv[ADD ? VPT : 1];
+    float rinv = 0.f;
+    // every load of a row, issued back to back; the row scale goes last (timed: 0.7 % ahead of first)
+    auto load = [&](int row) {
+        const uint4* xr = reinterpret_cast<const uint4*>(x + static_cast<int64_t>(row) * cols);
+        const uint4* gr = reinterpret_cast<const uint4*>(dy + static_cast<int64_t>(row) * cols);
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int v = t + k * TPR;
+            const bool on = v < nvec;
+            xv[k] = on ? ld_stream16(xr + v) : make_uint4(0, 0, 0, 0);
+            gv[k] = on ? ld_stream16(gr + v) : make_uint4(0, 0, 0, 0);
+        }
+        if constexpr (ADD) {
+            const uint4* rr = reinterpret_cast<const uint4*>(dres + static_cast<int64_t>(row) * cols);
+#pragma unroll
+            for (int k = 0; k < VPT; ++k) {
+                const int v = t + k * TPR;
+                dv[k] = v < nvec ? ld_stream16(rr + v) : make_uint4(0, 0, 0, 0);
+            }
+        }
+        rinv = __ldg(inv_rms + row);
+    };
+    for (int v = threadIdx.x; v < TPR * VPT; v += kBlock)
+        wsm[v] = v < nvec ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
+    const int stride = gridDim.x * G;
+    bool weights_pending = true;   // every thread meets the CTA exactly once, behind its first row's loads
+    for (; r < rows; r += stride) {
+        load(r);
+        if (weights_pending) { __syncthreads(); weights_pending = false; }
+        float c = 0.f;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            float fx[VEC], fg[VEC], fw[VEC];
+            unpack16<T>(xv[k], fx);
+            unpack16<T>(gv[k], fg);
+            unpack16<T>(wsm[t + k * TPR], fw);
+#pragma unroll
+            for (int i = 0; i < VEC; ++i) {
+                c += (fg[i] * fw[i]) * fx[i];
+                acc[k][i] += (fg[i] * fx[i]) * rinv;
+            }
+        }
+        c = group_sum<TPR>(c, red_all, buf, group);
+        const float term2 = c * (rinv * rinv) * inv_cols;
+        uint4* dr = reinterpret_cast<uint4*>(dx + static_cast<int64_t>(r) * cols);
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int v = t + k * TPR;
+            if (v < nvec) {
+                float fx[VEC], fg[VEC], fw[VEC], o[VEC];
+                unpack16<T>(xv[k], fx);
+                unpack16<T>(gv[k], fg);
+                unpack16<T>(wsm[v], fw);
+#pragma unroll
+                for (int i = 0; i < VEC; ++i) o[i] = rinv * (fg[i] * fw[i] - fx[i] * term2);
+                if constexpr (ADD) {
+                    float fr[VEC];
+                    unpack16<T>(dv[k], fr);
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) o[i] += fr[i];
+                }
+                st_stream16(dr + v, pack16<T>(o));
+            }
+        }
+    }
+    if (weights_pending) __syncthreads();   // a group that was dealt no row still owes the CTA its one meeting
+
+    // Fold the G groups (the fixed tree of rms_bwd_fat), then one partial row out.
+    if constexpr (G > 1) {
+        __syncthreads();   // every group has read its last weights: the pool becomes the fold buffer
+#pragma unroll
+        for (int d = 1; d < G; d <<= 1) {
+            const int pos = group & (2 * d - 1);
+            float* slot = fold + (group / (2 * d)) * kRow;
+            if (pos == d) {
+#pragma unroll
+                for (int k = 0; k < VPT; ++k)
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) slot[(k * VEC + i) * TPR + t] = acc[k][i];
+            }
+            __syncthreads();
+            if (pos == 0 && group + d < G) {
+#pragma unroll
+                for (int k = 0; k < VPT; ++k)
+#pragma unroll
+                    for (int i = 0; i < VEC; ++i) acc[k][i] += slot[(k * VEC + i) * TPR + t];
+            }
+            __syncthreads();
+        }
+    }
+    if (group == 0) {
+        float* out = ws + static_cast<int64_t>(blockIdx.x) * cols;
+#pragma unroll
+        for (int k = 0; k < VPT; ++k) {
+            const int v = t + k * TPR;
+            if (v < nvec) {
+#pragma unroll
+                for (int i = 0; i < VEC; i += 4)
+                    *reinterpret_cast<float4*>(out + static_cast<int64_t>(v) * VEC + i) =
+                        make_float4(acc[k][i], acc[k][i + 1], acc[k][i + 2], acc[k][i + 3]);
+            }
+        }
+    }
+}
+
 // dw[j] = sum_{p<P} ws[p, j] for cols % 4 == 0. A CTA of 1024 threads takes 8 packets of four columns (128 bytes of
 // every partial row) and cuts the P rows into 128 slices, so that a thread loads only ceil(P / 128) packets, all at
 // once: the sum is one round trip to L2 deep instead of a chain of them. Fixed order: a thread adds its rows in
@@ -738,6 +889,7 @@ struct RegShape {
     int tpr, vpt;
     bool fwd_ok, bwd_ok;   // fitted shapes only: whether the forward / the backward may pick it (from measurements)
     bool fat_bwd;          // backward: one fat CTA per SM (rms_bwd_fat) instead of one CTA per row group (rms_bwd_reg)
+    bool fat_wsm = false;  // ... in the form that keeps the weight row in shared memory (rms_bwd_wsm), at every row count
 };
 // Indices 8-10 are alternatives to {128,4}, {256,4} and {128,2} with one row per CTA pass; only the backward
 // picks them (bwd_shape_for), the size-ordered search of reg_shape_for never reaches them.
@@ -757,7 +909,7 @@ struct RegShape {
 // and lose more to spills than the fewer partial rows give back (bf16 hidden 4096: 0.67 / 0.90; 8192: 0.88 / 0.93;
 // fp32 hidden 1024: 0.95 / 1.00).
 constexpr RegShape kRegShapes[] = {{32, 1, true, true, true},     {32, 2, true, true, true},    {32, 4, true, true, true},
-                                   {128, 2, true, true, false},   {128, 4, true, true, false},  {256, 4, true, true, false},
+                                   {128, 2, true, true, true, true}, {128, 4, true, true, true, true}, {256, 4, true, true, false},
                                    {512, 4, true, true, true},    {1024, 4, true, true, false}, {256, 2, true, true, false},
                                    {512, 2, true, true, false},   {256, 1, true, true, false},  {160, 2, false, true, false},
                                    {192, 1, true, true, false},   {192, 2, false, true, false}, {320, 2, false, true, false},
@@ -799,14 +951,19 @@ constexpr int reg_shape_for(int64_t nvec) {
     return -1;
 }
 constexpr int default_fwd_shape(int64_t nvec) { return tighter_fitted(nvec, reg_shape_for(nvec), false); }
-constexpr int default_bwd_shape(int64_t nvec) {
+// add16: the residual-add backward of a 16-bit type, whose third operand costs {128,2} in eight groups its register
+// budget (112 bytes of spills at 64 registers: 0.79 against 0.92 for {256,1}, bf16 hidden 2048); it keeps {256,1}.
+constexpr int default_bwd_shape(int64_t nvec, bool add16 = false) {
     // Measured on B200 (bf16, 2^29 elements, fraction of the copy bandwidth): rows of 257-512 packets run at
     // 0.92 with {256,2} (one row per pass, 4 CTAs per SM) against 0.86 with {128,4}; rows of 513-1024 packets
     // are better left with {256,4} (0.92 against 0.89 for {512,2}).
     // Rows of 129-256 packets: 0.93 with {256,1} against 0.76 with {128,2} (and 0.84 for the ring kernel).
+    // Both have since given way to fat CTAs with the weights in shared memory (rms_bwd_wsm): {128,4} in four groups
+    // for rows of 257-512 packets (0.95 against 0.92) and {128,2} in eight groups for 129-256 packets (0.96 against
+    // 0.93), which is what the size-ordered search returns for them. MGR_RMSNORM_BWD_SHAPE=8 / 10 bring the earlier
+    // choices back for comparison.
     int base = reg_shape_for(nvec);
-    if (nvec > 256 && nvec <= 512) base = 8;
-    if (nvec > 128 && nvec <= 256) base = 10;
+    if (add16 && nvec > 128 && nvec <= 256) base = 10;
     return tighter_fitted(nvec, base, true);
 }
 // Checked at compile time: every row of up to 4096 packets gets a shape that holds it (forward and backward),
@@ -822,8 +979,8 @@ constexpr bool shape_tables_ok() {
         if (static_cast<int64_t>(bg / 2) * tpr * vpt * 8 * 4 > 44 * 1024) return false;              // the fold buffer (static shared memory)
     }
     for (int64_t nvec = 1; nvec <= 4096; ++nvec) {
-        const int f = default_fwd_shape(nvec), b = default_bwd_shape(nvec);
-        if (f < 0 || b < 0 || shape_capacity(f) < nvec || shape_capacity(b) < nvec) return false;
+        const int f = default_fwd_shape(nvec), b = default_bwd_shape(nvec), ba = default_bwd_shape(nvec, true);
+        if (f < 0 || b < 0 || ba < 0 || shape_capacity(f) < nvec || shape_capacity(b) < nvec || shape_capacity(ba) < nvec) return false;
     }
     return default_fwd_shape(4097) < 0 && default_bwd_shape(4097) < 0;
 }
@@ -833,9 +990,9 @@ int fwd_shape_for(int64_t nvec) {
     const int pinned = pinned_shape(overrides().fwd_shape, nvec);
     return pinned >= 0 ? pinned : default_fwd_shape(nvec);
 }
-int bwd_shape_for(int64_t nvec) {
+int bwd_shape_for(int64_t nvec, bool add16 = false) {
     const int pinned = pinned_shape(overrides().bwd_shape, nvec);
-    return pinned >= 0 ? pinned : default_bwd_shape(nvec);
+    return pinned >= 0 ? pinned : default_bwd_shape(nvec, add16);
 }
 
 template <typename K>
@@ -859,13 +1016,15 @@ struct RegKernels {
     static constexpr int G = RegGeom<TPR>::kGroups;
     static constexpr int BWD_BLOCK = BwdGeom<TPR, VPT>::kBlock;
     static constexpr int BWD_G = BwdGeom<TPR, VPT>::kGroups;
+    static constexpr bool WSM = kRegShapes[I].fat_wsm;
     // Which backward kernel this problem runs: the table's choice unless MGR_RMSNORM_BWD_FAT pins it. A problem with
     // too few rows to give every group of every fat CTA a few of them stays with one CTA per row group (2048 x 512
     // bf16: 5.1 us against 5.4 us).
     static bool fat_bwd(int64_t rows, const DeviceInfo& di) {
+        if (WSM && rows >= (1ll << 31) - (1ll << 24)) return false;   // rms_bwd_wsm counts rows in 32 bits
         const int pinned = overrides().bwd_fat;
         if (pinned >= 0) return pinned != 0;
-        return kRegShapes[I].fat_bwd && rows >= 4ll * BWD_G * di.sm_count;
+        return kRegShapes[I].fat_bwd && (WSM || rows >= 4ll * BWD_G * di.sm_count);
     }
 
     static int64_t fwd_grid(int64_t rows, const DeviceInfo& di) {
@@ -879,7 +1038,10 @@ struct RegKernels {
         static std::atomic<int> occ_fat[kMaxDevices];
         if (fat_bwd(rows, di)) {
             const int64_t ngroups = (rows + BWD_G - 1) / BWD_G;
-            const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_bwd_fat<T, TPR, VPT, ADD>, BWD_BLOCK, occ_fat, di.device);
+            int resident;
+            if constexpr (WSM) resident = resident_ctas(rms_bwd_wsm<T, TPR, VPT, ADD>, BWD_BLOCK, occ_fat, di.device);
+            else resident = resident_ctas(rms_bwd_fat<T, TPR, VPT, ADD>, BWD_BLOCK, occ_fat, di.device);
+            const int64_t cap = static_cast<int64_t>(di.sm_count) * resident;
             return ngroups < cap ? ngroups : cap;
         }
         const int64_t ngroups = (rows + G - 1) / G;
@@ -892,9 +1054,12 @@ struct RegKernels {
     }
     static void bwd(T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv, int64_t rows,
                     int cols, int64_t grid, const DeviceInfo& di, cudaStream_t s, const T* dres) {
-        if (fat_bwd(rows, di))
-            rms_bwd_fat<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BWD_BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres);
-        else
+        if (fat_bwd(rows, di)) {
+            if constexpr (WSM)
+                rms_bwd_wsm<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BWD_BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, static_cast<int>(rows), cols, dres);
+            else
+                rms_bwd_fat<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BWD_BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres);
+        } else
             rms_bwd_reg<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres);
     }
 };
@@ -1100,7 +1265,10 @@ int64_t bwd_partials(int64_t rows, int64_t cols, const DeviceInfo& di) {
         if (shape >= 0) {
             const int64_t g = RegDispatch<T>::bwd_grid(shape, rows, di);
             if (g > p) p = g;
-            const int64_t ga = RegDispatch<T>::bwd_grid(shape, rows, di, true);
+        }
+        const int shape_add = bwd_shape_for(cols / VEC, sizeof(T) == 2);
+        if (shape_add >= 0) {
+            const int64_t ga = RegDispatch<T>::bwd_grid(shape_add, rows, di, true);
             if (ga > p) p = ga;
         }
         const BwdRingPlan rp = bwd_ring_plan(rows, cols, sizeof(T), di);
@@ -1129,7 +1297,7 @@ int bwd_typed(void* dx, void* dw, float* dw_f32, const void* dy, const void* x, 
         }
     }
     if (P < 0) {
-        const int shape = packets ? bwd_shape_for(cols / VEC) : -1;
+        const int shape = packets ? bwd_shape_for(cols / VEC, add && sizeof(T) == 2) : -1;
         if (shape >= 0) {
             P = RegDispatch<T>::bwd_grid(shape, rows, di, add);
             RegDispatch<T>::bwd(shape, static_cast<T*>(dx), ws, static_cast<const T*>(dy), static_cast<const T*>(x),
