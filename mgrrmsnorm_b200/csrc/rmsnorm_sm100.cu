@@ -62,7 +62,10 @@ __device__ __forceinline__ float row_sum(float v, float (*red)[RegGeom<TPR>::kWa
 
 // ADD: the row that is normalised is h = round_T(x + res); h is also written out (the new residual
 // stream). h_out may be the buffer of x or of res: a thread reads its packets of a row before it writes them.
-template <typename T, int TPR, int VPT, bool ADD = false>
+// WSM: the weight row is kept in shared memory (one copy per CTA) instead of VPT packets per thread, and the CTA
+// meets once, behind its first row's loads, before it reads them. Used by the residual-add form of the shapes whose
+// table entry says so (wsm_add): the registers it frees are the ones the second operand would otherwise spill.
+template <typename T, int TPR, int VPT, bool ADD = false, bool WSM = false>
 // (the warp-per-row shape with four packets per lane is held to 3 CTAs per SM instead of 4: at 64 registers it
 // spilled and ran at 0.88 of the copy bandwidth on 2 KB rows; at 77 registers, no spills, 0.95)
 __global__ void __launch_bounds__(RegGeom<TPR>::kBlock, (TPR == 32 && VPT == 4) ? 3 : RegGeom<TPR>::kFwdMinBlocks)
@@ -71,18 +74,25 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
     using Geo = RegGeom<TPR>;
     constexpr int VEC = Elem<T>::kVec;
     __shared__ float red[2][Geo::kWarps];
+    __shared__ uint4 wsm[WSM ? TPR * VPT : 1];
     int buf = 0;
 
     const int group = threadIdx.x / TPR;
     const int t = threadIdx.x % TPR;
     const int nvec = cols / VEC;
 
-    uint4 wv[VPT];
+    uint4 wv[WSM ? 1 : VPT];
+    if constexpr (WSM) {
+        for (int v = threadIdx.x; v < TPR * VPT; v += Geo::kBlock)
+            wsm[v] = v < nvec ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
+    } else {
 #pragma unroll
-    for (int k = 0; k < VPT; ++k) {
-        const int v = t + k * TPR;
-        wv[k] = v < nvec ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
+        for (int k = 0; k < VPT; ++k) {
+            const int v = t + k * TPR;
+            wv[k] = v < nvec ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
+        }
     }
+    [[maybe_unused]] bool weights_pending = WSM;   // every CTA runs at least one pass of the loop below (grid <= row groups)
 
     const float inv_cols = 1.0f / static_cast<float>(cols);
     const int64_t ngroups = (rows + Geo::kGroups - 1) / Geo::kGroups;
@@ -95,7 +105,7 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
         for (int k = 0; k < VPT; ++k) {
             const int v = t + k * TPR;
             xv[k] = (live && v < nvec) ? ld_stream16(xr + v) : make_uint4(0, 0, 0, 0);
-            keep_packed(wv[k]);
+            if constexpr (!WSM) keep_packed(wv[k]);
         }
         if constexpr (ADD) {
             const int64_t off = (live ? r : 0) * static_cast<int64_t>(cols);
@@ -124,6 +134,12 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
 #pragma unroll
             for (int i = 0; i < VEC; ++i) ss += f[i] * f[i];
         }
+        if constexpr (WSM) {
+            if (weights_pending) {   // rg is the same for the whole CTA: every thread takes this branch in the same pass
+                __syncthreads();
+                weights_pending = false;
+            }
+        }
         ss = row_sum<TPR>(ss, red, buf, group);
         const float inv = 1.0f / sqrtf(ss * inv_cols + eps);
         if (live && t == 0 && inv_rms != nullptr) inv_rms[r] = inv;
@@ -135,7 +151,8 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
                 if (v < nvec) {
                     float f[VEC], g[VEC], o[VEC];
                     unpack16<T>(xv[k], f);
-                    unpack16<T>(wv[k], g);
+                    if constexpr (WSM) unpack16<T>(wsm[v], g);
+                    else unpack16<T>(wv[k], g);
 #pragma unroll
                     for (int i = 0; i < VEC; ++i) o[i] = (f[i] * inv) * g[i];
                     st_stream16(yr + v, pack16<T>(o));
@@ -890,6 +907,11 @@ struct RegShape {
     bool fwd_ok, bwd_ok;   // fitted shapes only: whether the forward / the backward may pick it (from measurements)
     bool fat_bwd;          // backward: one fat CTA per SM (rms_bwd_fat) instead of one CTA per row group (rms_bwd_reg)
     bool fat_wsm = false;  // ... in the form that keeps the weight row in shared memory (rms_bwd_wsm), at every row count
+    bool wsm_add = false;  // the residual-add kernels alone take the shared-memory-weights forms (backward: rms_bwd_wsm;
+                           // forward: rms_fwd_reg with WSM): their third operand costs the plain forms spills. Measured
+                           // on B200 (backward, fraction of the copy bandwidth, bf16): {256,4} at hidden 8192 0.98 against
+                           // 0.91, {384,2} at hidden 6144 0.98 against 0.91; without the residual the plain forms stay
+                           // ahead there (0.925 against 0.915), and the other shapes lose either way.
 };
 // Indices 8-10 are alternatives to {128,4}, {256,4} and {128,2} with one row per CTA pass; only the backward
 // picks them (bwd_shape_for), the size-ordered search of reg_shape_for never reaches them.
@@ -909,11 +931,11 @@ struct RegShape {
 // and lose more to spills than the fewer partial rows give back (bf16 hidden 4096: 0.67 / 0.90; 8192: 0.88 / 0.93;
 // fp32 hidden 1024: 0.95 / 1.00).
 constexpr RegShape kRegShapes[] = {{32, 1, true, true, true},     {32, 2, true, true, true},    {32, 4, true, true, true},
-                                   {128, 2, true, true, true, true}, {128, 4, true, true, true, true}, {256, 4, true, true, false},
+                                   {128, 2, true, true, true, true}, {128, 4, true, true, true, true}, {256, 4, true, true, false, false, true},
                                    {512, 4, true, true, true},    {1024, 4, true, true, false}, {256, 2, true, true, false},
                                    {512, 2, true, true, false},   {256, 1, true, true, false},  {160, 2, false, true, false},
                                    {192, 1, true, true, false},   {192, 2, false, true, false}, {320, 2, false, true, false},
-                                   {384, 2, false, true, false},  {448, 2, false, true, false},
+                                   {384, 2, false, true, false, false, true},  {448, 2, false, true, false},
                                    // forward only: four packets per thread (as {128,4}, the best forward shape of its size
                                    // class) at 96 / 160 / 192 threads per row, for rows of 257-384 / 513-640 / 641-768 packets.
                                    // Measured (bf16, 2^29 elements, fraction of the copy bandwidth): hidden 2560 0.98 against 0.87
@@ -1016,7 +1038,8 @@ struct RegKernels {
     static constexpr int G = RegGeom<TPR>::kGroups;
     static constexpr int BWD_BLOCK = BwdGeom<TPR, VPT>::kBlock;
     static constexpr int BWD_G = BwdGeom<TPR, VPT>::kGroups;
-    static constexpr bool WSM = kRegShapes[I].fat_wsm;
+    static constexpr bool WSM = kRegShapes[I].fat_wsm || (ADD && kRegShapes[I].wsm_add);
+    static constexpr bool FWD_WSM = ADD && kRegShapes[I].wsm_add && kRegShapes[I].fwd_ok;
     // Which backward kernel this problem runs: the table's choice unless MGR_RMSNORM_BWD_FAT pins it. A problem with
     // too few rows to give every group of every fat CTA a few of them stays with one CTA per row group (2048 x 512
     // bf16: 5.1 us against 5.4 us).
@@ -1024,13 +1047,14 @@ struct RegKernels {
         if (WSM && rows >= (1ll << 31) - (1ll << 24)) return false;   // rms_bwd_wsm counts rows in 32 bits
         const int pinned = overrides().bwd_fat;
         if (pinned >= 0) return pinned != 0;
-        return kRegShapes[I].fat_bwd && (WSM || rows >= 4ll * BWD_G * di.sm_count);
+        if (WSM) return true;
+        return kRegShapes[I].fat_bwd && rows >= 4ll * BWD_G * di.sm_count;
     }
 
     static int64_t fwd_grid(int64_t rows, const DeviceInfo& di) {
         static std::atomic<int> occ[kMaxDevices];
         const int64_t ngroups = (rows + G - 1) / G;
-        const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_fwd_reg<T, TPR, VPT, ADD>, BLOCK, occ, di.device);
+        const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_fwd_reg<T, TPR, VPT, ADD, FWD_WSM>, BLOCK, occ, di.device);
         return ngroups < cap ? ngroups : cap;
     }
     static int64_t bwd_grid(int64_t rows, const DeviceInfo& di) {
@@ -1050,7 +1074,7 @@ struct RegKernels {
     }
     static void fwd(T* y, float* inv, const T* x, const T* w, int64_t rows, int cols, float eps,
                     const DeviceInfo& di, cudaStream_t s, const T* res, T* h_out) {
-        rms_fwd_reg<T, TPR, VPT, ADD><<<static_cast<unsigned>(fwd_grid(rows, di)), BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps, res, h_out);
+        rms_fwd_reg<T, TPR, VPT, ADD, FWD_WSM><<<static_cast<unsigned>(fwd_grid(rows, di)), BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps, res, h_out);
     }
     static void bwd(T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv, int64_t rows,
                     int cols, int64_t grid, const DeviceInfo& di, cudaStream_t s, const T* dres) {

@@ -60,11 +60,13 @@ def test_matches_two_step_sequence_and_oracle(ops, rows, cols, dtype):
     assert torch.equal(dw, dw32.to(dw.dtype))
     # dW does not depend on the residual gradient: same bits as the unfused backward
     _, dw_plain, dw32_plain = ops.rmsnorm_backward_full(dyd, h, wd, inv, want_dw_f32=True)
-    # ... where both run the same kernel with the same grid. Not so for 16-bit rows of 193-256 packets, where the plain
-    # backward sums its partial rows per fat CTA (rms_bwd_wsm) and the residual-add form keeps one CTA per row:
-    # the same products in another fixed grouping, held to the oracle above.
+    # ... where both run the same kernel with the same grid. Not so where only one of the two takes the fat-CTA form
+    # with the weights in shared memory (rms_bwd_wsm): the plain backward alone for 16-bit rows of 193-256 packets,
+    # the residual-add backward alone for rows of 641-768 and 897-1024 packets. There dW is the same products in
+    # another fixed grouping, held to the oracle above.
     packets = cols * x.element_size() // 16
-    same_kernel = (cols * x.element_size() <= 16384 or rows < 8 * 148) and not (x.element_size() == 2 and 192 < packets <= 256)
+    one_sided = (x.element_size() == 2 and 192 < packets <= 256) or 640 < packets <= 768 or 896 < packets <= 1024
+    same_kernel = (cols * x.element_size() <= 16384 or rows < 8 * 148) and not one_sided
     if same_kernel:
         assert torch.equal(dw32, dw32_plain) and torch.equal(dw, dw_plain)
 
