@@ -912,6 +912,7 @@ struct RegShape {
                            // on B200 (backward, fraction of the copy bandwidth, bf16): {256,4} at hidden 8192 0.98 against
                            // 0.91, {384,2} at hidden 6144 0.98 against 0.91; without the residual the plain forms stay
                            // ahead there (0.925 against 0.915), and the other shapes lose either way.
+    bool fwd_wsm = false;  // the plain forward of a 16-bit type takes the shared-memory-weights form too, when there are rows enough
 };
 // Indices 8-10 are alternatives to {128,4}, {256,4} and {128,2} with one row per CTA pass; only the backward
 // picks them (bwd_shape_for), the size-ordered search of reg_shape_for never reaches them.
@@ -931,7 +932,7 @@ struct RegShape {
 // and lose more to spills than the fewer partial rows give back (bf16 hidden 4096: 0.67 / 0.90; 8192: 0.88 / 0.93;
 // fp32 hidden 1024: 0.95 / 1.00).
 constexpr RegShape kRegShapes[] = {{32, 1, true, true, true},     {32, 2, true, true, true},    {32, 4, true, true, true},
-                                   {128, 2, true, true, true, true}, {128, 4, true, true, true, true}, {256, 4, true, true, false, false, true},
+                                   {128, 2, true, true, true, true, false, true}, {128, 4, true, true, true, true, false, true}, {256, 4, true, true, false, false, true},
                                    {512, 4, true, true, true},    {1024, 4, true, true, false}, {256, 2, true, true, false},
                                    {512, 2, true, true, false},   {256, 1, true, true, false},  {160, 2, false, true, false},
                                    {192, 1, true, true, false},   {192, 2, false, true, false}, {320, 2, false, true, false},
@@ -1039,7 +1040,17 @@ struct RegKernels {
     static constexpr int BWD_BLOCK = BwdGeom<TPR, VPT>::kBlock;
     static constexpr int BWD_G = BwdGeom<TPR, VPT>::kGroups;
     static constexpr bool WSM = kRegShapes[I].fat_wsm || (ADD && kRegShapes[I].wsm_add);
-    static constexpr bool FWD_WSM = ADD && kRegShapes[I].wsm_add && kRegShapes[I].fwd_ok;
+    // Forward with the weights in shared memory: always for the residual-add form of the shapes marked wsm_add; for
+    // the plain forward of the shapes marked fwd_wsm when the type is 16-bit and every CTA makes two passes or more
+    // (measured, bf16 / fp16 hidden 4096: 0.98 against 0.96 at 131 072 rows, 13.6 against 14.0 us at 4096 rows, but
+    // 3.4 against 3.1 us at 256 rows, where the fill and its barrier are not hidden; fp32 hidden 2048 loses 1-5 %).
+    static constexpr bool FWD_WSM_ALWAYS = ADD && kRegShapes[I].wsm_add && kRegShapes[I].fwd_ok;
+    static constexpr bool FWD_WSM_LARGE = !FWD_WSM_ALWAYS && kRegShapes[I].fwd_wsm && sizeof(T) == 2;
+    static bool fwd_wsm(int64_t rows, const DeviceInfo& di) {
+        if constexpr (FWD_WSM_ALWAYS) return true;
+        if constexpr (FWD_WSM_LARGE) return (rows + G - 1) / G >= 8ll * di.sm_count;
+        return false;
+    }
     // Which backward kernel this problem runs: the table's choice unless MGR_RMSNORM_BWD_FAT pins it. A problem with
     // too few rows to give every group of every fat CTA a few of them stays with one CTA per row group (2048 x 512
     // bf16: 5.1 us against 5.4 us).
@@ -1053,8 +1064,17 @@ struct RegKernels {
 
     static int64_t fwd_grid(int64_t rows, const DeviceInfo& di) {
         static std::atomic<int> occ[kMaxDevices];
+        static std::atomic<int> occ_wsm[kMaxDevices];
         const int64_t ngroups = (rows + G - 1) / G;
-        const int64_t cap = static_cast<int64_t>(di.sm_count) * resident_ctas(rms_fwd_reg<T, TPR, VPT, ADD, FWD_WSM>, BLOCK, occ, di.device);
+        int resident;
+        if (fwd_wsm(rows, di)) {
+            if constexpr (FWD_WSM_ALWAYS || FWD_WSM_LARGE) resident = resident_ctas(rms_fwd_reg<T, TPR, VPT, ADD, true>, BLOCK, occ_wsm, di.device);
+            else resident = 1;   // not reached
+        } else {
+            if constexpr (!FWD_WSM_ALWAYS) resident = resident_ctas(rms_fwd_reg<T, TPR, VPT, ADD, false>, BLOCK, occ, di.device);
+            else resident = 1;   // not reached
+        }
+        const int64_t cap = static_cast<int64_t>(di.sm_count) * resident;
         return ngroups < cap ? ngroups : cap;
     }
     static int64_t bwd_grid(int64_t rows, const DeviceInfo& di) {
@@ -1074,7 +1094,12 @@ struct RegKernels {
     }
     static void fwd(T* y, float* inv, const T* x, const T* w, int64_t rows, int cols, float eps,
                     const DeviceInfo& di, cudaStream_t s, const T* res, T* h_out) {
-        rms_fwd_reg<T, TPR, VPT, ADD, FWD_WSM><<<static_cast<unsigned>(fwd_grid(rows, di)), BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps, res, h_out);
+        const unsigned grid = static_cast<unsigned>(fwd_grid(rows, di));
+        if (fwd_wsm(rows, di)) {
+            if constexpr (FWD_WSM_ALWAYS || FWD_WSM_LARGE) rms_fwd_reg<T, TPR, VPT, ADD, true><<<grid, BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps, res, h_out);
+        } else {
+            if constexpr (!FWD_WSM_ALWAYS) rms_fwd_reg<T, TPR, VPT, ADD, false><<<grid, BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps, res, h_out);
+        }
     }
     static void bwd(T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv, int64_t rows,
                     int cols, int64_t grid, const DeviceInfo& di, cudaStream_t s, const T* dres) {
@@ -1244,7 +1269,14 @@ bool prefer_ring_fwd(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& 
     const int64_t row_bytes = cols * static_cast<int64_t>(elem);
     // 2 KB rows: fp32 0.92 register / 0.97 ring; bf16 and fp16 0.95 register / 0.87 ring
     const bool from = row_bytes > 2048 || (row_bytes == 2048 && elem == 4);
-    return rows >= 8ll * di.sm_count && from && row_bytes <= 4096;
+    // The ring pays about 4 us to come up (a 200 KB ring per SM to fill before the first row is normalised), which a
+    // small tensor never earns back. Measured (register / ring, forward, us): bf16 2048 x 2048 5.4 / 8.5; 4096 x 2048
+    // 8.3 / 10.5; 16 384 x 2048 26.1 / 26.7; 65 536 x 2048 94.0 / 88.4; fp32 4096 x 512 4.6 / 8.6; 65 536 x 512
+    // 46.9 / 47.7. fp32 rows of 4 KB stay with the register kernels at every size measured (131 072 x 1024: 0.93
+    // against 0.90 of the copy bandwidth).
+    const int64_t min_bytes = elem == 4 ? (256ll << 20) : (128ll << 20);
+    if (elem == 4 && row_bytes > 2048) return false;
+    return rows >= 8ll * di.sm_count && rows * row_bytes >= min_bytes && from && row_bytes <= 4096;
 }
 bool prefer_ring_bwd(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& di) {
     const int64_t row_bytes = cols * static_cast<int64_t>(elem);
