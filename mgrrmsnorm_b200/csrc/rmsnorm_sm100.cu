@@ -1280,7 +1280,10 @@ bool prefer_ring_fwd(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& 
 }
 bool prefer_ring_bwd(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& di) {
     const int64_t row_bytes = cols * static_cast<int64_t>(elem);
-    return rows >= 8ll * di.sm_count && row_bytes > 16384;
+    // Rows of 16-24 KB (1025-1536 packets) have a packet shape of their own, {384,4}: bf16 hidden 12 288 at 16 384 rows
+    // 0.75 with it against 0.69 for the ring (2048 rows: 0.59 against 0.55). Beyond that the ring is ahead at every
+    // row count measured (32 KB rows, 2048 to 32 768 rows: 0.66-0.90 against 0.65-0.84; fp32 0.86-0.98 against 0.74-0.87).
+    return rows >= 8ll * di.sm_count && row_bytes > 24576;
 }
 
 template <typename T>
