@@ -29,7 +29,7 @@ void load_env() {
     int pdl = 1;
     if (const char* e = std::getenv("MGR_GEMM_PDL")) pdl = e[0] != '0';
     int narrow = -1;
-    if (const char* e = std::getenv("MGR_GEMM_NARROW")) narrow = e[0] == '0' ? 0 : (e[0] == '3' ? 32 : 64);
+    if (const char* e = std::getenv("MGR_GEMM_NARROW")) narrow = e[0] == '0' ? 0 : (e[0] == '3' ? 32 : (e[0] == '9' ? 96 : 64));
     g_env[0].store(path, std::memory_order_relaxed);
     g_env[1].store(num("MGR_RMSNORM_FWD_SHAPE", -1), std::memory_order_relaxed);
     g_env[2].store(num("MGR_RMSNORM_BWD_SHAPE", -1), std::memory_order_relaxed);

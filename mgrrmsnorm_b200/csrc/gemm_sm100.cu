@@ -41,6 +41,8 @@ constexpr int kBM = 128;         // tile rows (UMMA M)
 constexpr int kBN = 256;         // accumulator columns per tile (UMMA N) of the throughput kernels
 constexpr int kBNSmall = 64;     // ... of the narrow-tile kernels used when a problem has few tiles (skinny M)
 constexpr int kBNTiny = 32;      // ... and of the narrowest ones, for problems that still leave SMs idle at 64
+constexpr int kBNMid = 96;       // ... 48 gate + 48 value columns: the fused projection of a skinny batch whose 32-column
+                                 // tiles would need two rounds over the SMs (hidden 6912: 216 tiles of 32 against 144 of 48)
 constexpr int kBK = 64;          // K per stage: 64 x 2 B = one 128-byte swizzle row
 constexpr int kUmmaK = 16;       // K of one tcgen05.mma for 16-bit operands
 constexpr uint32_t kABytes = kBM * kBK * 2;   // 16 KB: this CTA's 128 rows of A
@@ -58,8 +60,10 @@ __host__ __device__ constexpr uint32_t gemm_smem(int cg, int bn) {
 }
 // The dh -> [d_gate | d_val] epilogue moves its global traffic (the stored projection in, the gradients out)
 // in a coalesced layout and converts to and from the accumulator's row-per-thread layout through a small
-// per-warp staging buffer behind the ring: 32 rows x 64 B, rows padded to 80 B against bank conflicts.
-constexpr uint32_t kEpiRowPitch = 80;
+// per-warp staging buffer behind the ring: 32 rows x 64 B. The four 16-byte pieces of row r sit at piece ^ ((r >> 1) & 3):
+// with that, a quarter-warp touches eight different 16-byte slots of the 128 bank bytes both ways round (one row per
+// lane, and four lanes per row), where rows padded to 80 B left the four-lanes-per-row accesses a two-way conflict.
+constexpr uint32_t kEpiRowPitch = 64;
 constexpr uint32_t kEpiStageBytes = 32 * kEpiRowPitch;
 constexpr int kMaxStages = 8;
 // Narrow-tile kernels: a sub-stage is the A box actually loaded (8..128 rows) plus the 8 KB B tile of one
@@ -97,7 +101,7 @@ constexpr bool narrow_geom_fits(int bn) {
     }
     return true;
 }
-static_assert(narrow_geom_fits(kBNSmall) && narrow_geom_fits(kBNTiny), "narrow-tile ring geometry leaves shared memory");
+static_assert(narrow_geom_fits(kBNSmall) && narrow_geom_fits(kBNTiny) && narrow_geom_fits(kBNMid), "narrow-tile ring geometry leaves shared memory");
 
 constexpr int kEpiWarps = 8;      // epilogue warps: two per 32-lane quarter of tensor memory
 // ring depth and dynamic shared memory of a kernel instance (a CTA pair gives up one stage to the staging buffers)
@@ -118,7 +122,8 @@ constexpr bool smem_budgets_ok() {
             if (gemm_smem_epi(epi, cg, kBN) + kStatic > kCtaLimit) return false;
             if (stage_bytes(cg, kBN) % 1024u != 0 || num_stages_epi(epi, cg, kBN) > kMaxStages) return false;
         }
-    if (gemm_smem(1, kBNSmall) + kStatic > kCtaLimit || gemm_smem(1, kBNTiny) + kStatic > kCtaLimit) return false;
+    if (gemm_smem(1, kBNSmall) + kStatic > kCtaLimit || gemm_smem(1, kBNTiny) + kStatic > kCtaLimit || gemm_smem(1, kBNMid) + kStatic > kCtaLimit) return false;
+    if ((b_bytes(kBNMid) / 2) % 1024u != 0) return false;   // the value half of a 96-column B tile starts on a swizzle-group boundary
     return kEpiRowPitch % 16u == 0 && kEpiStageBytes % 16u == 0 && kNarrowRing % 1024u == 0 && b_bytes(kBNTiny) % 1024u == 0;
 }
 static_assert(smem_budgets_ok(), "a GEMM kernel instance exceeds the shared-memory budget or breaks an alignment rule");
@@ -243,9 +248,15 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             uint32_t a_box_bytes, const float* __restrict__ row_scale,
             int* __restrict__ status) {
     static_assert(n_step_of(EPI, BN) == BN || !B_MN, "the gate/value split reads w12 K-major");
-    static_assert(BN == kBN || ((BN == kBNSmall || BN == kBNTiny) && CG == 1 && !A_MN && !B_MN && (EPI == kEpiPlain || EPI == kEpiSwiglu)),
-                  "narrow tiles: single CTA, K-major operands, plain or fused-activation epilogue");
+    static_assert(BN == kBN || ((BN == kBNSmall || BN == kBNTiny) && CG == 1 && !A_MN && !B_MN && (EPI == kEpiPlain || EPI == kEpiSwiglu)) ||
+                      (BN == kBNMid && CG == 1 && !A_MN && !B_MN && EPI == kEpiSwiglu),
+                  "narrow tiles: single CTA, K-major operands, plain or fused-activation epilogue (96 columns: the latter only)");
     constexpr int kNStep = n_step_of(EPI, BN);  // output columns per tile
+    // tensor-memory columns from one accumulator to the next: the tile width, rounded up to 128 for the 96-column tile
+    // (whose second 32-column read of each half runs past column 96 and must not reach the other accumulator)
+    constexpr int kAccStride = BN == kBNMid ? 128 : BN;
+    // 32-column chunks of the tile's output an epilogue warp pair walks (the 16-column tile has a path of its own)
+    constexpr int kChunks = kNStep < 32 ? 0 : (kNStep + 31) / 32;
     constexpr uint32_t kBBytes = b_bytes(BN);
     constexpr bool kNarrow = BN < kBN;
     // wide tiles: compile-time ring of one K block per stage; narrow tiles: see narrow_geom()
@@ -338,8 +349,14 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                                 for (int c = 0; c < kBM / 64; ++c) ptx::tma_load_2d(ssa + c * 8192u, &tmA, m0 + 64 * c, kk, full);
                             }
                             if constexpr (!B_MN) {
-                                ptx::tma_load_2d(ssb, &tmB, kk, tc.n0, full);
-                                ptx::tma_load_2d(ssb + kBBytes / 2, &tmB, kk, b_row1, full);
+                                if constexpr (kNarrow && kNStep == BN) {
+                                    // plain narrow tile: its B rows are contiguous, one box of BN rows (half as many copies
+                                    // to issue as two boxes of BN / 2; the copies, not the bytes, bound a skinny tile)
+                                    ptx::tma_load_2d(ssb, &tmB, kk, tc.n0, full);
+                                } else {
+                                    ptx::tma_load_2d(ssb, &tmB, kk, tc.n0, full);
+                                    ptx::tma_load_2d(ssb + kBBytes / 2, &tmB, kk, b_row1, full);
+                                }
                             } else {
 #pragma unroll
                                 for (int c = 0; c < BN / 64; ++c) ptx::tma_load_2d(ssb + c * 8192u, &tmB, tc.n0 + 64 * c, kk, full);
@@ -384,7 +401,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             for (int t = first_tile; ok && t < num_tiles; t += tile_stride) {
                 if (!ptx::mbar_wait(ptx::smem_addr(&bar_tempty[acc]), acc_phase ^ 1u, &abort_flag)) break;
                 ptx::tc_fence_after_sync();
-                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * BN;
+                const uint32_t d_tmem = tmem_base + static_cast<uint32_t>(acc) * kAccStride;
                 for (int kb = 0; kb < num_kb; kb += kSub) {
                     if (!ptx::mbar_wait(ptx::smem_addr(&bar_full[stage]), phase, &abort_flag)) {
                         ok = false;
@@ -429,7 +446,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
             if (!ptx::mbar_wait(ptx::smem_addr(&bar_tfull[acc]), acc_phase, &abort_flag)) break;
             ptx::tc_fence_after_sync();
             const int row = tc.m0 + static_cast<int>(cta_rank) * kBM + q * 32 + lane;
-            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * BN;
+            const uint32_t t_row = tmem_base + (static_cast<uint32_t>(q * 32) << 16) + static_cast<uint32_t>(acc) * kAccStride;
             T* crow = C + static_cast<int64_t>(row) * ldc + tc.n0;
             [[maybe_unused]] float rs = 1.0f;                 // kEpiSwiglu: this row's scale
             if constexpr (EPI == kEpiSwiglu) {
@@ -456,7 +473,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                 }
             }
 #pragma unroll 1
-            for (int c = chunk0; c < kNStep / 32; c += kEpiWarps / 4) {
+            for (int c = chunk0; c < kChunks; c += kEpiWarps / 4) {
                 if constexpr (EPI == kEpiSwigluBwd) {
                     uint32_t g[32], v[32];
                     ptx::tmem_ld_32x32(t_row + c * 32, g);
@@ -511,8 +528,10 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     const int cr = lane >> 2, cp = lane & 3;
                     const int row0 = tc.m0 + static_cast<int>(cta_rank) * kBM + q * 32;
                     const uint32_t sbuf = ring + static_cast<uint32_t>(kStages) * kStageBytes + static_cast<uint32_t>(warp - 2) * kEpiStageBytes;
-                    const uint32_t s_co = sbuf + static_cast<uint32_t>(cr) * kEpiRowPitch + static_cast<uint32_t>(cp) * 16u;   // + i * 8 rows
-                    const uint32_t s_row = sbuf + static_cast<uint32_t>(lane) * kEpiRowPitch;                                    // + j * 16
+                    // rows cr + 8 i share (row >> 1) & 3 with row cr, so one swizzled address serves all four i
+                    const uint32_t s_co = sbuf + static_cast<uint32_t>(cr) * kEpiRowPitch + ((static_cast<uint32_t>(cp) ^ ((static_cast<uint32_t>(cr) >> 1) & 3u)) << 4);   // + i * 8 rows
+                    const uint32_t s_row = sbuf + static_cast<uint32_t>(lane) * kEpiRowPitch;   // piece j at + ((j ^ sw_row) << 4)
+                    const uint32_t sw_row = (static_cast<uint32_t>(lane) >> 1) & 3u;
                     uint32_t a[32];
                     ptx::tmem_ld_32x32(t_row + c * 32, a);
                     auto fetch = [&](int cc) {
@@ -532,13 +551,13 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
                     for (int i = 0; i < 4; ++i) ptx::sts128(s_co + static_cast<uint32_t>(i) * 8u * kEpiRowPitch, gp_next[i]);
                     __syncwarp();
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) gp[j] = ptx::lds128(s_row + 16u * j);
+                    for (int j = 0; j < 4; ++j) gp[j] = ptx::lds128(s_row + ((static_cast<uint32_t>(j) ^ sw_row) << 4));
                     __syncwarp();
 #pragma unroll
                     for (int i = 0; i < 4; ++i) ptx::sts128(s_co + static_cast<uint32_t>(i) * 8u * kEpiRowPitch, vp_next[i]);
                     __syncwarp();
 #pragma unroll
-                    for (int j = 0; j < 4; ++j) vp[j] = ptx::lds128(s_row + 16u * j);
+                    for (int j = 0; j < 4; ++j) vp[j] = ptx::lds128(s_row + ((static_cast<uint32_t>(j) ^ sw_row) << 4));
                     __syncwarp();
                     if (c + kStride < kNStep / 32) fetch(c + kStride);
                     ptx::tmem_ld_wait();
@@ -563,7 +582,7 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
                     for (int half = 0; half < 2; ++half) {
 #pragma unroll
-                        for (int j = 0; j < 4; ++j) ptx::sts128(s_row + 16u * j, half == 0 ? og[j] : ov[j]);
+                        for (int j = 0; j < 4; ++j) ptx::sts128(s_row + ((static_cast<uint32_t>(j) ^ sw_row) << 4), half == 0 ? og[j] : ov[j]);
                         __syncwarp();
 #pragma unroll
                         for (int i = 0; i < 4; ++i) {
@@ -621,7 +640,9 @@ gemm_kernel(const __grid_constant__ CUtensorMap tmA, const __grid_constant__ CUt
 #pragma unroll
                         for (int j = 0; j < 4; ++j) {
                             const int col = tc.n0 + c * 32 + j * 8;
-                            if (col < n_out)  // n_out is a multiple of 8: a 16-byte vector is entirely in or out
+                            // n_out is a multiple of 8: a 16-byte vector is entirely in or out; a 48-column tile ends
+                            // in the middle of its second chunk
+                            if (col < n_out && (kNStep % 32 == 0 || c * 32 + j * 8 < kNStep))
                                 *reinterpret_cast<uint4*>(crow + c * 32 + j * 8) =
                                     make_uint4(out[4 * j], out[4 * j + 1], out[4 * j + 2], out[4 * j + 3]);
                         }
@@ -756,7 +777,7 @@ int launch_gemm(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
     // K-major B: a single CTA loads its B rows as two boxes of BN/2 rows (second one at the value rows for the
     // gate|value split); a pair loads one box of 128 rows per CTA.
     const bool okB = B_MN ? make_tmap(&tmB, g.b, g.k, g.b_rows, g.ldb, 64, g.dtype)
-                          : make_tmap(&tmB, g.b, g.b_rows, g.k, g.ldb, CG == 2 ? 128 : BN / 2, g.dtype);
+                          : make_tmap(&tmB, g.b, g.b_rows, g.k, g.ldb, CG == 2 ? 128 : ((BN < kBN && n_step_of(EPI, BN) == BN) ? BN : BN / 2), g.dtype);
     if (!okA || !okB) return MGR_ERR_CUDA;
     int* status = gemm_status_ptr(di);
     if (status == nullptr) return MGR_ERR_CUDA;
@@ -826,12 +847,30 @@ int launch_gemm_cg(const GemmArgs& g, const DeviceInfo& di, cudaStream_t s) {
         // 36 / 26 / 27 us. So: 32 columns only while 64 would still leave half the SMs idle.
         const int pinned = overrides().narrow;
         int bn = 0;
-        if (pinned >= 0) bn = pinned == 0 ? 0 : (pinned == 32 ? kBNTiny : kBNSmall);
-        // Up to 384 rows only: from 4 row tiles on, every narrow tile re-reads its 128 rows of A and the wide
-        // tiling wins again (w3 GEMM at 512 rows: 37.9 us wide against 42.3 us narrow; at 256 rows 36.6 against 21.8).
-        else if (wide_tiles * 2 <= di.sm_count && m_tiles <= 3) bn = small_tiles * 2 <= di.sm_count ? kBNTiny : kBNSmall;
+        if (pinned >= 0) {
+            bn = pinned == 0 ? 0 : (pinned == 32 ? kBNTiny : (pinned == 96 && EPI == kEpiSwiglu ? kBNMid : kBNSmall));
+        } else if (wide_tiles * 2 <= di.sm_count && m_tiles <= 3) {
+            // Up to 384 rows only: from 4 row tiles on, every narrow tile re-reads its 128 rows of A and the wide
+            // tiling wins again (w3 GEMM at 512 rows: 37.9 us wide against 42.3 us narrow; at 256 rows 36.6 against 21.8).
+            // Among the narrow widths: the one with the least (rounds over the SMs) x (tile width + a fixed cost per
+            // tile of about 16 columns' worth). For the 16-row batch above that is 32 columns for w3 (128 tiles, one
+            // round) and 48 + 48 for the projection (144 tiles, one round, where 32 + 32 needs two and 16 + 16 three).
+            (void)small_tiles;
+            const int widths[3] = {kBNTiny, kBNSmall, kBNMid};
+            int64_t best = 0;
+            for (int i = 0; i < (EPI == kEpiSwiglu ? 3 : 2); ++i) {
+                const int step = widths[i] / (EPI == kEpiSwiglu ? 2 : 1);
+                const int64_t tiles = m_tiles * ((g.n_out + step - 1) / step);
+                const int64_t rounds = (tiles + di.sm_count - 1) / di.sm_count;
+                const int64_t cost = rounds * (widths[i] + 16);
+                if (bn == 0 || cost < best) bn = widths[i], best = cost;
+            }
+        }
         if (bn == kBNTiny) return launch_gemm<EPI, A_MN, B_MN, 1, T, kBNTiny>(g, di, s);
         if (bn == kBNSmall) return launch_gemm<EPI, A_MN, B_MN, 1, T, kBNSmall>(g, di, s);
+        if constexpr (EPI == kEpiSwiglu) {
+            if (bn == kBNMid) return launch_gemm<EPI, A_MN, B_MN, 1, T, kBNMid>(g, di, s);
+        }
     }
     int cg = forced_cta_group();
     if (cg == 0) {

@@ -28,7 +28,7 @@ DeviceInfo current_device_info();
 // mgr_reload_env() is called, so that no launch pays for getenv:
 //   MGR_RMSNORM_PATH=reg|ring|scalar   kernel family            MGR_RMSNORM_FWD_SHAPE / _BWD_SHAPE=<index>  packet shape
 //   MGR_RMSNORM_BWD_FAT=0|1            backward packet kernel: one CTA per row group / one fat CTA per SM, for every shape
-//   MGR_GEMM_CTA_GROUP=1|2             MGR_GEMM_PDL=0           MGR_GEMM_NARROW=0|1|32
+//   MGR_GEMM_CTA_GROUP=1|2             MGR_GEMM_PDL=0           MGR_GEMM_NARROW=0|1|32|96
 struct Overrides {
     int rms_path;    // 0 automatic, 1 reg, 2 ring, 3 scalar
     int fwd_shape;   // -1 unset
@@ -36,7 +36,7 @@ struct Overrides {
     int bwd_fat;     // -1 per packet shape (the table's choice), 0 never, 1 always
     int cta_group;   // 0 automatic, 1, 2
     int pdl;         // 0 off, 1 on
-    int narrow;      // -1 automatic, 0 never, 64, 32
+    int narrow;      // -1 automatic, 0 never, 64, 32, 96 (the fused projection only; others take 64)
 };
 Overrides overrides();
 

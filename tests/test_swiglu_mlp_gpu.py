@@ -414,7 +414,8 @@ def test_cta_pair_kernels_equal_single_cta_kernels(ops, built_lib, mgr_env, dtyp
                                    # short A boxes whose contraction wraps the (run-time sized) stage ring several times
                                    (8, 4096, 1024), (1, 2048, 256), (24, 2048, 512), (56, 1600, 384), (120, 1536, 256)])
 def test_narrow_tile_kernels_equal_wide_tile_kernels(ops, built_lib, mgr_env, dtype, m, d, f):
-    """Skinny problems run on 64- or 32-column tiles (MGR_GEMM_NARROW=1 / =32 forces them, =0 forbids them) so
+    """Skinny problems run on 96-, 64- or 32-column tiles (MGR_GEMM_NARROW=96 / =1 / =32 forces them, =0 forbids
+    them; 96 = 48 gate + 48 value columns exists for the fused projection only, the plain GEMM then takes 64) so
     that more CTAs share the weight stream. Same K order, so the fused projection and the plain GEMM must be
     bit-identical to the 256-column kernels."""
     g = torch.Generator().manual_seed(m + d + f + 4)
@@ -423,14 +424,14 @@ def test_narrow_tile_kernels_equal_wide_tile_kernels(ops, built_lib, mgr_env, dt
     w12 = (torch.randn(2 * f, d, generator=g) / d ** 0.5).to(td).cuda()
     w3 = (torch.randn(d, f, generator=g) / f ** 0.5).to(td).cuda()
     outs = {}
-    for narrow in ("0", "1", "32"):
+    for narrow in ("0", "1", "32", "96"):
         mgr_env("MGR_GEMM_NARROW", narrow)
         mgr_env("MGR_GEMM_CTA_GROUP", "1")
         h = ops.swiglu_fused_forward(x, w12, f)
         outs[narrow] = (h, ops.linear_tn(h, w3))
         torch.cuda.synchronize()
     assert built_lib.mgr_device_status(1) == 0
-    for narrow in ("1", "32"):
+    for narrow in ("1", "32", "96"):
         assert torch.equal(outs["0"][0], outs[narrow][0]), f"fused projection differs with tile width {narrow}"
         assert torch.equal(outs["0"][1], outs[narrow][1]), f"plain GEMM differs with tile width {narrow}"
     gv = oracle.linear(to_np(x), to_np(w12))
