@@ -49,7 +49,23 @@ CPU_SAMPLE_ROWS = 4096
 # from the ncu capture summarised in profiles/rmsnorm_bf16_h8192_reg_kernels.txt: 16384 rows x 8192 bf16,
 # 537.0 MB read + 235.7 MB written against 805.4 MB algorithmic. Traffic grows in proportion to the rows,
 # so the full-size figure is this ratio times the full launch's algorithmic bytes.
-TRAFFIC_PER_ALGO_BYTE = (536.965888 + 235.687424) / 805.404672
+def _traffic_per_algorithmic_byte():
+    """Read from the committed ncu summary (the figures of the capture, not a copy of them); None when it is not there."""
+    import re
+    path = os.path.join(os.path.dirname(os.path.abspath(__file__)), "profiles", "rmsnorm_bf16_h8192_reg_kernels.txt")
+    try:
+        text = open(path).read()
+        block = text.split("kernel: rms_bwd_reg<__nv_bfloat16, 256, 4, 0>")[1].split("kernel:")[0]
+        rd = float(re.search(r"dram__bytes_read\.sum\s+([0-9.]+) Mbyte", block).group(1))
+        wr = float(re.search(r"dram__bytes_write\.sum\s+([0-9.]+) Mbyte", block).group(1))
+        rows = int(re.search(r"one launch each, (\d+) rows x 8192 bf16", text).group(1))
+    except (OSError, IndexError, AttributeError, ValueError):
+        return None
+    algorithmic = 3 * rows * 8192 * 2 + 2 * 8192 * 2 + 4 * rows
+    return (rd + wr) * 1e6 / algorithmic
+
+
+TRAFFIC_PER_ALGO_BYTE = _traffic_per_algorithmic_byte()
 
 
 def rms_bytes(rows: int, cols: int, s: int) -> dict:
