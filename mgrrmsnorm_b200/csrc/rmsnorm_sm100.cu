@@ -987,6 +987,11 @@ constexpr int default_bwd_shape(int64_t nvec, bool add16 = false) {
     // choices back for comparison.
     int base = reg_shape_for(nvec);
     if (add16 && nvec > 128 && nvec <= 256) base = 10;
+    // ... and where the fitted shapes lose to the shared-memory-weights form of the power-of-two shape above them
+    // (residual-add backward, bf16, fraction of the copy bandwidth): hidden 2560 0.87 with {128,4} against 0.83 with
+    // {160,2}; 3072 0.94 against 0.84 with {192,2}; 7168 0.96 with {256,4} against 0.93 with {448,2}. (Not at 5120:
+    // 0.83 against 0.87 with {320,2}.)
+    if (add16 && ((nvec > 256 && nvec <= 384) || (nvec > 768 && nvec <= 896))) return base;
     return tighter_fitted(nvec, base, true);
 }
 // Checked at compile time: every row of up to 4096 packets gets a shape that holds it (forward and backward),

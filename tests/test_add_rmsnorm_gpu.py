@@ -65,7 +65,8 @@ def test_matches_two_step_sequence_and_oracle(ops, rows, cols, dtype):
     # the residual-add backward alone for rows of 641-768 and 897-1024 packets. There dW is the same products in
     # another fixed grouping, held to the oracle above.
     packets = cols * x.element_size() // 16
-    one_sided = (x.element_size() == 2 and 192 < packets <= 256) or 640 < packets <= 768 or 896 < packets <= 1024
+    one_sided = (x.element_size() == 2 and (192 < packets <= 256 or 256 < packets <= 384 or 768 < packets <= 896)) or \
+        640 < packets <= 768 or 896 < packets <= 1024   # (16-bit 257-384 and 769-896: the residual-add form skips the fitted shapes)
     same_kernel = (cols * x.element_size() <= 16384 or rows < 8 * 148) and not one_sided
     if same_kernel:
         assert torch.equal(dw32, dw32_plain) and torch.equal(dw, dw_plain)
