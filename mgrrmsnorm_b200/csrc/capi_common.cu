@@ -11,7 +11,7 @@ namespace mgr {
 
 namespace {
 std::atomic<bool> g_env_loaded{false};
-std::atomic<int> g_env[7];
+std::atomic<int> g_env[8];
 
 void load_env() {
     auto num = [](const char* name, int unset) {
@@ -37,6 +37,7 @@ void load_env() {
     g_env[4].store(cg, std::memory_order_relaxed);
     g_env[5].store(pdl, std::memory_order_relaxed);
     g_env[6].store(narrow, std::memory_order_relaxed);
+    g_env[7].store(num("MGR_RMSNORM_PREFETCH", -1), std::memory_order_relaxed);
     g_env_loaded.store(true, std::memory_order_release);
 }
 }  // namespace
@@ -51,6 +52,7 @@ Overrides overrides() {
     o.cta_group = g_env[4].load(std::memory_order_relaxed);
     o.pdl = g_env[5].load(std::memory_order_relaxed);
     o.narrow = g_env[6].load(std::memory_order_relaxed);
+    o.prefetch = g_env[7].load(std::memory_order_relaxed);
     return o;
 }
 

@@ -41,6 +41,17 @@ struct RegGeom {
     static constexpr int kBwdMinBlocks = 512 / kBlock < 1 ? 1 : 512 / kBlock;
 };
 
+// Whether a kernel instance carries the code that asks L2 for the next row (prefetch_l2_bulk) at all. The host's
+// policy (use_prefetch) never turns it on for the shapes excluded here, and its mere presence costs the kernels
+// that are held to 40-64 registers: bf16 hidden 1536 ({192,1}) backward 0.78 with the unused code against 0.93
+// without, hidden 5120 ({320,2}) residual-add backward 0.75 against 0.87.
+constexpr bool prefetch_compiled(int tpr, int vpt, bool add, bool backward) {
+    const int cap = tpr * vpt;
+    if (!backward) return cap > 1024;
+    if (add) return cap > 128 && !(tpr == 320 && vpt == 2);
+    return cap >= 256;
+}
+
 // Sum of `v` over the TPR threads that share a row. `red` is a [2][kWarps] shared array used
 // alternately (`buf`), which makes one __syncthreads per reduction sufficient.
 template <int TPR>
@@ -70,7 +81,7 @@ template <typename T, int TPR, int VPT, bool ADD = false, bool WSM = false>
 // spilled and ran at 0.88 of the copy bandwidth on 2 KB rows; at 77 registers, no spills, 0.95)
 __global__ void __launch_bounds__(RegGeom<TPR>::kBlock, (TPR == 32 && VPT == 4) ? 3 : RegGeom<TPR>::kFwdMinBlocks)
 rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
-            const T* __restrict__ w, int64_t rows, int cols, float eps, const T* res = nullptr, T* h_out = nullptr) {
+            const T* __restrict__ w, int64_t rows, int cols, float eps, const T* res = nullptr, T* h_out = nullptr, int prefetch = 0) {
     using Geo = RegGeom<TPR>;
     constexpr int VEC = Elem<T>::kVec;
     __shared__ float red[2][Geo::kWarps];
@@ -96,9 +107,17 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
 
     const float inv_cols = 1.0f / static_cast<float>(cols);
     const int64_t ngroups = (rows + Geo::kGroups - 1) / Geo::kGroups;
+    [[maybe_unused]] const uint32_t row_bytes = static_cast<uint32_t>(cols) * sizeof(T);
     for (int64_t rg = blockIdx.x; rg < ngroups; rg += gridDim.x) {
         const int64_t r = rg * Geo::kGroups + group;
         const bool live = r < rows;
+        if constexpr (prefetch_compiled(TPR, VPT, ADD, false)) {   // the row this group visits next goes on its way into L2
+            const int64_t rn = (rg + gridDim.x) * Geo::kGroups + group;
+            if (prefetch != 0 && t == 0 && rn < rows) {
+                prefetch_l2_bulk(x + rn * static_cast<int64_t>(cols), row_bytes);
+                if constexpr (ADD) prefetch_l2_bulk(res + rn * static_cast<int64_t>(cols), row_bytes);
+            }
+        }
         const uint4* xr = reinterpret_cast<const uint4*>(x + (live ? r : 0) * static_cast<int64_t>(cols));
         uint4 xv[VPT];
 #pragma unroll
@@ -170,7 +189,7 @@ rms_fwd_reg(T* __restrict__ y, float* __restrict__ inv_rms, const T* x,
 template <typename T, int TPR, int VPT, bool ADD = false>
 __global__ void __launch_bounds__(RegGeom<TPR>::kBlock, (VPT <= 2 && TPR >= 160) ? (VPT == 1 ? 1536 : 1024) / RegGeom<TPR>::kBlock : RegGeom<TPR>::kBwdMinBlocks)
 rms_bwd_reg(T* dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
-            const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int cols, const T* dres = nullptr) {
+            const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int cols, const T* dres = nullptr, int prefetch = 0) {
     using Geo = RegGeom<TPR>;
     constexpr int VEC = Elem<T>::kVec;
     constexpr int G = Geo::kGroups;
@@ -198,9 +217,19 @@ rms_bwd_reg(T* dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __
 
     const float inv_cols = 1.0f / static_cast<float>(cols);
     const int64_t ngroups = (rows + G - 1) / G;
+    [[maybe_unused]] const uint32_t row_bytes = static_cast<uint32_t>(cols) * sizeof(T);
     for (int64_t rg = blockIdx.x; rg < ngroups; rg += gridDim.x) {
         const int64_t r = rg * G + group;
         const bool live = r < rows;
+        if constexpr (prefetch_compiled(TPR, VPT, ADD, true)) {   // the row this group visits next goes on its way into L2
+            const int64_t rn = (rg + gridDim.x) * G + group;
+            if (prefetch != 0 && t == 0 && rn < rows) {
+                const int64_t offn = rn * static_cast<int64_t>(cols);
+                prefetch_l2_bulk(x + offn, row_bytes);
+                prefetch_l2_bulk(dy + offn, row_bytes);
+                if constexpr (ADD) prefetch_l2_bulk(dres + offn, row_bytes);
+            }
+        }
         const int64_t off = (live ? r : 0) * static_cast<int64_t>(cols);
         const uint4* xr = reinterpret_cast<const uint4*>(x + off);
         const uint4* gr = reinterpret_cast<const uint4*>(dy + off);
@@ -398,7 +427,7 @@ __device__ __forceinline__ float group_sum(float v, float* red_all, int& buf, in
 template <typename T, int TPR, int VPT, bool ADD = false>
 __global__ void __launch_bounds__(BwdGeom<TPR, VPT>::kBlock, BwdGeom<TPR, VPT>::kMinBlocks)
 rms_bwd_fat(T* dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
-            const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int cols, const T* dres = nullptr) {
+            const T* __restrict__ w, const float* __restrict__ inv_rms, int64_t rows, int cols, const T* dres = nullptr, int prefetch = 0) {
     using Geo = BwdGeom<TPR, VPT>;
     constexpr int VEC = Elem<T>::kVec;
     constexpr int G = Geo::kGroups;
@@ -431,9 +460,19 @@ rms_bwd_fat(T* dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __
     // rows, so the early exit below is taken by whole groups. (Written with the row-group counter as the loop
     // variable: the form that counts rows directly costs the half-precision kernels 50-80 bytes more in spills.)
     const int64_t ngroups = (rows + G - 1) / G;
+    [[maybe_unused]] const uint32_t row_bytes = static_cast<uint32_t>(cols) * sizeof(T);
     for (int64_t rg = blockIdx.x; rg < ngroups; rg += gridDim.x) {
         const int64_t r = rg * G + group;
         if (r >= rows) break;
+        if constexpr (prefetch_compiled(TPR, VPT, ADD, true)) {   // the row this group visits next goes on its way into L2
+            const int64_t rn = (rg + gridDim.x) * G + group;
+            if (prefetch != 0 && t == 0 && rn < rows) {
+                const int64_t offn = rn * static_cast<int64_t>(cols);
+                prefetch_l2_bulk(x + offn, row_bytes);
+                prefetch_l2_bulk(dy + offn, row_bytes);
+                if constexpr (ADD) prefetch_l2_bulk(dres + offn, row_bytes);
+            }
+        }
         const int64_t off = r * static_cast<int64_t>(cols);
         const uint4* xr = reinterpret_cast<const uint4*>(x + off);
         const uint4* gr = reinterpret_cast<const uint4*>(dy + off);
@@ -593,7 +632,7 @@ __global__ void __launch_bounds__(BwdGeom<TPR, VPT>::kBlock, BwdGeom<TPR, VPT>::
 // (dx carries __restrict__ although the residual-add form allows dx == dres: a thread reads its packets of a row
 // before it writes them and no other thread touches them, so no reordering the qualifier permits can change a value)
 rms_bwd_wsm(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy, const T* __restrict__ x,
-            const T* __restrict__ w, const float* __restrict__ inv_rms, int rows, int cols, const T* dres = nullptr) {
+            const T* __restrict__ w, const float* __restrict__ inv_rms, int rows, int cols, const T* dres = nullptr, int prefetch = 0) {
     using Geo = BwdGeom<TPR, VPT>;
     constexpr int VEC = Elem<T>::kVec;
     constexpr int G = Geo::kGroups;
@@ -645,7 +684,16 @@ rms_bwd_wsm(T* __restrict__ dx, float* __restrict__ ws, const T* __restrict__ dy
         wsm[v] = v < nvec ? __ldg(reinterpret_cast<const uint4*>(w) + v) : make_uint4(0, 0, 0, 0);
     const int stride = gridDim.x * G;
     bool weights_pending = true;   // every thread meets the CTA exactly once, behind its first row's loads
+    [[maybe_unused]] const uint32_t row_bytes = static_cast<uint32_t>(cols) * sizeof(T);
     for (; r < rows; r += stride) {
+        if constexpr (prefetch_compiled(TPR, VPT, ADD, true)) {   // the row this group visits next goes on its way into L2
+            if (prefetch != 0 && t == 0 && r + stride < rows) {
+                const int64_t offn = static_cast<int64_t>(r + stride) * cols;
+                prefetch_l2_bulk(x + offn, row_bytes);
+                prefetch_l2_bulk(dy + offn, row_bytes);
+                if constexpr (ADD) prefetch_l2_bulk(dres + offn, row_bytes);
+            }
+        }
         load(r);
         if (weights_pending) { __syncthreads(); weights_pending = false; }
         float c = 0.f;
@@ -1023,6 +1071,26 @@ int bwd_shape_for(int64_t nvec, bool add16 = false) {
     return pinned >= 0 ? pinned : default_bwd_shape(nvec, add16);
 }
 
+// Whether a packet kernel asks L2 for its next row while it works on the current one (prefetch_l2_bulk). From
+// measurements on B200, 2^28 elements, fraction of the copy bandwidth with / without (MGR_RMSNORM_PREFETCH=0|1 pins it):
+//   backward, bf16: hidden 2048 0.95 / 0.94, 2560 0.98 / 0.93, 3072 0.99 / 0.93, 4096 0.98 / 0.96, 5120 0.99 / 0.89,
+//     6144 0.98 / 0.85, 7168 1.02 / 0.88, 8192 1.00 / 0.93, 12 288 0.91 / 0.75, 16 384 0.95 / 0.84 (the ring: 0.87),
+//     32 768 0.95 / 0.71 -- but hidden 1024 0.92 / 1.00 and 1536 0.77 / 0.93: rows of 2-3 KB mean many small requests;
+//   backward, fp32: hidden 4096 1.03 / 0.97, 8192 1.05 / 0.98 -- but 1024 0.96 / 1.05 and 2048 0.98 / 1.01;
+//   residual-add backward, bf16: hidden 1536 1.05 / 0.93, 2048 1.04 / 0.92, 2560-4096 0.99-1.03 / 0.87-0.99, 6144-12 288
+//     1.04-1.07 / 0.96-0.99, 32 768 0.82 / 0.73 -- but 5120 ({320,2}, one CTA per row) 0.71 / 0.87; fp32 4096 1.01 / 1.06;
+//   forward: already at the copy rate without it and slower with (bf16 hidden 4096 0.91 / 1.00, 8192 0.92 / 0.99),
+//     except for rows beyond 16 KB: hidden 12 288 0.98 / 0.86, 16 384 0.94 / 0.94, 32 768 0.99 / 0.80.
+// (The shapes for which this never says yes do not carry the code at all: prefetch_compiled.)
+bool use_prefetch(bool backward, bool add, size_t elem, int64_t nvec) {
+    const int pinned = overrides().prefetch;
+    if (pinned >= 0) return pinned != 0;
+    if (!backward) return nvec > 1024;
+    if (elem == 4) return add ? nvec >= 2048 : nvec >= 1024;
+    if (add) return (nvec > 128 && nvec <= 512) || nvec > 640;
+    return nvec >= 256;
+}
+
 template <typename K>
 int resident_ctas(K kernel, int block, std::atomic<int>* cache /* [kMaxDevices] */, int device) {
     int v = cache[device].load(std::memory_order_relaxed);
@@ -1100,21 +1168,23 @@ struct RegKernels {
     static void fwd(T* y, float* inv, const T* x, const T* w, int64_t rows, int cols, float eps,
                     const DeviceInfo& di, cudaStream_t s, const T* res, T* h_out) {
         const unsigned grid = static_cast<unsigned>(fwd_grid(rows, di));
+        const int pf = use_prefetch(false, ADD, sizeof(T), cols / Elem<T>::kVec) ? 1 : 0;
         if (fwd_wsm(rows, di)) {
-            if constexpr (FWD_WSM_ALWAYS || FWD_WSM_LARGE) rms_fwd_reg<T, TPR, VPT, ADD, true><<<grid, BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps, res, h_out);
+            if constexpr (FWD_WSM_ALWAYS || FWD_WSM_LARGE) rms_fwd_reg<T, TPR, VPT, ADD, true><<<grid, BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps, res, h_out, pf);
         } else {
-            if constexpr (!FWD_WSM_ALWAYS) rms_fwd_reg<T, TPR, VPT, ADD, false><<<grid, BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps, res, h_out);
+            if constexpr (!FWD_WSM_ALWAYS) rms_fwd_reg<T, TPR, VPT, ADD, false><<<grid, BLOCK, 0, s>>>(y, inv, x, w, rows, cols, eps, res, h_out, pf);
         }
     }
     static void bwd(T* dx, float* ws, const T* dy, const T* x, const T* w, const float* inv, int64_t rows,
                     int cols, int64_t grid, const DeviceInfo& di, cudaStream_t s, const T* dres) {
+        const int pf = use_prefetch(true, ADD, sizeof(T), cols / Elem<T>::kVec) ? 1 : 0;
         if (fat_bwd(rows, di)) {
             if constexpr (WSM)
-                rms_bwd_wsm<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BWD_BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, static_cast<int>(rows), cols, dres);
+                rms_bwd_wsm<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BWD_BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, static_cast<int>(rows), cols, dres, pf);
             else
-                rms_bwd_fat<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BWD_BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres);
+                rms_bwd_fat<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BWD_BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres, pf);
         } else
-            rms_bwd_reg<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres);
+            rms_bwd_reg<T, TPR, VPT, ADD><<<static_cast<unsigned>(grid), BLOCK, 0, s>>>(dx, ws, dy, x, w, inv, rows, cols, dres, pf);
     }
 };
 
@@ -1288,7 +1358,10 @@ bool prefer_ring_bwd(int64_t rows, int64_t cols, size_t elem, const DeviceInfo& 
     // Rows of 16-24 KB (1025-1536 packets) have a packet shape of their own, {384,4}: bf16 hidden 12 288 at 16 384 rows
     // 0.75 with it against 0.69 for the ring (2048 rows: 0.59 against 0.55). Beyond that the ring is ahead at every
     // row count measured (32 KB rows, 2048 to 32 768 rows: 0.66-0.90 against 0.65-0.84; fp32 0.86-0.98 against 0.74-0.87).
-    return rows >= 8ll * di.sm_count && row_bytes > 24576;
+    // With the next row requested into L2 ahead of time the {512,4} packet kernel passes the ring at 32 KB rows of a
+    // 16-bit type as well (bf16 hidden 16 384: 0.95 against 0.87; 2048 rows: 0.74 against 0.66); fp32 rows of 32 KB
+    // stay with the ring (1.07 against 1.05), and so do rows beyond 32 KB (equal at 64 KB: 0.95 / 0.94).
+    return rows >= 8ll * di.sm_count && row_bytes > (elem == 4 ? 24576 : 32768);
 }
 
 template <typename T>
