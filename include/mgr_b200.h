@@ -65,8 +65,8 @@ int mgr_abi_version(void);
 const char* mgr_status_str(int status);
 
 /* Re-reads the MGR_* environment variables that pin kernel choices for measurements and tests
- * (MGR_RMSNORM_PATH, MGR_RMSNORM_FWD_SHAPE, MGR_RMSNORM_BWD_SHAPE, MGR_RMSNORM_BWD_FAT, MGR_GEMM_CTA_GROUP,
- * MGR_GEMM_PDL, MGR_GEMM_NARROW). The library reads them once, at its first launch, so that no call pays
+ * (MGR_RMSNORM_PATH, MGR_RMSNORM_FWD_SHAPE, MGR_RMSNORM_BWD_SHAPE, MGR_RMSNORM_BWD_FAT, MGR_RMSNORM_PREFETCH,
+ * MGR_GEMM_CTA_GROUP, MGR_GEMM_PDL, MGR_GEMM_NARROW). The library reads them once, at its first launch, so that no call pays
  * for getenv; a process that changes them afterwards calls this. No reference counterpart (the reference
  * has no environment switches). */
 void mgr_reload_env(void);

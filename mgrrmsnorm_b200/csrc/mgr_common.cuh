@@ -28,6 +28,7 @@ DeviceInfo current_device_info();
 // mgr_reload_env() is called, so that no launch pays for getenv:
 //   MGR_RMSNORM_PATH=reg|ring|scalar   kernel family            MGR_RMSNORM_FWD_SHAPE / _BWD_SHAPE=<index>  packet shape
 //   MGR_RMSNORM_BWD_FAT=0|1            backward packet kernel: one CTA per row group / one fat CTA per SM, for every shape
+//   MGR_RMSNORM_PREFETCH=0|1           packet kernels: never / always ask L2 for the next row (where the kernel carries the code)
 //   MGR_GEMM_CTA_GROUP=1|2             MGR_GEMM_PDL=0           MGR_GEMM_NARROW=0|1|32|96
 struct Overrides {
     int rms_path;    // 0 automatic, 1 reg, 2 ring, 3 scalar
