@@ -355,6 +355,38 @@ def test_fat_and_thin_backward_kernels_agree(ops, built_lib, mgr_env, dtype, row
         assert torch.equal(dw, dw32.to(dw.dtype)), "dw must be exactly the rounded fp32 sum"
 
 
+# ---- the packet kernels' request to L2 for the next row ---------------------------------------------
+
+@pytest.mark.parametrize("dtype", ["f32", "f16", "bf16"])
+@pytest.mark.parametrize("rows,cols", [(3000, 8192), (5000, 4096), (2500, 12288), (4000, 2048), (1500, 16384), (2600, 5120),
+                                        (6000, 1024)])
+def test_l2_requests_for_the_next_row_do_not_change_results(ops, built_lib, mgr_env, dtype, rows, cols):
+    """MGR_RMSNORM_PREFETCH pins whether a packet kernel asks L2 for the row its group visits next (0 never, 1
+    wherever the kernel carries the request; unset: a measured policy per direction, type and row length). The
+    request moves nothing into the SM, so every output must be bit-identical either way -- with rows enough
+    that every CTA visits several."""
+    x, w, dy = seeded_rmsnorm_inputs(rows, cols, dtype, rows + cols + 1)
+    g = torch.Generator().manual_seed(rows)
+    res = torch.randn(rows, cols, generator=g).to(TORCH_DTYPES[dtype])
+    xd, wd, dyd, rd = x.cuda(), w.cuda(), dy.cuda(), res.cuda()
+    mgr_env("MGR_RMSNORM_PATH", "reg")
+    outs = {}
+    for pf in ("0", "1"):
+        mgr_env("MGR_RMSNORM_PREFETCH", pf)
+        y, inv = ops.rmsnorm_forward(xd, wd, 1e-6)
+        dx, dw, dw32 = ops.rmsnorm_backward_full(dyd, xd, wd, inv, True)
+        ya, h, inva = ops.add_rmsnorm_forward(xd, rd, wd, 1e-6)
+        dh, dwa, dwa32 = ops.add_rmsnorm_backward(dyd, rd, h, wd, inva, want_dw_f32=True)
+        torch.cuda.synchronize()
+        outs[pf] = [t.clone() for t in (y, inv, dx, dw, dw32, ya, h, inva, dh, dwa, dwa32)]
+    assert built_lib.mgr_device_status(1) == 0
+    names = ("y", "inv", "dx", "dw", "dw_f32", "add: y", "add: h", "add: inv", "add: dh", "add: dw", "add: dw_f32")
+    for name, a, b in zip(names, outs["0"], outs["1"]):
+        assert torch.equal(a, b), f"{name} differs with the L2 requests switched on"
+    tdx, _ = oracle.rmsnorm_bwd(to_np(dy), to_np(x), to_np(w), 1e-6)
+    assert_matches_truth(outs["1"][2], tdx, dtype, "dx")
+
+
 # ---- every kernel family on the same inputs --------------------------------------------------------
 
 @pytest.mark.parametrize("path", ["reg", "ring", "scalar"])
