@@ -5,7 +5,10 @@
 // rounding on store), different execution plan:
 //   * a row lives in registers (16-byte packets), so x (and dy) are read from HBM once per direction
 //     -- the reference makes two passes over each row;
-//   * CTAs are persistent (grid = SMs x resident CTAs) and keep the weight row in registers;
+//   * CTAs are persistent (grid = SMs x resident CTAs) and keep the weight row in registers, or, where the registers
+//     are better spent on rows in flight, in shared memory (rms_bwd_wsm, rms_fwd_reg<.., WSM>);
+//   * while a group of threads works on one row, L2 is asked for the row it visits next (prefetch_l2_bulk), by a
+//     measured per-case policy (use_prefetch);
 //   * dW is accumulated per thread in fp32 registers over all rows a CTA visits, written once as a
 //     per-CTA partial row, and summed by a second fixed-order kernel -- no atomics, so dW is
 //     bit-reproducible (the reference: atomicAdd at :319-322, half-precision atomics at :421-422).
