@@ -238,8 +238,8 @@ def workload_config(n_gpus: int, rows: int = TOTAL_ROWS) -> dict:
     return {"workload": f"RMSNorm bf16 forward+backward, {rows} rows x hidden {HIDDEN} in total, eps 1e-6 "
                         "(x~N(0,2), w=1+0.1N(0,1), dy~N(0,1))" + ("" if rows == TOTAL_ROWS else " [REDUCED CASE, not the benchmark]"),
             "rows_total": rows, "rows_per_gpu": per, "hidden": HIDDEN,
-            "sharding": (f"contiguous row blocks over {n_gpus} ranks, fp32 dW all-reduce every step (on a side stream, beside the next "
-                         "step's forward), one rounding after it") if n_gpus > 1 else "none",
+            "sharding": (f"contiguous row blocks over {n_gpus} ranks, fp32 dW summed across the ranks every step, "
+                         "one rounding after it") if n_gpus > 1 else "none",
             "l2": f"inputs larger than L2 ({per * HIDDEN * 2 >> 20} MiB per tensor and GPU, four tensors per step, 126 MB L2)", "seed": SEED}
 
 
@@ -316,7 +316,7 @@ class RmsBuffers:
             raise RuntimeError(f"mgr_rmsnorm_bwd status {st}")
 
 
-def time_device_resident(bufsets, steps, warmup, world, sampler=None, reduce="side", per_kernel_events=True):
+def time_device_resident(bufsets, steps, warmup, world, sampler=None, reduce="side", per_kernel_events=True, peer=None):
     """K steps over `bufsets` (rotated), CUDA events on the launching stream. Returns total ms, mean
     fwd-call ms, mean bwd-call ms and the wall-clock window of the timed region."""
     import torch.distributed as dist
@@ -330,12 +330,17 @@ def time_device_resident(bufsets, steps, warmup, world, sampler=None, reduce="si
     # (mgrrmsnorm_b200.sharding.AsyncDwReduce is the library's helper for exactly this.)
     # reduce="inline": the same all-reduce and rounding on the compute stream, right after the backward
     # (sharding.allreduce_dw), so its whole latency is exposed.
+    # reduce="peer": the sum as ONE kernel per rank over NVLink peer memory (sharding.PeerDwAllReduce,
+    # mgr_peer_allreduce_f32) on the compute stream right after the backward: a few microseconds where the NCCL
+    # collective takes 18 (2-4 GPUs) to 55 (8 GPUs).
+    # reduce="peer_side": that kernel on the (high-priority) side stream, beside the next forward.
     red = None
     inline = world > 1 and reduce == "inline"
-    if world > 1 and reduce == "side":
+    use_peer = world > 1 and reduce == "peer" and peer is not None
+    if world > 1 and reduce in ("side", "peer_side"):
         from mgrrmsnorm_b200.sharding import AsyncDwReduce
 
-        red = AsyncDwReduce(torch.cuda.current_device())
+        red = AsyncDwReduce(torch.cuda.current_device(), peer=peer if reduce == "peer_side" else None)
         for b in bufsets:
             b.second_dw_pair()
     turn = [0]
@@ -359,6 +364,8 @@ def time_device_resident(bufsets, steps, warmup, world, sampler=None, reduce="si
             evs[2].record(stream)
         if red is not None:
             red.start(*b.dw_pairs[pair])
+        elif use_peer:
+            peer(b.dw32, b.dw)                       # fp32 sum over the ranks in rank order, one rounding
         elif inline:
             dist.all_reduce(b.dw32, op=dist.ReduceOp.SUM)
             b.dw.copy_(b.dw32)                       # the single rounding
@@ -968,13 +975,16 @@ def time_cpu_mlp(mlp, f) -> dict:
 # compact side records of the default run
 # ---------------------------------------------------------------------------------------------------
 
-def allreduce_cost(buf, steps, warmup, world, job_bytes, side_run) -> dict:
-    """What the latency-bound dW collective costs: the same resident loop with the fp32 all-reduce and the
-    rounding on the COMPUTE stream (fully exposed), against the default (side stream, beside the next forward);
-    and the collective alone, back to back on one stream."""
+def allreduce_cost(buf, steps, warmup, world, job_bytes, side_run, peer=None, peer_run=None) -> dict:
+    """What the latency-bound dW collective costs: the same resident loop with the fp32 NCCL all-reduce and the
+    rounding on the COMPUTE stream (fully exposed), on a side stream beside the next forward, and -- the default
+    where peer memory is available -- as the library's own peer-memory kernel on the compute stream; and each
+    collective alone, back to back on one stream."""
     import torch.distributed as dist
 
     inline = time_device_resident([buf], steps, warmup, world, reduce="inline")
+    if peer is not None and side_run is None:
+        side_run = time_device_resident([buf], steps, warmup, world, reduce="side")
     t = torch.zeros(HIDDEN, dtype=torch.float32, device=buf.x.device)
     for _ in range(10):
         dist.all_reduce(t)
@@ -990,18 +1000,36 @@ def allreduce_cost(buf, steps, warmup, world, job_bytes, side_run) -> dict:
     alone_us = e0.elapsed_time(e1) * 1e3 / n
     ms_inline = inline["total_ms"] / steps
     ms_side = side_run["total_ms"] / steps
-    return {"bytes": HIDDEN * 4, "alone_us": alone_us, "on_compute_stream": {"ms_per_step": ms_inline, "value": job_bytes / ms_inline / 1e6},
-            "beside_next_forward": {"ms_per_step": ms_side, "value": job_bytes / ms_side / 1e6},
-            "exposed_us_per_step": (ms_inline - ms_side) * 1e3,
-            "note": "32 KB fp32 all-reduce per step: far below any bandwidth regime, so NCCL runs it as a single-step low-latency "
-                    "(LL protocol) exchange and its cost is launch + NVLink round-trip latency, not bytes"}
+    out = {"bytes": HIDDEN * 4, "nccl_alone_us": alone_us,
+           "nccl_on_compute_stream": {"ms_per_step": ms_inline, "value": job_bytes / ms_inline / 1e6},
+           "nccl_beside_next_forward": {"ms_per_step": ms_side, "value": job_bytes / ms_side / 1e6},
+           "note": "32 KB fp32 all-reduce per step: far below any bandwidth regime, so NCCL runs it as a low-latency (LL protocol) "
+                   "exchange and its cost is launch + NVLink round trips, not bytes; the peer-memory kernel is one launch per rank "
+                   "(stores to every peer, a bounded wait on flags, a local sum in rank order)"}
+    if peer is not None and peer_run is not None:
+        out_t = torch.empty(HIDDEN, dtype=torch.bfloat16, device=buf.x.device)
+        for _ in range(10):
+            peer(t, out_t)
+        dist.barrier()
+        torch.cuda.synchronize()
+        e0.record()
+        for _ in range(n):
+            peer(t, out_t)
+        e1.record()
+        torch.cuda.synchronize()
+        ms_peer = peer_run["total_ms"] / steps
+        out["peer_kernel_alone_us"] = e0.elapsed_time(e1) * 1e3 / n
+        out["peer_kernel_beside_next_forward"] = {"ms_per_step": ms_peer, "value": job_bytes / ms_peer / 1e6, "default": True}
+        ms_pi = time_device_resident([buf], steps, warmup, world, reduce="peer", peer=peer)["total_ms"] / steps
+        out["peer_kernel_on_compute_stream"] = {"ms_per_step": ms_pi, "value": job_bytes / ms_pi / 1e6}
+    return out
 
 
-def weak_scaling_figure(L, device, rank, world, warmup) -> dict:
+def weak_scaling_figure(L, device, rank, world, warmup, peer=None) -> dict:
     """The same loop with 65536 rows on EVERY GPU (per-GPU work fixed as N grows)."""
     buf = RmsBuffers(L, ROWS_PER_GPU, HIDDEN, torch.bfloat16, device, SEED + rank, x_scale=2.0 ** 0.5)
     steps = 40
-    r = time_device_resident([buf], steps, warmup, world)
+    r = time_device_resident([buf], steps, warmup, world, reduce="peer_side" if peer is not None else "side", peer=peer)
     ms = r["total_ms"] / steps
     out = {"scaling": "weak", "rows_per_gpu": ROWS_PER_GPU, "steps": steps, "ms_per_step": ms,
            "value": world * rms_bytes(ROWS_PER_GPU, HIDDEN, 2)["total"] / ms / 1e6, "unit": UNIT}
@@ -1077,7 +1105,7 @@ def prenorm_inference_compact(device) -> dict:
             "hbm_bytes_not_moved": 2 * m * d * 2}
 
 
-def parity_check(device, world, rank) -> dict:
+def parity_check(device, world, rank, peer=None) -> dict:
     """Sharded results against the one-rank result of the same library on the same seeded inputs, computed on the
     spot on every rank: row-sharded RMSNorm (y, dx bit-equal; dW = fp32 sum across ranks, one rounding, within one
     bf16 ulp of the one-rank dW), the side-stream all-reduce against the synchronous one (same bits), and the
@@ -1118,6 +1146,19 @@ def parity_check(device, world, rank) -> dict:
     red.drain()
     torch.cuda.synchronize()
     async_equal = bool(torch.equal(dw_async, shard.weight.grad))
+    # the peer-memory kernel: the partials added in rank order, the same bits on every rank, one rounding
+    peer_equal = None
+    if peer is not None:
+        _, _, part = ops.rmsnorm_backward_full(dy[r0:r1].contiguous(), xs.detach(), shard.weight.detach(), inv, True)
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        ordered = parts[0].clone()
+        for q in range(1, world):
+            ordered += parts[q]
+        dw_peer, dw_peer32 = torch.empty_like(shard.weight), torch.empty_like(part)
+        peer(part, dw_peer, dw_peer32)
+        torch.cuda.synchronize()
+        peer_equal = bool(torch.equal(dw_peer32, ordered) and torch.equal(dw_peer, ordered.to(dt)))
 
     torch.manual_seed(SEED)
     mlp = MegaGemmTriton(1024, multiple_of=256, hidden_multiple=2.0).to(device).to(dt)     # hidden 2048: divides by 2, 4, 8
@@ -1143,14 +1184,15 @@ def parity_check(device, world, rank) -> dict:
             "dw3": rel(tp.local.w3.weight.grad, mlp.w3.weight.grad[:, f0:f1])}
     torch.cuda.synchronize()
     status = int(_capi_status())
-    ok = rows_equal and async_equal and dw_ulps <= 1.0 and dw_differ < 0.05 and max(errs.values()) < 2e-2 and status == 0
+    ok = rows_equal and async_equal and peer_equal is not False and dw_ulps <= 1.0 and dw_differ < 0.05 and max(errs.values()) < 2e-2 and status == 0
     flag = torch.tensor([1.0 if ok else 0.0, dw_ulps, max(errs.values())], device=device)
     lo = flag.clone()
     dist.all_reduce(lo, op=dist.ReduceOp.MIN)
     dist.all_reduce(flag, op=dist.ReduceOp.MAX)
     return {"ok": bool(lo[0].item() == 1.0), "ranks": world,
             "rmsnorm": {"rows": rows, "hidden": cols, "y_dx_bit_equal_to_one_rank": rows_equal, "dw_max_bf16_ulps_from_one_rank": float(flag[1].item()),
-                        "dw_columns_differing": dw_differ, "async_allreduce_bit_equal_to_sync": async_equal},
+                        "dw_columns_differing": dw_differ, "async_allreduce_bit_equal_to_sync": async_equal,
+                        "peer_memory_sum_bit_equal_to_rank_ordered_sum": peer_equal},
             "tp_mlp": {"tokens": 512, "d_model": 1024, "hidden": mlp.hidden, "max_rel_err_over_ranks": float(flag[2].item()),
                        "rank0_rel_err": errs, "tolerance": 2e-2},
             "device_status": status}
@@ -1230,7 +1272,23 @@ def main(argv=None) -> int:
     sampler = ClockSampler(local_rank) if rank == 0 else None
     if sampler:
         sampler.start()
-    r = time_device_resident([main_buf], args.steps, warmup, world)
+    # dW across the ranks: the library's peer-memory kernel where symmetric memory can be had (every rank takes the
+    # same branch: the constructor is collective and its outcome is agreed on below), else NCCL on a side stream
+    peer = None
+    if world > 1:
+        import torch.distributed as dist
+
+        try:
+            peer = sharding.PeerDwAllReduce(HIDDEN, device)
+            have = 1
+        except Exception as e:  # noqa: BLE001
+            peer_error = f"{type(e).__name__}: {str(e)[:200]}"
+            have = 0
+        flag = torch.tensor([have], device=device)
+        dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+        if int(flag.item()) == 0:
+            peer = None
+    r = time_device_resident([main_buf], args.steps, warmup, world, reduce="peer_side" if peer is not None else "side", peer=peer)
     if sampler:
         sampler.stop()
     nb = rms_bytes(local_rows, HIDDEN, 2)                 # this rank (rank 0 holds a largest block)
@@ -1251,7 +1309,8 @@ def main(argv=None) -> int:
             extras[name] = {"error": f"{type(e).__name__}: {str(e)[:300]}"}
 
     if world > 1:
-        guarded("allreduce", lambda: allreduce_cost(main_buf, args.steps, warmup, world, job_bytes, r))
+        guarded("allreduce", lambda: allreduce_cost(main_buf, args.steps, warmup, world, job_bytes, None if peer is not None else r,
+                                                    peer=peer, peer_run=r if peer is not None else None))
 
     e2e = None
     if not args.no_e2e:
@@ -1266,8 +1325,8 @@ def main(argv=None) -> int:
     del main_buf
     torch.cuda.empty_cache()
     if world > 1 and not args.no_side:
-        guarded("weak", lambda: weak_scaling_figure(L, device, rank, world, warmup))
-        guarded("parity_n", lambda: parity_check(device, world, rank))
+        guarded("weak", lambda: weak_scaling_figure(L, device, rank, world, warmup, peer))
+        guarded("parity_n", lambda: parity_check(device, world, rank, peer))
     side = {}
     if world == 1 and not args.no_side:
         side = side_results(L, device, peak_gbs)
@@ -1287,6 +1346,9 @@ def main(argv=None) -> int:
             "metric": METRIC, "value": value, "unit": UNIT, "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": ms_per_step, "higher_is_better": True, "scaling": "strong", "vs_baseline": None,
             "dtype": "bf16", "data": "synthetic", "config": workload_config(world, args.rows),
+            "dw_reduction": (None if world == 1 else
+                             "the library's peer-memory kernel (stores to every rank over NVLink, sum in rank order) on a high-priority side stream, beside the next step's forward" if peer is not None
+                             else "NCCL all-reduce on a side stream, beside the next step's forward"),
             "frac_of_hbm_peak": value / world / peak_gbs,
             "roofline": {"bound": "hbm", "kernel": "rms_bwd_reg + rms_dw_reduce4 (one mgr_rmsnorm_bwd call: dx and per-CTA partial rows of dW, then their fixed-order column sum)",
                          "achieved": bwd_gbs, "peak": peak_gbs, "unit": "GB/s", "frac": bwd_gbs / peak_gbs,
@@ -1309,7 +1371,8 @@ def main(argv=None) -> int:
                         "dW: fp32 sum all-reduced across ranks, rounded once, copied to pinned host memory",
                 "unpipelined_value": e2e["unpipelined_value"],
                 "unpipelined_path": "pinned host -> whole-tensor copies around the RMSNorm module fwd+bwd -> pinned host"},
-            "gpu_launches": 3 * args.steps, "launches_per_step": {"rms_fwd_reg": 1, "rms_bwd_reg": 1, "rms_dw_reduce4": 1},
+            "gpu_launches": (4 if peer is not None else 3) * args.steps,
+            "launches_per_step": dict({"rms_fwd_reg": 1, "rms_bwd_reg": 1, "rms_dw_reduce4": 1}, **({"peer_allreduce_f32": 1} if peer is not None else {})),
             "clocks": sampler.summary(*r["window"]) if sampler else None,
             "sm_count": sms.value, "device_status": status,
         }

@@ -273,6 +273,28 @@ int mgr_swiglu_fused_fwd_save(void* h, void* gv, const void* x, const void* w12,
 int mgr_swiglu_dh_dgv(void* dgv, const void* dy, const void* w3, const void* gv, int64_t m, int64_t d, int64_t f,
                       int dtype, void* stream);
 
+/* ------------------------------------------------------------------------------------------------
+ * Cross-rank sum of a short fp32 vector over NVLink peer memory (one process per GPU): the dW of a row-sharded
+ * RMSNorm, summed in fp32 across the ranks and rounded once. The reference has no distributed code, so this has no
+ * counterpart there; it replaces the NCCL all-reduce the multi-GPU layer of this library used first, which for a
+ * 32 KB vector is pure latency (18 us on 2-4 GPUs, 55 us on 8).
+ *
+ * Every rank owns one buffer of mgr_peer_allreduce_buffer_bytes(world, n_max) bytes that EVERY rank can write
+ * (peer-mapped: torch symmetric memory, CUDA IPC or cuMem exports all do), zero-filled before the first call,
+ * 256-byte aligned. `peer_buffers` is a HOST array of `world` device pointers: entry q is rank q's buffer as mapped
+ * in the calling process (entry `rank` is the caller's own). `calls` is MGR_PEER_ALLREDUCE_CTAS uint32 counters in
+ * the caller's own device memory, zero-filled once; the kernel keeps its call number there, so a captured graph
+ * replays correctly. One launch per rank: stores this rank's `src[n]` into every rank's buffer, waits until every
+ * rank's contribution has arrived in its own, adds them in rank order (the same order, hence the same bits, on
+ * every rank) and writes out_f32[n] (may be NULL) and out[n] in `dtype` (may be NULL; not both).
+ *   n a multiple of 4, n <= n_max; all ranks call with the same n, in the same order, once per step each.
+ * The wait is bounded (about a second); if a rank never arrives the kernel returns, leaves the outputs unwritten and
+ * mgr_device_status() reports MGR_ERR_DEVICE_TIMEOUT. Only peer STORES and local loads are used. */
+#define MGR_PEER_ALLREDUCE_CTAS 16
+size_t mgr_peer_allreduce_buffer_bytes(int world, int64_t n_max);
+int mgr_peer_allreduce_f32(const void* const* peer_buffers, int rank, int world, const float* src, float* out_f32,
+                           void* out, int dtype, int64_t n, int64_t n_max, void* calls, void* stream);
+
 /* Limits the GEMM kernels of this process to `sms` SMs (0 = all of them); returns the previous limit.
  * The GEMM kernels are persistent (one CTA per SM), so a collective launched beside one finds no free SM
  * unless some are left out: a tensor-parallel caller lowers the limit around the GEMMs it overlaps with an

@@ -13,6 +13,7 @@ PKG_DIR = Path(__file__).resolve().parent
 LIB_PATH = PKG_DIR / "lib" / "libmgr_b200.so"
 
 MGR_F32, MGR_F16, MGR_BF16 = 0, 1, 2
+MGR_PEER_ALLREDUCE_CTAS = 16   # as in include/mgr_b200.h
 
 MGR_OK = 0
 MGR_ERR_BAD_DTYPE = -1
@@ -57,6 +58,8 @@ SIGNATURES = {
     "mgr_swiglu_fused_fwd_save": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "mgr_swiglu_dh_dgv": (_int, [_vp, _vp, _vp, _vp, _i64, _i64, _i64, _int, _vp]),
     "mgr_gemm_set_sm_limit": (_int, [_int]),
+    "mgr_peer_allreduce_buffer_bytes": (_sz, [_int, _i64]),
+    "mgr_peer_allreduce_f32": (_int, [_vp, _int, _int, _vp, _vp, _vp, _int, _i64, _i64, _vp, _vp]),
 }
 
 

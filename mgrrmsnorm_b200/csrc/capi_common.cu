@@ -84,6 +84,7 @@ DeviceInfo current_device_info() {
 
 int rmsnorm_status_fetch(int clear);  // rmsnorm_sm100.cu
 int gemm_status_fetch(int clear);     // gemm_sm100.cu
+int peer_status_fetch(int clear);     // peer_allreduce_sm100.cu
 int rmsnorm_status_poke(int value);   // rmsnorm_sm100.cu
 int gemm_status_poke(int value);      // gemm_sm100.cu
 
@@ -94,7 +95,8 @@ extern "C" int mgr_device_status(int clear) {
     if (di.status != MGR_OK) return di.status;
     const int a = mgr::rmsnorm_status_fetch(clear);
     const int b = mgr::gemm_status_fetch(clear);
-    return a != MGR_OK ? a : b;
+    const int c = mgr::peer_status_fetch(clear);
+    return a != MGR_OK ? a : (b != MGR_OK ? b : c);
 }
 
 extern "C" int mgr_debug_poke_device_status(int family, int value) {

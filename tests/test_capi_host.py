@@ -169,3 +169,26 @@ def test_no_device_is_reported_not_crashed(built_lib):
     assert built_lib.mgr_device_check(ctypes.byref(sms)) == _capi.MGR_ERR_CUDA
     st = built_lib.mgr_rmsnorm_fwd(P, P, P, P, 4, 64, 1e-5, _capi.MGR_F32, None)
     assert st == _capi.MGR_ERR_CUDA
+
+
+def test_peer_allreduce_argument_errors(built_lib):
+    """mgr_peer_allreduce_f32 checks its arguments on the host before anything is launched (no GPU needed)."""
+    import ctypes
+
+    L = built_lib
+    assert L.mgr_peer_allreduce_buffer_bytes(2, 8192) == (2 * 2 * 8192 * 4) + 2 * _capi.MGR_PEER_ALLREDUCE_CTAS * 4
+    assert L.mgr_peer_allreduce_buffer_bytes(0, 8192) == 0 and L.mgr_peer_allreduce_buffer_bytes(17, 8192) == 0
+    assert L.mgr_peer_allreduce_buffer_bytes(2, 6) == 0          # not a multiple of 4
+    P = 0x10000
+    bufs = (ctypes.c_void_p * 2)(P, P)
+    call = lambda **kw: L.mgr_peer_allreduce_f32(kw.get("bufs", bufs), kw.get("rank", 0), kw.get("world", 2), kw.get("src", P),  # noqa: E731
+                                                 kw.get("out32", P), kw.get("out", None), kw.get("dtype", _capi.MGR_BF16),
+                                                 kw.get("n", 64), kw.get("n_max", 64), kw.get("calls", P), None)
+    assert call(dtype=7) == _capi.MGR_ERR_BAD_DTYPE
+    assert call(rank=2) == _capi.MGR_ERR_BAD_SHAPE and call(world=0) == _capi.MGR_ERR_BAD_SHAPE and call(world=17) == _capi.MGR_ERR_BAD_SHAPE
+    assert call(n=6) == _capi.MGR_ERR_BAD_SHAPE and call(n=128, n_max=64) == _capi.MGR_ERR_BAD_SHAPE
+    assert call(src=None) == _capi.MGR_ERR_NULL_PTR and call(calls=None) == _capi.MGR_ERR_NULL_PTR
+    assert call(out32=None, out=None) == _capi.MGR_ERR_NULL_PTR
+    assert call(bufs=(ctypes.c_void_p * 2)(P, None)) == _capi.MGR_ERR_NULL_PTR
+    assert call(bufs=(ctypes.c_void_p * 2)(P, P + 16)) == _capi.MGR_ERR_MISALIGNED
+    assert call(src=P + 4) == _capi.MGR_ERR_MISALIGNED

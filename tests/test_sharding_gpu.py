@@ -1,6 +1,8 @@
 """Row-sharded RMSNorm, tensor-parallel SwiGLU and the sequence-parallel pre-norm block on two real GPUs
-(NCCL), against the single-GPU result of the same library. Skipped with fewer than two devices. Ranks are child processes; they meet
-only in collectives between kernels, NVLS is switched off, and nothing waits on a peer inside a kernel."""
+(NCCL), against the single-GPU result of the same library. Skipped with fewer than two devices. Ranks are child processes; in
+the first test they meet only in collectives between kernels, with NVLS switched off. The second test runs the library's
+own peer-memory sum of dW, whose kernel waits for its peers with a bound of about a second and reports a timeout through
+the status word; no rank leaves early and nothing is made to time out."""
 import os
 import socket
 
@@ -174,3 +176,86 @@ def test_sharded_paths_on_two_gpus(built_lib):
         assert p.exitcode == 0
     for r in results:
         assert all(v is True or v == 1 for v in r[1:]), f"rank {r[0]}: rows/dw/y/dx/dw12/dw3/sequence-parallel = {r[1:]}"
+
+
+def _peer_worker(rank: int, world: int, port: int, q):
+    import torch.distributed as dist
+
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    torch.cuda.set_device(rank)
+    dev = torch.device("cuda", rank)
+    dist.init_process_group("nccl", rank=rank, world_size=world, device_id=dev)
+    try:
+        import rmsnorm_cuda_ops as ops
+        from mgrrmsnorm_b200 import sharding
+
+        n = 8192
+        try:
+            red = sharding.PeerDwAllReduce(n, dev)
+        except Exception as e:  # noqa: BLE001  (no symmetric memory on this machine: nothing to test)
+            q.put((rank, "skip", repr(e)[:200]))
+            return
+        g = torch.Generator(device=dev).manual_seed(50 + rank)
+        bad = []
+        for it, m in enumerate((8192, 8192, 4096, 8, 8192, 2560)):          # shorter vectors reuse the same buffers
+            part = torch.randn(m, device=dev, generator=g) * (10.0 ** (it % 3))
+            parts = [torch.empty_like(part) for _ in range(world)]
+            dist.all_gather(parts, part)
+            want = parts[0].clone()
+            for p_ in parts[1:]:
+                want += p_                                                    # rank order, as the kernel adds them
+            out32 = torch.empty_like(part)
+            out16 = torch.empty(m, device=dev, dtype=torch.bfloat16)
+            red(part, out16, out32)
+            torch.cuda.synchronize()
+            if not torch.equal(out32, want):
+                bad.append(f"call {it}: fp32 sum differs (max {float((out32 - want).abs().max()):.3g})")
+            if not torch.equal(out16, want.to(torch.bfloat16)):
+                bad.append(f"call {it}: rounded sum differs")
+        # behind the side-stream helper: same bits, and the partial buffer may be reused after wait_for
+        helper = sharding.AsyncDwReduce(dev, peer=red)
+        part = torch.randn(n, device=dev, generator=g)
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        want = sum(parts[1:], parts[0].clone())
+        outs = []
+        for _ in range(3):
+            o = torch.empty(n, device=dev, dtype=torch.float16)
+            helper.start(part, o)
+            helper.wait_for(part)
+            outs.append(o)
+        helper.drain()
+        torch.cuda.synchronize()
+        if not all(torch.equal(o, want.to(torch.float16)) for o in outs):
+            bad.append("AsyncDwReduce(peer=...) differs from the rank-ordered sum")
+        try:
+            ops.device_status()
+        except Exception as e:  # noqa: BLE001
+            bad.append(f"device status: {e}")
+        q.put((rank, "; ".join(bad) if bad else True, ""))
+    finally:
+        dist.barrier()
+        dist.destroy_process_group()
+
+
+def test_peer_memory_dw_sum_on_two_gpus(built_lib):
+    """mgr_peer_allreduce_f32 through sharding.PeerDwAllReduce: every rank gets the partials added in rank order
+    (bit-equal to that sum computed with torch on gathered partials), the rounded output is its one rounding,
+    vectors shorter than the buffers' capacity work, and the side-stream helper gives the same bits."""
+    if torch.cuda.device_count() < 2:
+        pytest.skip("needs two GPUs")
+    world = 2
+    ctx = mp.get_context("spawn")
+    q = ctx.Queue()
+    port = _free_port()
+    procs = [ctx.Process(target=_peer_worker, args=(r, world, port, q)) for r in range(world)]
+    for p in procs:
+        p.start()
+    results = [q.get(timeout=300) for _ in range(world)]
+    for p in procs:
+        p.join(timeout=120)
+        assert p.exitcode == 0
+    if any(r[1] == "skip" for r in results):
+        pytest.skip(f"symmetric memory unavailable: {results[0][2]}")
+    for r in results:
+        assert r[1] is True, f"rank {r[0]}: {r[1]}"
