@@ -284,9 +284,10 @@ int mgr_swiglu_dh_dgv(void* dgv, const void* dy, const void* w3, const void* gv,
  * 256-byte aligned. `peer_buffers` is a HOST array of `world` device pointers: entry q is rank q's buffer as mapped
  * in the calling process (entry `rank` is the caller's own). `calls` is MGR_PEER_ALLREDUCE_CTAS uint32 counters in
  * the caller's own device memory, zero-filled once; the kernel keeps its call number there, so a captured graph
- * replays correctly. One launch per rank: stores this rank's `src[n]` into every rank's buffer, waits until every
- * rank's contribution has arrived in its own, adds them in rank order (the same order, hence the same bits, on
- * every rank) and writes out_f32[n] (may be NULL) and out[n] in `dtype` (may be NULL; not both).
+ * replays correctly. One launch per rank: stores this rank's `src[n]` into every rank's buffer (each value paired
+ * with the call's number in one 8-byte store, so no fence or flag is needed), waits on the elements of every rank as
+ * they arrive in its own, adds them in rank order (the same order, hence the same bits, on every rank) and writes
+ * out_f32[n] (may be NULL) and out[n] in `dtype` (may be NULL; not both).
  *   n a multiple of 4, n <= n_max; all ranks call with the same n, in the same order, once per step each.
  * The wait is bounded (about a second); if a rank never arrives the kernel returns, leaves the outputs unwritten and
  * mgr_device_status() reports MGR_ERR_DEVICE_TIMEOUT. Only peer STORES and local loads are used. */

@@ -2,19 +2,20 @@
 // NVLink peer memory, one process per GPU.
 //
 // The reference has no distributed code. The library's multi-GPU layer first summed dW with an NCCL all-reduce, which
-// for 32 KB is pure latency: 18 us on 2-4 GPUs and 55 us on 8, against a rank's whole forward+backward of about
+// for 32 KB is pure latency: 18 us on 2-4 GPUs and 26-55 us on 8, against a rank's whole forward+backward of about
 // 105 us once 65 536 rows are split eight ways. This kernel is the same sum as ONE launch per rank over memory every
 // rank can write (torch symmetric memory; any peer-mapped allocation will do):
-//   1. every CTA owns a slice of the vector; it stores this rank's slice into slot [rank] of EVERY rank's buffer
-//      (plain peer stores: posted writes, no round trip), fences, and raises its flag in every rank's flag array;
-//   2. it waits (bounded) until every rank's flag for this slice has arrived in its own flag array;
-//   3. it adds the P slots of its slice in rank order and writes the fp32 sum and its one rounding to the weight type.
+//   1. every CTA owns a slice of the vector; it stores this rank's slice into slot [rank] of EVERY rank's buffer, each
+//      value paired with the number of this call in one 8-byte store (plain peer stores: posted writes, no round trip);
+//   2. it reads the P slots of its slice from its OWN buffer, waiting (bounded) on each element until it carries this
+//      call's number, adds them in rank order and writes the fp32 sum and its one rounding to the weight type.
 // The order of the additions is the rank order on every rank, so all ranks hold the same bits, and the same bits as a
 // one-rank run that adds the partials in that order. CTAs never wait for other CTAs of the same GPU, only for the
-// same slice on other GPUs, so no grid-wide barrier and no co-residency requirement on one GPU arises. Buffers are
-// double-buffered by the parity of a per-CTA call counter kept in device memory (so a captured graph replays
-// correctly): a rank can be at most one call ahead of any other, because finishing call k needs every rank's flag k.
-// No multicast and no remote loads are involved: stores to peers, loads from local memory.
+// same elements from other GPUs, so no grid-wide barrier and no co-residency requirement on one GPU arises. Buffers
+// are double-buffered by the parity of a per-CTA call counter kept in device memory (so a captured graph replays
+// correctly): a rank can be at most one call ahead of any other, because finishing call k needs every rank's
+// elements of call k, and those are only written once that rank has finished reading call k - 1.
+// No multicast, no fences and no remote loads are involved: 8-byte stores to peers, 8-byte loads from local memory.
 
 #include <atomic>
 
@@ -33,18 +34,21 @@ struct PeerBufs {
 };
 
 // Byte layout of every rank's buffer for vectors of up to `n_max` floats and `world` ranks:
-//   [0, 2 * world * n_max * 4)                 data: [parity][sender][n_max] floats
-//   [flags_off, + world * kPeerCtas * 4)       flags: [sender][cta] call numbers
-__host__ __device__ inline size_t peer_flags_offset(int world, int64_t n_max) {
-    return (static_cast<size_t>(2) * world * n_max * 4 + 255) / 256 * 256;
+//   [parity][sender][n_max] pairs {float bits, call number}, 8 bytes each
+// A pair is written with ONE 8-byte store and read with ONE 8-byte load, which are single accesses on NVLink as on
+// local memory: whoever sees the call number of this call sees the value written with it. So no fence and no
+// separate flag are needed (the fence.sys + release / acquire form of this kernel took 13 us on ONE rank; this form
+// takes 3), and a reader only ever waits for the very elements it is about to add.
+__host__ __device__ inline size_t peer_buffer_bytes(int world, int64_t n_max) {
+    return static_cast<size_t>(2) * world * n_max * 8;
 }
 
-__device__ __forceinline__ void st_release_sys(uint32_t* p, uint32_t v) {
-    asm volatile("st.release.sys.global.u32 [%0], %1;" ::"l"(p), "r"(v) : "memory");
+__device__ __forceinline__ void st_pair(uint2* p, uint32_t value, uint32_t call) {
+    asm volatile("st.volatile.global.v2.u32 [%0], {%1, %2};" ::"l"(p), "r"(value), "r"(call) : "memory");
 }
-__device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
-    uint32_t v;
-    asm volatile("ld.acquire.sys.global.u32 %0, [%1];" : "=r"(v) : "l"(p) : "memory");
+__device__ __forceinline__ uint2 ld_pair(const uint2* p) {
+    uint2 v;
+    asm volatile("ld.volatile.global.v2.u32 {%0, %1}, [%2];" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
     return v;
 }
 
@@ -62,65 +66,51 @@ peer_allreduce_f32(PeerBufs bufs, int rank, int world, const float* __restrict__
     }
     __syncthreads();
     const uint32_t call = call_s;
-    const int parity = static_cast<int>(call & 1u);
-    const size_t flags_off = peer_flags_offset(world, n_max);
-    // this CTA's slice, in packets of four floats (n is a multiple of 4)
-    const int n4 = n >> 2;
-    const int per = (n4 + ctas - 1) / ctas;
-    const int lo = cta * per, hi = lo + per < n4 ? lo + per : n4;
+    const size_t parity = call & 1u;
+    // this CTA's slice of the vector
+    const int per = (n + ctas - 1) / ctas;
+    const int lo = cta * per, hi = lo + per < n ? lo + per : n;
 
-    // 1. this rank's slice into slot [rank] of every rank's buffer
-    const float4* s4 = reinterpret_cast<const float4*>(src);
-    for (int q = 0; q < world; ++q) {
-        float4* dst = reinterpret_cast<float4*>(bufs.base[q]) + (static_cast<size_t>(parity) * world + rank) * (n_max >> 2);
-        for (int i = lo + threadIdx.x; i < hi; i += kPeerThreads) dst[i] = s4[i];
-    }
-    __threadfence_system();
-    __syncthreads();
-    if (threadIdx.x < world) {
-        uint32_t* flag = reinterpret_cast<uint32_t*>(bufs.base[threadIdx.x] + flags_off) + static_cast<size_t>(rank) * ctas + cta;
-        st_release_sys(flag, call);
-    }
-
-    // 2. every rank's slice has arrived here (bounded wait: about a second, then the status word says so)
-    if (threadIdx.x < world) {
-        const uint32_t* flag = reinterpret_cast<const uint32_t*>(bufs.base[rank] + flags_off) + static_cast<size_t>(threadIdx.x) * ctas + cta;
-        bool seen = false;
-        for (int spin = 0; spin < (1 << 22); ++spin) {
-            if (static_cast<int32_t>(ld_acquire_sys(flag) - call) >= 0) {
-                seen = true;
-                break;
-            }
-            __nanosleep(200);
-        }
-        if (!seen) abort_s = 1;
-    }
-    __syncthreads();
-    if (abort_s != 0) {
-        if (threadIdx.x == 0) {
-            atomicExch(status, MGR_ERR_DEVICE_TIMEOUT);
-            calls[cta] = call;
-        }
-        return;
-    }
-
-    // 3. the sum, in rank order, from local memory (written by the peers: read past L1)
-    const float4* mine = reinterpret_cast<const float4*>(bufs.base[rank]) + static_cast<size_t>(parity) * world * (n_max >> 2);
+    // 1. this rank's slice, paired with the call number, into slot [rank] of every rank's buffer (peer stores)
     for (int i = lo + threadIdx.x; i < hi; i += kPeerThreads) {
-        float4 a = __ldcg(mine + i);
-        for (int q = 1; q < world; ++q) {
-            const float4 b = __ldcg(mine + static_cast<size_t>(q) * (n_max >> 2) + i);
-            a.x += b.x, a.y += b.y, a.z += b.z, a.w += b.w;
-        }
-        if (out_f32 != nullptr) reinterpret_cast<float4*>(out_f32)[i] = a;
-        if (out_t != nullptr) {
-            out_t[4 * i] = from_f32<T>(a.x);
-            out_t[4 * i + 1] = from_f32<T>(a.y);
-            out_t[4 * i + 2] = from_f32<T>(a.z);
-            out_t[4 * i + 3] = from_f32<T>(a.w);
+        const uint32_t v = __float_as_uint(src[i]);
+        for (int q = 0; q < world; ++q) {
+            uint2* dst = reinterpret_cast<uint2*>(bufs.base[q]) + (parity * world + rank) * n_max;
+            st_pair(dst + i, v, call);
         }
     }
-    if (threadIdx.x == 0) calls[cta] = call;
+
+    // 2. + 3. every rank's element as it arrives here (bounded wait: about a second in all, then the status word
+    // says so), added in rank order from local memory
+    const uint2* mine = reinterpret_cast<const uint2*>(bufs.base[rank]) + parity * world * n_max;
+    bool ok = true;
+    int budget = 1 << 22;
+    for (int i = lo + threadIdx.x; i < hi && ok; i += kPeerThreads) {
+        float sum = 0.f;
+        for (int q = 0; q < world && ok; ++q) {
+            const uint2* p = mine + static_cast<size_t>(q) * n_max + i;
+            uint2 v = ld_pair(p);
+            while (v.y != call) {
+                if (--budget <= 0 || *reinterpret_cast<volatile int*>(&abort_s) != 0) {
+                    ok = false;
+                    break;
+                }
+                __nanosleep(100);
+                v = ld_pair(p);
+            }
+            sum = q == 0 ? __uint_as_float(v.x) : sum + __uint_as_float(v.x);
+        }
+        if (ok) {
+            if (out_f32 != nullptr) out_f32[i] = sum;
+            if (out_t != nullptr) out_t[i] = from_f32<T>(sum);
+        }
+    }
+    if (!ok) abort_s = 1;
+    __syncthreads();
+    if (threadIdx.x == 0) {
+        if (abort_s != 0) atomicExch(status, MGR_ERR_DEVICE_TIMEOUT);
+        calls[cta] = call;
+    }
 }
 
 int* peer_status_ptr(const DeviceInfo& di) {
@@ -157,14 +147,14 @@ using namespace mgr;
 
 extern "C" size_t mgr_peer_allreduce_buffer_bytes(int world, int64_t n_max) {
     if (world < 1 || world > kPeerMaxRanks || n_max < 4 || n_max % 4 != 0 || n_max > (1ll << 24)) return 0;
-    return peer_flags_offset(world, n_max) + static_cast<size_t>(world) * MGR_PEER_ALLREDUCE_CTAS * 4;
+    return peer_buffer_bytes(world, n_max);
 }
 
 extern "C" int mgr_peer_allreduce_f32(const void* const* peer_buffers, int rank, int world, const float* src, float* out_f32,
                                       void* out, int dtype, int64_t n, int64_t n_max, void* calls, void* stream) {
     if (dtype_size(dtype) == 0) return MGR_ERR_BAD_DTYPE;
     if (world < 1 || world > kPeerMaxRanks || rank < 0 || rank >= world) return MGR_ERR_BAD_SHAPE;
-    if (n < 4 || n % 4 != 0 || n_max < n || n_max % 4 != 0 || n_max > (1ll << 24)) return MGR_ERR_BAD_SHAPE;
+    if (n < 4 || n % 4 != 0 || n_max < n || n_max % 4 != 0 || n_max > (1ll << 24)) return MGR_ERR_BAD_SHAPE;   // (multiples of 4: 16-byte rows)
     if (peer_buffers == nullptr || src == nullptr || calls == nullptr || (out_f32 == nullptr && out == nullptr)) return MGR_ERR_NULL_PTR;
     if (!aligned_to(src, 16) || !aligned_to(out_f32, 16) || !aligned_to(out, dtype_size(dtype)) || !aligned_to(calls, 4)) return MGR_ERR_MISALIGNED;
     PeerBufs bufs{};

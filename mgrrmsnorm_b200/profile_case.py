@@ -4,7 +4,9 @@
     ncu --set full --clock-control none -k regex:rms_ -c 6 -o out python -m mgrrmsnorm_b200.profile_case ...
 
 Cases: rmsnorm (forward + backward), add_rmsnorm (residual add fused, forward + backward), swiglu_act
-(stand-alone activation forward + backward; --cols is the hidden size f, the projected tensor is [rows, 2f]).
+(stand-alone activation forward + backward; --cols is the hidden size f, the projected tensor is [rows, 2f]),
+peer_allreduce (the cross-rank sum of a --cols long fp32 vector run as a ONE-rank group in this process, which is
+the only form a profiler may wrap: the kernel stores to and reads from its own buffer; --rows is ignored).
 --path reg|ring|scalar pins the RMSNorm kernel family (MGR_RMSNORM_PATH); the default is the library's own
 choice for the shape, which is what the profiles under profiles/ document. Inputs are generated on the
 device before the first call; keep them larger than L2 (126 MB) and small enough for a profiler's replays.
@@ -22,7 +24,7 @@ DTYPES = {"f32": torch.float32, "f16": torch.float16, "bf16": torch.bfloat16}
 
 def main(argv=None) -> int:
     ap = argparse.ArgumentParser(description=__doc__)
-    ap.add_argument("--case", choices=["rmsnorm", "add_rmsnorm", "swiglu_act"], required=True)
+    ap.add_argument("--case", choices=["rmsnorm", "add_rmsnorm", "swiglu_act", "peer_allreduce"], required=True)
     ap.add_argument("--rows", type=int, required=True)
     ap.add_argument("--cols", type=int, required=True)
     ap.add_argument("--dtype", choices=sorted(DTYPES), default="bf16")
@@ -44,7 +46,23 @@ def main(argv=None) -> int:
     def rnd(*shape):
         return torch.randn(*shape, device=dev, generator=g).to(dt)
 
-    if args.case == "swiglu_act":
+    if args.case == "peer_allreduce":
+        import ctypes
+
+        from . import _capi
+
+        L = _capi.lib()
+        n = cols // 4 * 4
+        buf = torch.zeros(int(L.mgr_peer_allreduce_buffer_bytes(1, n)), dtype=torch.uint8, device=dev)
+        calls = torch.zeros(_capi.MGR_PEER_ALLREDUCE_CTAS, dtype=torch.int32, device=dev)
+        src, out = torch.randn(n, device=dev, generator=g), torch.empty(n, device=dev, dtype=dt)
+        ptrs = (ctypes.c_void_p * 1)(buf.data_ptr())
+        for _ in range(args.iters):
+            _capi.check("mgr_peer_allreduce_f32", L.mgr_peer_allreduce_f32(ptrs, 0, 1, src.data_ptr(), None, out.data_ptr(), ops._DTYPES[dt], n, n,
+                                                                          calls.data_ptr(), torch.cuda.current_stream().cuda_stream))
+        torch.cuda.synchronize()
+        assert torch.equal(out, src.to(dt))
+    elif args.case == "swiglu_act":
         gv, dh = rnd(rows, 2 * cols), rnd(rows, cols)
         for _ in range(args.iters):
             ops.swiglu_act_forward(gv, cols)

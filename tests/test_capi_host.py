@@ -176,7 +176,7 @@ def test_peer_allreduce_argument_errors(built_lib):
     import ctypes
 
     L = built_lib
-    assert L.mgr_peer_allreduce_buffer_bytes(2, 8192) == (2 * 2 * 8192 * 4) + 2 * _capi.MGR_PEER_ALLREDUCE_CTAS * 4
+    assert L.mgr_peer_allreduce_buffer_bytes(2, 8192) == 2 * 2 * 8192 * 8      # [parity][sender][n] pairs of {value, call number}
     assert L.mgr_peer_allreduce_buffer_bytes(0, 8192) == 0 and L.mgr_peer_allreduce_buffer_bytes(17, 8192) == 0
     assert L.mgr_peer_allreduce_buffer_bytes(2, 6) == 0          # not a multiple of 4
     P = 0x10000
