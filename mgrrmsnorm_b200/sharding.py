@@ -244,13 +244,14 @@ class RowShardedRMSNormFunction(torch.autograd.Function):
     """RMSNormFunction for a rank that holds a row block: same forward; backward all-reduces dW."""
 
     @staticmethod
-    def forward(ctx, input, weight, epsilon, group):
+    def forward(ctx, input, weight, epsilon, group, peer=None):
         orig_shape = input.shape
         input_2d = input.view(-1, input.size(-1))
         output, inv_rms = rmsnorm_cuda_ops.rmsnorm_forward(input_2d, weight, epsilon)
         ctx.save_for_backward(input_2d, weight, inv_rms)
         ctx.orig_shape = orig_shape
         ctx.group = group
+        ctx.peer = peer
         return output.view(orig_shape)
 
     @staticmethod
@@ -258,23 +259,29 @@ class RowShardedRMSNormFunction(torch.autograd.Function):
         input_2d, weight, inv_rms = ctx.saved_tensors
         g2d = grad_output.contiguous().view(-1, grad_output.size(-1))
         grad_input, _, dw_f32 = rmsnorm_cuda_ops.rmsnorm_backward_full(g2d, input_2d, weight, inv_rms, want_dw_f32=True)
-        grad_weight = allreduce_dw(dw_f32, weight.dtype, ctx.group)
-        return grad_input.view(ctx.orig_shape), grad_weight, None, None
+        if ctx.peer is not None:      # the library's peer-memory kernel: partials added in rank order, one rounding
+            grad_weight = torch.empty_like(weight)
+            ctx.peer(dw_f32, grad_weight)
+        else:
+            grad_weight = allreduce_dw(dw_f32, weight.dtype, ctx.group)
+        return grad_input.view(ctx.orig_shape), grad_weight, None, None, None
 
 
 class RowShardedRMSNorm(nn.Module):
     """megagemm.RMSNorm whose input is this rank's row block of a larger batch; `weight` is replicated
-    and its gradient is the sum over all ranks' rows."""
+    and its gradient is the sum over all ranks' rows. `peer`: a PeerDwAllReduce of the same group (and at least
+    hidden_size long); the sum is then taken by that kernel over NVLink peer memory instead of NCCL."""
 
-    def __init__(self, hidden_size: int, epsilon: float = 1e-5, group=None):
+    def __init__(self, hidden_size: int, epsilon: float = 1e-5, group=None, peer=None):
         super().__init__()
         self.hidden_size = hidden_size
         self.epsilon = epsilon
         self.group = group
+        self.peer = peer
         self.weight = nn.Parameter(torch.ones(hidden_size))
 
     def forward(self, input: torch.Tensor) -> torch.Tensor:
-        return RowShardedRMSNormFunction.apply(input, self.weight, self.epsilon, self.group)
+        return RowShardedRMSNormFunction.apply(input, self.weight, self.epsilon, self.group, self.peer)
 
     def extra_repr(self) -> str:
         return f"hidden_size={self.hidden_size}, eps={self.epsilon}, row-sharded"

@@ -228,6 +228,23 @@ def _peer_worker(rank: int, world: int, port: int, q):
         torch.cuda.synchronize()
         if not all(torch.equal(o, want.to(torch.float16)) for o in outs):
             bad.append("AsyncDwReduce(peer=...) differs from the rank-ordered sum")
+        # inside the row-sharded module: dW = the one rounding of the rank-ordered sum of the ranks' fp32 partials
+        gen = torch.Generator().manual_seed(9)
+        rows, cols = 1000, 4096
+        x = torch.randn(rows, cols, generator=gen).bfloat16()
+        dy = torch.randn(rows, cols, generator=gen).bfloat16()
+        r0, r1 = sharding.row_shard(rows, world, rank)
+        mod = sharding.RowShardedRMSNorm(cols, epsilon=1e-6, peer=red).to(dev).bfloat16()
+        xs = x[r0:r1].to(dev).requires_grad_(True)
+        mod(xs).backward(dy[r0:r1].to(dev))
+        _, inv = ops.rmsnorm_forward(xs.detach(), mod.weight.detach(), 1e-6)
+        _, _, part = ops.rmsnorm_backward_full(dy[r0:r1].to(dev), xs.detach(), mod.weight.detach(), inv, want_dw_f32=True)
+        parts = [torch.empty_like(part) for _ in range(world)]
+        dist.all_gather(parts, part)
+        want = sum(parts[1:], parts[0].clone()).to(torch.bfloat16)
+        torch.cuda.synchronize()
+        if not torch.equal(mod.weight.grad, want):
+            bad.append("RowShardedRMSNorm(peer=...) weight gradient differs from the rank-ordered sum")
         try:
             ops.device_status()
         except Exception as e:  # noqa: BLE001
