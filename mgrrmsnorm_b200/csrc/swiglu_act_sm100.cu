@@ -13,8 +13,8 @@ namespace {
 
 // 16-bit types: MUFU exp + MUFU reciprocal (about 2 ulp in fp32, far below the rounding of the output). With an IEEE
 // division the 16-bit kernels, which do twice the arithmetic per byte of the fp32 ones, were held back by it: fp16
-// forward 0.87 of the copy bandwidth with the division, 0.97 without (65 536 x 6912; 4096 rows: 0.78 -> 0.90; bf16
-// 0.88 -> 0.88-0.92). fp32 keeps the division: it runs at 0.99 with it and measured 0.95 without.
+// and bf16 forward 0.87 of the copy bandwidth with the division, 0.97 without (65 536 x 6912; 4096 rows: 0.78 -> 0.90).
+// fp32 keeps the division: it runs at 0.99 with it and measured 0.95 without.
 template <typename T>
 __device__ __forceinline__ float sigmoidf_(float g) {
     if constexpr (sizeof(T) == 2) return __fdividef(1.0f, 1.0f + __expf(-g));
